@@ -1,0 +1,45 @@
+// Gated activation of the feed-forward: out = act(gate) * up, act = SiLU,
+// computed in float32 (reference backend/model.cu:477-483:
+// g / (1 + expf(-g)) * u).  gate and up may be the two halves of one fused
+// projection output: each has its own row stride.
+#include "common.cuh"
+
+KLLM_EXPORT_LAST_ERROR(activation)
+
+namespace {
+
+template <typename T>
+__global__ void silu_mul_kernel(T* __restrict__ out, int64_t out_stride,
+                                const T* __restrict__ gate, int64_t gate_stride,
+                                const T* __restrict__ up, int64_t up_stride, int n, int f) {
+    const int64_t total = (int64_t)n * f;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = idx / f;
+        const int c = (int)(idx - r * f);
+        const float g = to_f32(gate[r * gate_stride + c]);
+        const float u = to_f32(up[r * up_stride + c]);
+        out[r * out_stride + c] = from_f32<T>((g / (1.f + expf(-g))) * u);
+    }
+}
+
+}  // namespace
+
+extern "C" int kllm_silu_mul(void* out, int64_t out_stride, const void* gate, int64_t gate_stride,
+                             const void* up, int64_t up_stride, int n, int f, int dtype,
+                             void* stream) {
+    if (n <= 0 || f <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int64_t total = (int64_t)n * f;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dtype == KLLM_F32)
+        silu_mul_kernel<float><<<(unsigned)blocks, 256, 0, s>>>(
+            (float*)out, out_stride, (const float*)gate, gate_stride, (const float*)up, up_stride, n, f);
+    else if (dtype == KLLM_BF16)
+        silu_mul_kernel<bf16><<<(unsigned)blocks, 256, 0, s>>>(
+            (bf16*)out, out_stride, (const bf16*)gate, gate_stride, (const bf16*)up, up_stride, n, f);
+    else
+        KLLM_FAIL("silu_mul: unknown element type %d", dtype);
+    KLLM_LAUNCH_STATUS();
+}

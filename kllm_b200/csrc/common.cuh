@@ -1,0 +1,87 @@
+// Shared helpers of the sm_100a kernels: element types, conversions, reductions
+// and the launch-status convention.
+//
+// Every exported launcher has C linkage, takes raw device pointers plus a
+// cudaStream_t (as void*), allocates nothing, and returns 0 or a positive
+// cudaError_t from the launch; argument errors return a negative code and leave a
+// message for kllm_last_error().  Element type codes: 0 = float32, 1 = bfloat16.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define KLLM_F32 0
+#define KLLM_BF16 1
+
+#define KLLM_ERR_ARG (-2)
+
+static thread_local char g_kllm_err[512];
+
+#define KLLM_FAIL(...)                                         \
+    do {                                                       \
+        snprintf(g_kllm_err, sizeof(g_kllm_err), __VA_ARGS__); \
+        return KLLM_ERR_ARG;                                   \
+    } while (0)
+
+#define KLLM_LAUNCH_STATUS()                                                   \
+    do {                                                                       \
+        cudaError_t e__ = cudaGetLastError();                                  \
+        if (e__ != cudaSuccess) {                                              \
+            snprintf(g_kllm_err, sizeof(g_kllm_err), "%s:%d: %s", __FILE__,    \
+                     __LINE__, cudaGetErrorString(e__));                       \
+            return (int)e__;                                                   \
+        }                                                                      \
+        return 0;                                                              \
+    } while (0)
+
+#define KLLM_EXPORT_LAST_ERROR(libname)                                 \
+    extern "C" const char* kllm_last_error_##libname() { return g_kllm_err; }
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  The
+// order of the additions is fixed by the thread count alone, so a row's result
+// does not depend on which other rows are in the launch.
+__device__ __forceinline__ float block_sum(float v, float* red /* [32] shared */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_sum(v);
+    __syncthreads();  // protect red from a previous use
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    const int nw = (blockDim.x + 31) >> 5;
+    float t = (lane < nw) ? red[lane] : 0.f;
+    t = warp_sum(t);
+    return t;
+}
+
+__device__ __forceinline__ float block_max(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    const int nw = (blockDim.x + 31) >> 5;
+    float t = (lane < nw) ? red[lane] : -INFINITY;
+    t = warp_max(t);
+    return t;
+}

@@ -1,0 +1,70 @@
+// RMSNorm with the residual sum folded in.
+//
+//   x[r,:] (+)= res[r,:]          residual stream, float32, written back
+//   out[r,:] = x[r,:] * rsqrt(mean(x^2) + eps) * gain[:]
+//
+// The sum of squares, the scale and the residual sum are float32 whatever the
+// element type of `res` and `out` is.  One block per row; the order of the
+// additions depends on the row width and the block size only.
+// Formula: reference backend/model.cu:101-122 (norm) and :144-165 (sum + norm).
+#include "common.cuh"
+
+KLLM_EXPORT_LAST_ERROR(norm)
+
+namespace {
+
+constexpr int kThreads = 256;
+
+// rows == nullptr: row r of x/res, x is written back.
+// rows != nullptr: row rows[r] of x/res is read, nothing is written back (used to
+// normalise only the rows whose logits are wanted).
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ res, T* __restrict__ out,
+                   const float* __restrict__ gain, const int* __restrict__ rows,
+                   int d, float eps) {
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const int64_t src = rows ? (int64_t)rows[r] : (int64_t)r;
+    float* xr = x + src * d;
+    const T* rr = res ? res + src * d : nullptr;
+    T* orow = out + (int64_t)r * d;
+    const bool write_back = (rows == nullptr) && (res != nullptr);
+
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += kThreads) {
+        float v = xr[i];
+        if (rr) {
+            v += to_f32(rr[i]);
+            if (write_back) xr[i] = v;
+        }
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float scale = rsqrtf(ss / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += kThreads) {
+        float v = xr[i];
+        if (rr && !write_back) v += to_f32(rr[i]);
+        orow[i] = from_f32<T>(v * scale * gain[i]);
+    }
+}
+
+}  // namespace
+
+extern "C" int kllm_add_rmsnorm(void* x, const void* res, void* out, const void* gain,
+                                const int* rows, int n_rows, int d, float eps, int dtype,
+                                void* stream) {
+    if (n_rows <= 0) return 0;
+    if (d <= 0) KLLM_FAIL("rmsnorm: width %d must be positive", d);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == KLLM_F32) {
+        add_rmsnorm_kernel<float><<<n_rows, kThreads, 0, s>>>(
+            (float*)x, (const float*)res, (float*)out, (const float*)gain, rows, d, eps);
+    } else if (dtype == KLLM_BF16) {
+        add_rmsnorm_kernel<bf16><<<n_rows, kThreads, 0, s>>>(
+            (float*)x, (const bf16*)res, (bf16*)out, (const float*)gain, rows, d, eps);
+    } else {
+        KLLM_FAIL("rmsnorm: unknown element type %d", dtype);
+    }
+    KLLM_LAUNCH_STATUS();
+}

@@ -1,0 +1,153 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+A batch may hold portions of prompts beside single decoded tokens, cut anywhere.
+It runs only the tokens it is given, as one batch, against the cache that earlier
+steps left, and returns float32 logits at the places that were asked for.  This
+is the role of ``te_forward_batch`` (reference backend/model.cu:995-1195) with two
+differences: logits come from the places the caller names (the reference returns
+each request's last row, :1184-1188), and the per-step token budget is a knob of
+its own (the reference ties it to the sequence cap, engine/engine.go:18).
+
+Everything is validated on the host before anything is launched (as :1000-1043):
+an invalid step changes neither the cache nor the device.  Pages are reserved for
+all entries together or not at all, and committed after the launch.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager, OutOfPages, RequestCache
+from ..parts.context import StepContext
+from ..parts.model import DecoderModel
+
+
+class StepError(ValueError):
+    """The batch is not one this engine can run; nothing was changed."""
+
+
+@dataclass
+class StepEntry:
+    request: RequestCache
+    tokens: Sequence[int]
+    want: Sequence[int] = ()      # places among ``tokens`` whose logits are wanted
+
+
+class StepRunner:
+    def __init__(self, model: DecoderModel, cache: CacheManager, max_step_tokens: int,
+                 max_batch: int, max_seq: int):
+        self.model = model
+        self.cache = cache
+        self.max_step_tokens = int(max_step_tokens)
+        self.max_batch = int(max_batch)
+        self.max_seq = int(min(max_seq, model.spec.max_position))
+        self.vocab = model.spec.vocab_size
+        self.device = model.device
+        self.steps = 0
+        self.tokens_run = 0
+
+    # ---- validation --------------------------------------------------------
+    def validate(self, entries: Sequence[StepEntry]) -> None:
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        if len(entries) > self.max_batch:
+            raise StepError(f"{len(entries)} requests in one step, the batch limit is {self.max_batch}")
+        seen = set()
+        total = 0
+        for e in entries:
+            r = e.request
+            if r.closed or self.cache.live.get(r.rid) is not r:
+                raise StepError(f"request {r.rid} is not open")
+            if r.rid in seen:
+                raise StepError(f"request {r.rid} appears twice in one step")
+            seen.add(r.rid)
+            n = len(e.tokens)
+            if n == 0:
+                raise StepError(f"request {r.rid} brings no tokens")
+            if r.length + n > self.max_seq:
+                raise StepError(f"request {r.rid}: positions [{r.length},{r.length + n}) exceed the "
+                                f"sequence limit {self.max_seq}")
+            for t in e.tokens:
+                if not (0 <= int(t) < self.vocab):
+                    raise StepError(f"request {r.rid}: token id {t} outside the vocabulary of {self.vocab}")
+            for w in e.want:
+                if not (0 <= int(w) < n):
+                    raise StepError(f"request {r.rid}: wanted place {w} outside its {n} tokens")
+            total += n
+        if total > self.max_step_tokens:
+            raise StepError(f"{total} tokens in one step, the budget is {self.max_step_tokens}")
+
+    # ---- the batch on the device ---------------------------------------------
+    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+        S = len(entries)
+        n_new = [len(e.tokens) for e in entries]
+        start = [e.request.length for e in entries]
+        n = sum(n_new)
+        want_rows: List[int] = []
+        q_start = [0]
+        for e, cnt in zip(entries, n_new):
+            want_rows.extend(q_start[-1] + int(w) for w in e.want)
+            q_start.append(q_start[-1] + cnt)
+        R = len(want_rows)
+        widths = []
+        for gi in range(len(self.cache.groups)):
+            widths.append(max(1, max(len(e.request.tables[gi]) for e in entries)))
+        sizes = [n, n, n, S + 1, S, S, S, max(R, 1)] + [S * w for w in widths]
+        offs = np.concatenate([[0], np.cumsum(sizes)])
+        host = torch.empty(int(offs[-1]), dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        h = host.numpy()
+        h[offs[0]:offs[1]] = np.fromiter((int(t) for e in entries for t in e.tokens), dtype=np.int32, count=n)
+        h[offs[1]:offs[2]] = np.concatenate([np.arange(s, s + c, dtype=np.int32) for s, c in zip(start, n_new)])
+        h[offs[2]:offs[3]] = np.repeat(np.arange(S, dtype=np.int32), n_new)
+        h[offs[3]:offs[4]] = q_start
+        h[offs[4]:offs[5]] = start
+        h[offs[5]:offs[6]] = [s + c for s, c in zip(start, n_new)]
+        h[offs[6]:offs[7]] = [e.request.state_slot for e in entries]
+        h[offs[7]:offs[8]] = (want_rows + [0] * (max(R, 1) - R))
+        for gi, w in enumerate(widths):
+            tab = np.full((S, w), -1, dtype=np.int32)
+            for si, e in enumerate(entries):
+                t = e.request.tables[gi]
+                tab[si, :len(t)] = t
+            h[offs[8 + gi]:offs[9 + gi]] = tab.reshape(-1)
+        dev = host.to(self.device, non_blocking=True)
+
+        def part(i):
+            return dev[int(offs[i]):int(offs[i + 1])]
+
+        tables = {gi: part(8 + gi).view(S, w) for gi, w in enumerate(widths)}
+        return StepContext(
+            n_tokens=n, n_requests=S, token_ids=part(0), positions=part(1), token_req=part(2),
+            q_start=part(3), start_pos=part(4), ctx_len=part(5), state_slots=part(6),
+            block_tables=tables, want_rows=part(7)[:R], n_want=R,
+            host_n_new=n_new, host_start_pos=start, max_new=max(n_new),
+            max_ctx=max(s + c for s, c in zip(start, n_new)), all_single=all(c == 1 for c in n_new))
+
+    # ---- run ---------------------------------------------------------------
+    def run(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Logits float32 [wanted, vocab] on the device, in the order of the entries
+        and of each entry's ``want``; None if nothing is wanted.  Raises ``StepError``
+        for an invalid batch and ``OutOfPages`` when the cache cannot hold it; in both
+        cases nothing has changed."""
+        self.validate(entries)
+        wants = [(e.request, len(e.tokens)) for e in entries]
+        if not self.cache.can_reserve_all(wants):
+            raise OutOfPages(f"the step's {sum(n for _, n in wants)} tokens do not fit the free pages "
+                             f"{self.cache.free_pages()}")
+        for r, n in wants:
+            self.cache.reserve(r, n)
+        try:
+            ctx = self.build_context(entries)
+            logits = self.model.forward(ctx, self.cache.layer_caches(ctx.block_tables))
+        except Exception:
+            for r, _ in wants:
+                self.cache.trim_reservation(r)
+            raise
+        for r, n in wants:
+            self.cache.commit(r, n)
+        self.steps += 1
+        self.tokens_run += sum(n for _, n in wants)
+        return logits

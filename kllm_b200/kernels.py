@@ -1,0 +1,212 @@
+"""Python faces of the CUDA kernels: each takes torch tensors on a CUDA device,
+checks what the kernel assumes, and launches on torch's current stream.
+
+The libraries are compiled and loaded on first use (``csrc/build.py``).  There is
+no CPU or library fallback here: a tensor that is not on a CUDA device is an error.
+``launches`` counts the kernels launched through this module (a captured CUDA
+graph replays its launches without passing through here; the graph runner adds
+its own count).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .csrc.build import load_library
+
+launches = 0
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DT[dtype]
+    except KeyError:
+        raise KernelError(f"kernels take float32 or bfloat16, not {dtype}") from None
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernel operand is not on a CUDA device (there is no CPU path)")
+
+
+def _check(lib, name: str, rc: int):
+    global launches
+    if rc != 0:
+        fn = getattr(lib, "kllm_last_error_" + name)
+        fn.restype = ctypes.c_char_p
+        raise KernelError(f"{name}: {fn().decode(errors='replace')} (code {rc})")
+    launches += 1
+
+
+def _i32(t: Optional[torch.Tensor], what: str):
+    if t is not None and (t.dtype != torch.int32 or not t.is_contiguous()):
+        raise KernelError(f"{what} must be a contiguous int32 tensor")
+
+
+def embed(out_x: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
+    """out_x[t,:] = float32(table[ids[t],:]); out_x float32 [n, d]."""
+    _cuda(out_x, table, ids)
+    _i32(ids, "ids")
+    n, d = out_x.shape
+    if out_x.dtype != torch.float32 or not out_x.is_contiguous() or not table.is_contiguous():
+        raise KernelError("embed: residual stream must be contiguous float32")
+    if table.shape[1] != d or ids.numel() != n:
+        raise KernelError("embed: shapes do not agree")
+    lib = load_library("embedding")
+    rc = lib.kllm_embed(_p(out_x), _p(table), _p(ids), n, d, table.shape[0], dtype_code(table.dtype), _stream())
+    _check(lib, "embedding", rc)
+
+
+def gather_rows(out: torch.Tensor, src: torch.Tensor, rows: torch.Tensor) -> None:
+    """out[r,:] = src[rows[r],:] for contiguous 2-D tensors of one dtype."""
+    _cuda(out, src, rows)
+    _i32(rows, "rows")
+    if out.dtype != src.dtype or not out.is_contiguous() or not src.is_contiguous() or out.shape[1] != src.shape[1]:
+        raise KernelError("gather_rows: operands do not agree")
+    lib = load_library("embedding")
+    rc = lib.kllm_gather_rows(_p(out), _p(src), _p(rows), rows.numel(),
+                              ctypes.c_int64(src.shape[1] * src.element_size()), _stream())
+    _check(lib, "embedding", rc)
+
+
+def add_rmsnorm(x: torch.Tensor, res: Optional[torch.Tensor], out: torch.Tensor, gain: torch.Tensor,
+                eps: float, rows: Optional[torch.Tensor] = None) -> None:
+    """x (+)= res in float32, out = rmsnorm(x) * gain.
+
+    ``rows`` given: out[r] comes from row rows[r] of x (+ res) and x is not written.
+    """
+    _cuda(x, res, out, gain, rows)
+    _i32(rows, "rows")
+    d = x.shape[1]
+    if x.dtype != torch.float32 or gain.dtype != torch.float32 or not x.is_contiguous() or not out.is_contiguous():
+        raise KernelError("add_rmsnorm: x and gain must be float32, contiguous")
+    if res is not None and (res.dtype != out.dtype or not res.is_contiguous() or res.shape != x.shape):
+        raise KernelError("add_rmsnorm: res must match x in shape and out in dtype")
+    if gain.numel() != d or out.shape[1] != d:
+        raise KernelError("add_rmsnorm: widths do not agree")
+    n_rows = out.shape[0]
+    if rows is None and n_rows != x.shape[0]:
+        raise KernelError("add_rmsnorm: row counts do not agree")
+    if rows is not None and rows.numel() != n_rows:
+        raise KernelError("add_rmsnorm: rows and out do not agree")
+    lib = load_library("norm")
+    rc = lib.kllm_add_rmsnorm(_p(x), _p(res), _p(out), _p(gain), _p(rows), n_rows, d,
+                              ctypes.c_float(eps), dtype_code(out.dtype), _stream())
+    _check(lib, "norm", rc)
+
+
+def rope_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cos_sin: Optional[torch.Tensor],
+                positions: torch.Tensor, token_req: torch.Tensor, block_table: Optional[torch.Tensor],
+                kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor],
+                n_heads: int, n_kv: int, head_dim: int) -> None:
+    """Rotate q in place; write rotated k and v into the paged cache.
+
+    q, k, v are 2-D views (rows may be strided, the last dim is dense); caches are
+    [pages, n_kv, page_size, head_dim].  With kcache None only q is rotated; with
+    cos_sin None nothing is rotated and k, v are only stored.
+    """
+    _cuda(q, k, v, cos_sin, positions, token_req, block_table, kcache, vcache)
+    _i32(positions, "positions"); _i32(token_req, "token_req"); _i32(block_table, "block_table")
+    for t in (q, k, v):
+        if t.stride(1) != 1:
+            raise KernelError("rope_append: q, k, v rows must be dense")
+    if cos_sin is not None and (cos_sin.dtype != torch.float32 or not cos_sin.is_contiguous()):
+        raise KernelError("rope_append: the cos/sin table must be contiguous float32")
+    n = q.shape[0]
+    rot = cos_sin.shape[1] if cos_sin is not None else 0
+    if kcache is not None:
+        if kcache.shape != vcache.shape or kcache.shape[1] != n_kv or kcache.shape[3] != head_dim \
+                or not kcache.is_contiguous() or not vcache.is_contiguous() or kcache.dtype != q.dtype:
+            raise KernelError("rope_append: cache layout must be [pages, n_kv, page_size, head_dim] in q's dtype")
+        page_size, max_blocks = kcache.shape[2], block_table.shape[1]
+    else:
+        page_size, max_blocks = 1, 0
+    lib = load_library("rope")
+    rc = lib.kllm_rope_append(_p(q), ctypes.c_int64(q.stride(0)), _p(k), ctypes.c_int64(k.stride(0)),
+                              _p(v), ctypes.c_int64(v.stride(0)), _p(cos_sin), _p(positions),
+                              _p(token_req), _p(block_table), max_blocks, _p(kcache), _p(vcache),
+                              n, n_heads, n_kv, head_dim, rot, page_size, dtype_code(q.dtype), _stream())
+    _check(lib, "rope", rc)
+
+
+def attention_generic(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
+                      positions: torch.Tensor, token_req: torch.Tensor, block_table: torch.Tensor,
+                      n_heads: int, n_kv: int, head_dim: int, window: int, scale: float) -> None:
+    """Causal GQA attention of every new token over its request's cached keys."""
+    _cuda(out, q, kcache, vcache, positions, token_req, block_table)
+    _i32(positions, "positions"); _i32(token_req, "token_req"); _i32(block_table, "block_table")
+    if q.stride(1) != 1 or not out.is_contiguous() or out.dtype != q.dtype or kcache.dtype != q.dtype:
+        raise KernelError("attention: operands must share a dtype; out contiguous, q rows dense")
+    if not kcache.is_contiguous() or not vcache.is_contiguous() or kcache.shape[1] != n_kv or kcache.shape[3] != head_dim:
+        raise KernelError("attention: cache layout must be [pages, n_kv, page_size, head_dim]")
+    n = q.shape[0]
+    lib = load_library("attention_generic")
+    rc = lib.kllm_attention_generic(_p(out), _p(q), ctypes.c_int64(q.stride(0)), _p(kcache), _p(vcache),
+                                    _p(positions), _p(token_req), _p(block_table), block_table.shape[1],
+                                    n, n_heads, n_kv, head_dim, kcache.shape[2], int(window or 0),
+                                    ctypes.c_float(scale), dtype_code(q.dtype), _stream())
+    _check(lib, "attention_generic", rc)
+
+
+def silu_mul(out: torch.Tensor, gate: torch.Tensor, up: torch.Tensor) -> None:
+    """out = silu(gate) * up; 2-D operands with dense rows (strided rows allowed)."""
+    _cuda(out, gate, up)
+    for t in (out, gate, up):
+        if t.stride(1) != 1 or t.dtype != out.dtype:
+            raise KernelError("silu_mul: operands must share a dtype and have dense rows")
+    n, f = out.shape
+    lib = load_library("activation")
+    rc = lib.kllm_silu_mul(_p(out), ctypes.c_int64(out.stride(0)), _p(gate), ctypes.c_int64(gate.stride(0)),
+                           _p(up), ctypes.c_int64(up.stride(0)), n, f, dtype_code(out.dtype), _stream())
+    _check(lib, "activation", rc)
+
+
+def sample(out: torch.Tensor, logits: torch.Tensor, temperature: Optional[torch.Tensor],
+           uniform: Optional[torch.Tensor]) -> None:
+    """out[r] = argmax (temperature[r] <= 0) or the inverse CDF of softmax(z/T) at uniform[r]."""
+    _cuda(out, logits, temperature, uniform)
+    _i32(out, "out")
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("sample: logits must be float32 with dense rows")
+    for t in (temperature, uniform):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous() or t.numel() != logits.shape[0]):
+            raise KernelError("sample: temperature and uniform must be float32 [rows]")
+    lib = load_library("sampling")
+    rc = lib.kllm_sample(_p(out), _p(logits), ctypes.c_int64(logits.stride(0)), logits.shape[0],
+                         logits.shape[1], _p(temperature), _p(uniform), _stream())
+    _check(lib, "sampling", rc)
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
+           out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """y = x @ weight^T through the vendor GEMM library (cuBLAS, via torch.mm), as
+    the reference does for every projection (backend/model.cu:496-503).
+
+    float32 operands run as true float32 (the reduced-precision TF32 mode stays
+    off); bfloat16 operands accumulate in float32.
+    """
+    _cuda(x, weight)
+    if torch.backends.cuda.matmul.allow_tf32:
+        raise KernelError("TF32 matmul mode is on; the float32 path must stay true 32-bit")
+    if out_dtype is not None and out_dtype != x.dtype:
+        return torch.mm(x, weight.t(), out_dtype=out_dtype)
+    if out is not None:
+        return torch.mm(x, weight.t(), out=out)
+    return torch.mm(x, weight.t())

@@ -1,0 +1,6 @@
+from .context import LayerCache, StepContext
+from .spec import (BlockSpec, BuildEnv, LayerCall, ModelSpec, PagedKVNeed, PartSpec, StateNeed,
+                   TensorSpec, part_factory, register_part)
+
+__all__ = ["LayerCache", "StepContext", "BlockSpec", "BuildEnv", "LayerCall", "ModelSpec",
+           "PagedKVNeed", "PartSpec", "StateNeed", "TensorSpec", "part_factory", "register_part"]

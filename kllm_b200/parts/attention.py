@@ -1,0 +1,93 @@
+"""Causal grouped-query attention over a paged cache: the mixer of a Llama layer.
+
+params: ``hidden``, ``n_heads``, ``n_kv_heads``, ``head_dim``; optional ``window``
+(None: every earlier key is visible; W: the last W keys, the query's own included),
+``scale`` (default 1/sqrt(head_dim)), ``position`` (a PartSpec of the position
+family, e.g. rotary; None for no position encoding).
+Tensors: ``<prefix>.{q,k,v,o}_proj.weight`` with shapes [H*hd, d], [G*hd, d],
+[G*hd, d], [d, H*hd]; no bias (reference backend/model.cu:1090-1104).  At bind time
+q, k and v are stacked into one [(H+2G)*hd, d] matrix so the three projections are
+one product.
+
+Interface of a mixer part:
+  ``cache_need()`` -> PagedKVNeed | StateNeed | None
+  ``forward(xn, ctx, cache) -> [n, hidden]`` in the model dtype, xn being the normed
+  input [n, hidden]; the residual sum is the block's business.
+The new keys and values of a step are written to the pages before attention runs,
+so a query sees the keys of its own portion through the cache, like every other
+key (reference :1096-1102).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import kernels
+from .spec import BuildEnv, PagedKVNeed, PartSpec, TensorSpec, part_factory, register_part
+
+
+class PagedAttention:
+    def __init__(self, spec: PartSpec, env: BuildEnv):
+        p = spec.params
+        self.hidden = int(p["hidden"])
+        self.n_heads = int(p["n_heads"])
+        self.n_kv = int(p["n_kv_heads"])
+        self.head_dim = int(p["head_dim"])
+        if self.n_heads % self.n_kv:
+            raise ValueError(f"{self.n_heads} heads are not a multiple of {self.n_kv} kv heads")
+        self.window = p.get("window")
+        self.scale = float(p.get("scale") or 1.0 / math.sqrt(self.head_dim))
+        self.q_dim = self.n_heads * self.head_dim
+        self.kv_dim = self.n_kv * self.head_dim
+        self.prefix = spec.prefix
+        self.dtype = env.dtype
+        pos = p.get("position")
+        self.position = part_factory("position", pos.kind)(pos, env) if pos is not None else None
+        self.w_qkv = None
+        self.w_o = None
+
+    def _names(self):
+        return {k: f"{self.prefix}.{k}_proj.weight" for k in "qkvo"}
+
+    def tensor_specs(self):
+        n = self._names()
+        return [TensorSpec(n["q"], (self.q_dim, self.hidden)),
+                TensorSpec(n["k"], (self.kv_dim, self.hidden)),
+                TensorSpec(n["v"], (self.kv_dim, self.hidden)),
+                TensorSpec(n["o"], (self.hidden, self.q_dim))] + \
+            (self.position.tensor_specs() if self.position else [])
+
+    def bind(self, tensors):
+        n = self._names()
+        self.w_qkv = torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]], dim=0).contiguous()
+        self.w_o = tensors[n["o"]]
+        if self.position:
+            self.position.bind(tensors)
+
+    def cache_need(self):
+        return PagedKVNeed(self.n_kv, self.head_dim, self.window)
+
+    def forward(self, xn, ctx, cache):
+        n = xn.shape[0]
+        if cache.writes:
+            qkv = kernels.linear(xn, self.w_qkv)
+            q = qkv[:, :self.q_dim]
+            k = qkv[:, self.q_dim:self.q_dim + self.kv_dim]
+            v = qkv[:, self.q_dim + self.kv_dim:]
+        else:  # reads keys and values that another layer call wrote
+            q = kernels.linear(xn, self.w_qkv[:self.q_dim])
+            k = v = q
+        if self.position is not None:
+            self.position.apply(q, k, v, ctx, cache, self.n_heads, self.n_kv)
+        elif cache.writes:
+            kernels.rope_append(q, k, v, None, ctx.positions, ctx.token_req, cache.block_table,
+                                cache.k, cache.v, self.n_heads, self.n_kv, self.head_dim)
+        attn = torch.empty((n, self.q_dim), dtype=self.dtype, device=xn.device)
+        kernels.attention_generic(attn, q, cache.k, cache.v, ctx.positions, ctx.token_req,
+                                  cache.block_table, self.n_heads, self.n_kv, self.head_dim,
+                                  self.window or 0, self.scale)
+        return kernels.linear(attn, self.w_o)
+
+
+register_part("mixer", "paged_attention", PagedAttention)

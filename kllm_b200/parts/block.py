@@ -1,0 +1,41 @@
+"""Arrangements of a layer's parts.
+
+``pre_norm``: x += mixer(norm1(x)); x += ff(norm2(x)), with the feed-forward's
+output handed on as ``pending`` and added inside the next norm (the next layer's
+first norm, or the model's final norm), as the reference does
+(backend/model.cu:1068-1072, 1083-1089, 1105, 1117).
+
+Interface of a block: ``forward(x, pending, ctx, cache) -> pending'``.  x is the
+float32 residual stream, updated in place; ``pending`` (model dtype, or None) is
+what is still to be added to x.
+"""
+from __future__ import annotations
+
+from .spec import BlockSpec, BuildEnv, part_factory, register_part
+
+
+class PreNormBlock:
+    def __init__(self, spec: BlockSpec, env: BuildEnv):
+        self.mixer = part_factory("mixer", spec.mixer.kind)(spec.mixer, env)
+        self.feed_forward = part_factory("feed_forward", spec.feed_forward.kind)(spec.feed_forward, env)
+        self.mixer_norm = part_factory("norm", spec.mixer_norm.kind)(spec.mixer_norm, env)
+        self.ff_norm = part_factory("norm", spec.ff_norm.kind)(spec.ff_norm, env)
+
+    def parts(self):
+        return [self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward]
+
+    def tensor_specs(self):
+        return [s for p in self.parts() for s in p.tensor_specs()]
+
+    def bind(self, tensors):
+        for p in self.parts():
+            p.bind(tensors)
+
+    def forward(self, x, pending, ctx, cache):
+        xn = self.mixer_norm.forward(x, pending)
+        mixed = self.mixer.forward(xn, ctx, cache)
+        xn = self.ff_norm.forward(x, mixed)
+        return self.feed_forward.forward(xn, ctx)
+
+
+register_part("block", "pre_norm", PreNormBlock)
