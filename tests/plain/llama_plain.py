@@ -86,38 +86,44 @@ def silu(x):
     return x / (1.0 + np.exp(-x))
 
 
-def swiglu(x, w_gate, w_up, w_down):
+def swiglu(x, w_gate, w_up, w_down, rnd=None):
     """down( silu(x Wg^T) * (x Wu^T) ) (backend/model.cu:1112-1115)."""
+    rnd = rnd or (lambda a: a)
     x = f64(x)
-    g = x @ f64(w_gate).T
-    u = x @ f64(w_up).T
-    return (silu(g) * u) @ f64(w_down).T
+    g = rnd(x @ f64(w_gate).T)
+    u = rnd(x @ f64(w_up).T)
+    return rnd(rnd(silu(g) * u) @ f64(w_down).T)
 
 
-def attention_block(x, w, prefix, cfg, positions):
+def _same(a):
+    return a
+
+
+def attention_block(x, w, prefix, cfg, positions, rnd=_same):
     """q, k, v projections without bias, rotary on q and k, attention, output
-    projection (backend/model.cu:1090-1104)."""
+    projection (backend/model.cu:1090-1104).  ``rnd`` rounds what a reduced-precision
+    engine stores between its kernels (identity for the exact yardstick)."""
     hd, nh, nkv = cfg["head_dim"], cfg["num_attention_heads"], cfg["num_key_value_heads"]
-    q = x @ f64(w[prefix + ".self_attn.q_proj.weight"]).T
-    k = x @ f64(w[prefix + ".self_attn.k_proj.weight"]).T
-    v = x @ f64(w[prefix + ".self_attn.v_proj.weight"]).T
-    q = rope(q, positions, nh, hd, cfg["rope_theta"])
-    k = rope(k, positions, nkv, hd, cfg["rope_theta"])
-    a = attention(q, k, v, nh, nkv, hd, window=cfg.get("sliding_window"))
-    return a @ f64(w[prefix + ".self_attn.o_proj.weight"]).T
+    q = rnd(x @ f64(w[prefix + ".self_attn.q_proj.weight"]).T)
+    k = rnd(x @ f64(w[prefix + ".self_attn.k_proj.weight"]).T)
+    v = rnd(x @ f64(w[prefix + ".self_attn.v_proj.weight"]).T)
+    q = rnd(rope(q, positions, nh, hd, cfg["rope_theta"]))
+    k = rnd(rope(k, positions, nkv, hd, cfg["rope_theta"]))
+    a = rnd(attention(q, k, v, nh, nkv, hd, window=cfg.get("sliding_window")))
+    return rnd(a @ f64(w[prefix + ".self_attn.o_proj.weight"]).T)
 
 
-def decoder_layer(x, w, layer, cfg, positions):
+def decoder_layer(x, w, layer, cfg, positions, rnd=_same):
     """Pre-norm block: x += attn(norm(x)); x += mlp(norm(x)).  The reference adds
     the feed-forward's output inside the next norm kernel, which is the same sum
     (backend/model.cu:1067-1118)."""
     prefix = f"model.layers.{layer}"
     eps = cfg["rms_norm_eps"]
-    xn = rmsnorm(x, w[prefix + ".input_layernorm.weight"], eps)
-    x = x + attention_block(xn, w, prefix, cfg, positions)
-    xn = rmsnorm(x, w[prefix + ".post_attention_layernorm.weight"], eps)
+    xn = rnd(rmsnorm(x, w[prefix + ".input_layernorm.weight"], eps))
+    x = x + attention_block(xn, w, prefix, cfg, positions, rnd)
+    xn = rnd(rmsnorm(x, w[prefix + ".post_attention_layernorm.weight"], eps))
     x = x + swiglu(xn, w[prefix + ".mlp.gate_proj.weight"], w[prefix + ".mlp.up_proj.weight"],
-                   w[prefix + ".mlp.down_proj.weight"])
+                   w[prefix + ".mlp.down_proj.weight"], rnd)
     return x
 
 
@@ -133,9 +139,11 @@ def normalise_config(cfg):
     return c
 
 
-def forward(w, cfg, ids, return_hidden=False):
+def forward(w, cfg, ids, return_hidden=False, rnd=_same):
     """Logits [T, V] in float64 at every position of one whole sequence
     (backend/model.cu:1056-1188; the reference keeps only the last row, :1184-1188).
+    With ``rnd=round_act_bf16`` every tensor that a bfloat16 engine stores between
+    two kernels is rounded to bfloat16 (the residual stream and the logits are not).
 
     ``lm_head.weight`` falls back to the embedding table when the configuration
     ties them (the reference resolves tying offline, tools/convert_hf.py:81-82).
@@ -145,9 +153,9 @@ def forward(w, cfg, ids, return_hidden=False):
     x = embed(w["model.embed_tokens.weight"], ids)
     hidden = [x.copy()]
     for layer in range(cfg["num_hidden_layers"]):
-        x = decoder_layer(x, w, layer, cfg, positions)
+        x = decoder_layer(x, w, layer, cfg, positions, rnd)
         hidden.append(x.copy())
-    xn = rmsnorm(x, w["model.norm.weight"], cfg["rms_norm_eps"])
+    xn = rnd(rmsnorm(x, w["model.norm.weight"], cfg["rms_norm_eps"]))
     hidden.append(xn.copy())
     head = w["lm_head.weight"] if "lm_head.weight" in w else w["model.embed_tokens.weight"]
     logits = xn @ f64(head).T
@@ -196,6 +204,11 @@ def round_bf16(a):
     bias = ((bits >> 16) & 1) + 0x7FFF
     out = (((bits + bias) >> 16) << 16).astype(np.uint32)
     return out.view(np.float32).reshape(a.shape)
+
+
+def round_act_bf16(a):
+    """float64 activations as a bfloat16 tensor would hold them."""
+    return round_bf16(np.asarray(a, dtype=np.float32)).astype(np.float64)
 
 
 def random_weights(cfg, seed, gain_std=0.0, std=0.02):

@@ -3,8 +3,7 @@ plain implementation; float32 and bfloat16; both tiny configurations."""
 import numpy as np
 import pytest
 
-from helpers import TINY, assert_close, make_weights, prompts_for, rounded_weights, write_model_dir
-from plain import llama_plain as plain
+from helpers import assert_close, make_weights, plain_logits, prompts_for, write_model_dir
 
 pytestmark = pytest.mark.gpu
 
@@ -17,14 +16,13 @@ def test_whole_prompts(tmp_path, name, dtype):
     from kllm_b200.engine import Engine, Options, StepEntry
     cfg, w = make_weights(name)
     d = write_model_dir(str(tmp_path / name), cfg, w)
-    ref_w = w if dtype == "float32" else rounded_weights(w)
     eng = Engine(d, Options(dtype=dtype, max_seq=cfg["max_position_embeddings"], block_size=16,
                             num_blocks=32, max_batch=4))
     for ids in prompts_for(cfg, LENGTHS[name], seed=1):
         req = eng.cache.open()
         logits = eng.step([StepEntry(req, ids, list(range(len(ids))))]).cpu().numpy()
         eng.cache.close(req)
-        want = plain.forward(ref_w, cfg, ids)
+        want = plain_logits(w, cfg, ids, dtype)
         assert logits.shape == want.shape
         assert_close(logits, want, dtype, f"{name} {dtype} len {len(ids)}")
     eng.cache.audit()

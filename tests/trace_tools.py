@@ -1,0 +1,85 @@
+"""Building step traces for ``bin/trace_run`` and reading back what it writes."""
+from __future__ import annotations
+
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TRACE_RUN = os.path.join(ROOT, "bin", "trace_run")
+
+
+def round64(n: int) -> int:
+    return -(-n // 64) * 64
+
+
+class TraceBuilder:
+    """Collects steps, remembers which (request, position) each written row is,
+    and tracks the most tokens that live requests hold (each rounded up to 64)."""
+
+    def __init__(self):
+        self.steps = []          # json records
+        self.rows = {}           # step -> list of (request id, absolute position)
+        self.held = {}           # live request id -> tokens held
+        self.peak = 0
+
+    def step(self, entries, end=()):
+        """entries: list of (rid, tokens, want places).  Positions follow from what
+        the request already holds."""
+        k = len(self.steps)
+        rec = {"step": k, "entries": [], "end": list(end)}
+        rows = []
+        for rid, tokens, want in entries:
+            start = self.held.get(rid, 0)
+            rec["entries"].append({"id": rid, "tokens": [int(t) for t in tokens], "want": [int(w) for w in want]})
+            rows.extend((rid, start + int(w)) for w in want)
+            self.held[rid] = start + len(tokens)
+        self.peak = max(self.peak, sum(round64(v) for v in self.held.values()))
+        for rid in end:
+            self.held.pop(rid, None)
+        if rows:
+            self.rows[k] = rows
+        self.steps.append(rec)
+        return k
+
+
+def run_trace(model_dir: str, dtype: str, builder: TraceBuilder, out_dir: str, vocab: int,
+              max_tokens: int = 0, timeout: float = 600.0):
+    """Run bin/trace_run on the trace, feeding a step only after the previous
+    ``done`` line.  Returns {(rid, position): logits row}."""
+    cmd = [sys.executable, TRACE_RUN, "--model", model_dir, "--dtype", dtype, "--out", out_dir,
+           "--max-tokens", str(max_tokens or builder.peak)]
+    proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, bufsize=1)
+    try:
+        for rec in builder.steps:
+            proc.stdin.write(json.dumps(rec) + "\n")
+            proc.stdin.flush()
+            line = proc.stdout.readline()
+            assert line.strip() == f"done {rec['step']}", f"trace_run answered {line!r} to step {rec['step']}"
+        proc.stdin.close()
+        rc = proc.wait(timeout=timeout)
+    finally:
+        if proc.poll() is None:
+            proc.kill()
+    assert rc == 0, f"trace_run exited with {rc}"
+    out = {}
+    for k, rows in builder.rows.items():
+        arr = np.fromfile(os.path.join(out_dir, f"{k}.f32"), dtype="<f4").reshape(len(rows), vocab)
+        for i, key in enumerate(rows):
+            assert key not in out, f"row {key} written twice"
+            out[key] = arr[i]
+    return out
+
+
+def portions(total: int, sizes):
+    """Cut ``total`` tokens into portions of the given sizes, cycling through them."""
+    out, i, done = [], 0, 0
+    while done < total:
+        n = min(sizes[i % len(sizes)], total - done)
+        out.append(n)
+        done += n
+        i += 1
+    return out
