@@ -90,7 +90,7 @@ class Engine:
         self.dtype = _DTYPES[opts.dtype]
         self.config: ModelConfig = load_config(model_dir)
         self.spec = build_model_spec(self.config)
-        with torch.inference_mode():
+        with torch.no_grad():
             self.model = DecoderModel(self.spec, self.dtype, self.device)
             tensors = load_weights(model_dir, self.model.tensor_specs(), self.dtype, self.device)
             self.model.bind(tensors)
@@ -108,12 +108,12 @@ class Engine:
     def new_sequence(self) -> Sequence_:
         return Sequence_(self)
 
-    @torch.inference_mode()
+    @torch.no_grad()
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """One batch through the model; see ``StepRunner.run``."""
         return self.runner.run(entries)
 
-    @torch.inference_mode()
+    @torch.no_grad()
     def generate(self, prompt: Union[Sequence[int], Sequence[Sequence[int]]], max_new_tokens: int = 16,
                  temperature: float = 0.0, seed: int = 0) -> Union[List[int], List[List[int]]]:
         """Token ids in, generated token ids out (host lists).  One prompt gives one

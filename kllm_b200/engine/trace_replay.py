@@ -54,7 +54,7 @@ def main(argv=None) -> int:
                                      block_size=args.page_size, num_blocks=pages,
                                      max_step_tokens=max(args.max_tokens, 1), max_batch=8))
     live = {}
-    with torch.inference_mode():
+    with torch.no_grad():
         for line in sys.stdin:
             line = line.strip()
             if not line:

@@ -1,0 +1,163 @@
+"""Generation through the Python entry point, the command line and the scheduler:
+greedy and temperature, alone and batched, long decoding, the first tokens of a
+sequence, pages running out."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from helpers import TOL, assert_close, make_weights, plain_logits, prompts_for, write_model_dir
+from plain import llama_plain as plain
+from plain import sampling_plain
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def check_choices(w, cfg, dtype, prompt, generated, temperature=0.0, seed=0, rid=0, eos=()):
+    """Every generated token is what the plain implementation would choose from
+    the same history, up to the rounding allowed between engine and plain."""
+    ids = list(prompt) + list(generated)
+    logits = plain_logits(w, cfg, ids[:-1], dtype)
+    slack = TOL[dtype] * np.abs(logits).max()
+    for i, tok in enumerate(generated):
+        row = logits[len(prompt) - 1 + i]
+        if temperature <= 0:
+            assert row[tok] >= row.max() - 2 * slack, f"token {i}: {tok} is not the maximum"
+            top2 = np.sort(row)[-2:]
+            if top2[1] - top2[0] > 2 * slack:           # no near tie: the choice is forced
+                assert tok == plain.argmax_first(row), f"token {i}"
+        else:
+            u = sampling_plain.uniform(seed, rid, i)
+            cdf = np.cumsum(plain.temperature_probs(row, temperature))
+            lo = cdf[tok - 1] if tok else 0.0
+            eps = 4 * slack / temperature + 1e-5         # how far rounding can move a CDF edge
+            assert lo - eps <= u <= cdf[tok] + eps, f"draw {i}: token {tok} does not bracket u={u}"
+        if i < len(generated) - 1:
+            assert tok not in eos, "generation went on after EOS"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_through_the_entry_point(tmp_path, name, dtype):
+    import kllm_b200
+    cfg, w = make_weights(name)
+    d = write_model_dir(str(tmp_path / "m"), cfg, w)
+    prompts = prompts_for(cfg, [5, 17, 31, 64] if name == "A" else [1, 3, 40, 100], seed=1)
+    steps = 16 if name == "A" else 24
+    outs = kllm_b200.generate(d, prompts, steps=steps, max_seq=cfg["max_position_embeddings"], dtype=dtype)
+    eos = (cfg["eos_token_id"],) if "eos_token_id" in cfg else ()
+    for p, out in zip(prompts, outs):
+        assert 1 <= len(out) <= steps and (len(out) == steps or out[-1] in eos)
+        check_choices(w, cfg, dtype, p, out, eos=eos)
+    solo = kllm_b200.generate(d, prompts[2], steps=steps, max_seq=cfg["max_position_embeddings"], dtype=dtype)
+    if dtype == "float32":
+        assert solo == outs[2]                      # batching is invisible
+        assert solo == plain.greedy_generate(w, cfg, prompts[2], steps, eos=set(eos))
+
+
+def test_temperature_is_reproducible_and_independent_of_batching(tmp_path):
+    from kllm_b200.engine import Engine, Options, Scheduler
+    cfg, w = make_weights("B")
+    d = write_model_dir(str(tmp_path / "m"), cfg, w)
+    prompts = prompts_for(cfg, [1, 3, 40, 100, 128, 200], seed=3)
+    eng = Engine(d, Options(dtype="float32", max_seq=256, num_blocks=80, max_batch=4, max_step_tokens=64))
+    runs = []
+    for order in (range(6), reversed(range(6))):          # different batch compositions
+        sched = Scheduler(eng)
+        reqs = {}
+        for i in order:
+            reqs[i] = sched.submit(prompts[i], 24, temperature=0.8, seed=1234)
+            reqs[i].rid = 100 + i                          # the draw is keyed by the request id
+        sched.run()
+        runs.append({i: r.generated for i, r in reqs.items()})
+        assert eng.cache.free_pages() == [80]
+    assert runs[0] == runs[1]
+    for i, p in enumerate(prompts):
+        check_choices(w, cfg, "float32", p, runs[0][i], temperature=0.8, seed=1234, rid=100 + i, eos=(511,))
+    other = Scheduler(eng)
+    r = other.submit(prompts[3], 24, temperature=0.8, seed=99)
+    r.rid = 103
+    other.run()
+    assert r.generated != runs[0][3]                      # another seed, other draws
+    eng.close()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_temperature_draws_are_valid_in_both_dtypes(tmp_path, dtype):
+    import kllm_b200
+    cfg, w = make_weights("A")
+    d = write_model_dir(str(tmp_path / "m"), cfg, w)
+    p = prompts_for(cfg, [9], seed=8)[0]
+    out = kllm_b200.generate(d, p, steps=20, max_seq=128, dtype=dtype, temperature=1.3, seed=5)
+    check_choices(w, cfg, dtype, p, out, temperature=1.3, seed=5, rid=0)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_first_tokens(tmp_path, dtype):
+    """One token of prompt, then token by token to the end of the position range."""
+    from kllm_b200.engine import Engine, Options, StepEntry
+    cfg, w = make_weights("B")
+    d = write_model_dir(str(tmp_path / "m"), cfg, w)
+    ids = prompts_for(cfg, [256], seed=11)[0]
+    eng = Engine(d, Options(dtype=dtype, max_seq=256, block_size=16, num_blocks=16, max_batch=2))
+    req = eng.cache.open()
+    rows = [eng.step([StepEntry(req, [t], [0])])[0].float().cpu().numpy() for t in ids]
+    want = plain_logits(w, cfg, ids, dtype)
+    assert_close(np.stack(rows[:4]), want[:4], dtype, "the first tokens of a sequence")
+    assert_close(np.stack(rows), want, dtype, "256 tokens one by one")
+    from kllm_b200.engine import StepError
+    with pytest.raises(StepError, match="sequence limit"):
+        eng.step([StepEntry(req, [1], [0])])              # position 256 does not exist
+    assert req.length == 256
+    eng.close()
+
+
+def test_scheduler_on_the_gpu_with_pages_running_out(tmp_path):
+    """So few pages that requests are preempted and recomputed; tokens equal the
+    solo runs all the same."""
+    from kllm_b200.engine import Engine, Options, Scheduler
+    cfg, w = make_weights("A")
+    d = write_model_dir(str(tmp_path / "m"), cfg, w)
+    prompts = prompts_for(cfg, [30, 25, 40, 12, 33], seed=21)
+    eng = Engine(d, Options(dtype="float32", max_seq=128, block_size=4, num_blocks=28, max_batch=4,
+                            max_step_tokens=24))
+    sched = Scheduler(eng)
+    reqs = [sched.submit(p, 30) for p in prompts]
+    sched.run()
+    assert sched.metrics.preemptions >= 1
+    solo = Scheduler(eng)
+    for p, r in zip(prompts, reqs):
+        s = solo.submit(p, 30)
+        solo.run()
+        assert r.status == "finished" and r.generated == s.generated
+    eng.cache.audit()
+    assert eng.cache.free_pages() == [28]
+    eng.close()
+
+
+def test_command_line(tmp_path):
+    cfg, w = make_weights("A")
+    d = write_model_dir(str(tmp_path / "m"), cfg, w)
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "generate"), "--model", d, "--ids", "1 17 42 100 7",
+           "--steps", "6", "--max-seq", "64", "--dtype", "float32"]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    lines = out.stdout.strip().splitlines()
+    assert lines[0] == "prompt:    [1 17 42 100 7]"
+    assert lines[1].startswith("generated: [") and lines[1].endswith("]")
+    toks = [int(t) for t in lines[1][len("generated: ["):-1].split()]
+    assert toks == plain.greedy_generate(w, cfg, [1, 17, 42, 100, 7], 6)
+    bad = subprocess.run(cmd[:4] + ["--ids", "1 x 3"], capture_output=True, text=True, timeout=300)
+    assert bad.returncode != 0 and 'bad token id "x"' in bad.stderr
+    # random-weights mode from the command line
+    cfgfile = tmp_path / "cfg.json"
+    import json
+    cfgfile.write_text(json.dumps(cfg))
+    rnd = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "generate"), "--model", str(tmp_path / "r"),
+                          "--random-config", str(cfgfile), "--random-seed", "3", "--steps", "4"],
+                         capture_output=True, text=True, timeout=300)
+    assert rnd.returncode == 0, rnd.stderr
+    assert os.path.exists(tmp_path / "r" / "model.safetensors") and "generated: [" in rnd.stdout

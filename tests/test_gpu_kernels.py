@@ -1,0 +1,301 @@
+"""Each kernel alone against a plain float64 formula, at sizes other than the
+tiny models': widths and vocabularies that are no power of two, head sizes in
+steps of 16, odd head counts, scattered pages.  Where random numbers would hide a
+fault the inputs are made so that it shows: one far key that must win, a key just
+outside a window that must not be seen, NaN in every cache slot that must not be
+read."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from plain import llama_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL = {"float32": 1e-5, "bfloat16": 1.6e-2}      # relative to the largest |value|
+
+
+def dev(a, dtype=None):
+    t = torch.as_tensor(np.asarray(a)).cuda()
+    return t.to(dtype) if dtype is not None else t
+
+
+def close(got, want, dtype, what=""):
+    got = got.detach().float().cpu().numpy().astype(np.float64)
+    scale = max(1e-9, np.abs(want).max())
+    err = np.abs(got - want).max()
+    assert err <= TOL[dtype] * scale, f"{what}: {err:.3e} > {TOL[dtype]:.0e} * {scale:.3e}"
+
+
+def as_stored(a, dtype):
+    """What the kernel sees of float32 data stored in the given dtype, as float64."""
+    return (plain.round_bf16(a) if dtype == "bfloat16" else np.asarray(a, np.float32)).astype(np.float64)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embed_and_gather(dtype):
+    from kllm_b200 import kernels
+    rng = np.random.default_rng(0)
+    table = rng.standard_normal((37, 24)).astype(np.float32)
+    ids = np.array([36, 0, 5, 5, 17], dtype=np.int32)
+    x = torch.empty((5, 24), dtype=torch.float32, device="cuda")
+    kernels.embed(x, dev(table, DT[dtype]), dev(ids))
+    assert np.array_equal(x.cpu().numpy().astype(np.float64), as_stored(table, dtype)[ids])
+    out = torch.empty((3, 24), dtype=torch.float32, device="cuda")
+    kernels.gather_rows(out, x, dev(np.array([4, 0, 2], dtype=np.int32)))
+    assert torch.equal(out, x[[4, 0, 2]])
+    bad = torch.empty((1, 24), dtype=torch.float32, device="cuda")
+    kernels.embed(bad, dev(table, DT[dtype]), dev(np.array([37], dtype=np.int32)))
+    assert torch.isnan(bad).all()          # an id outside the table is never looked up
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("d", [100, 2048 + 16, 7])
+def test_add_rmsnorm(dtype, d):
+    from kllm_b200 import kernels
+    rng = np.random.default_rng(d)
+    n, eps = 6, 3e-4
+    x0 = (rng.standard_normal((n, d)) * 3).astype(np.float32)
+    res = rng.standard_normal((n, d)).astype(np.float32)
+    gain = (1 + 0.3 * rng.standard_normal(d)).astype(np.float32)
+    res_s = as_stored(res, dtype)
+    x = dev(x0)
+    out = torch.empty((n, d), dtype=DT[dtype], device="cuda")
+    kernels.add_rmsnorm(x, dev(res, DT[dtype]), out, dev(gain), eps)
+    summed = x0.astype(np.float64) + res_s
+    close(x, summed, "float32", "residual sum is float32 in both dtypes")
+    close(out, plain.rmsnorm(summed, gain, eps), dtype, "norm")
+    # no residual: x untouched
+    x = dev(x0)
+    kernels.add_rmsnorm(x, None, out, dev(gain), eps)
+    assert np.array_equal(x.cpu().numpy(), x0)
+    close(out, plain.rmsnorm(x0, gain, eps), dtype, "norm without residual")
+    # chosen rows: only those are normalised, x is left alone
+    rows = np.array([5, 1, 1], dtype=np.int32)
+    x = dev(x0)
+    out3 = torch.empty((3, d), dtype=DT[dtype], device="cuda")
+    kernels.add_rmsnorm(x, dev(res, DT[dtype]), out3, dev(gain), eps, rows=dev(rows))
+    assert np.array_equal(x.cpu().numpy(), x0)
+    close(out3, plain.rmsnorm(summed[rows], gain, eps), dtype, "norm of chosen rows")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_silu_mul_on_strided_halves(dtype):
+    from kllm_b200 import kernels
+    rng = np.random.default_rng(1)
+    n, f = 5, 172
+    gu = (rng.standard_normal((n, 2 * f)) * 4).astype(np.float32)
+    t = dev(gu, DT[dtype])
+    out = torch.empty((n, f), dtype=DT[dtype], device="cuda")
+    kernels.silu_mul(out, t[:, :f], t[:, f:])
+    s = as_stored(gu, dtype)
+    close(out, plain.silu(s[:, :f]) * s[:, f:], dtype)
+
+
+def paged(k, v, page_size, n_pages, rng, dtype, lengths):
+    """Scatter per-request dense k, v [len, G, hd] into caches [pages, G, page_size, hd]
+    through random block tables; every slot that holds nothing is NaN."""
+    G, hd = k[0].shape[1:]
+    kc = np.full((n_pages, G, page_size, hd), np.nan, dtype=np.float32)
+    vc = np.full_like(kc, np.nan)
+    free = list(rng.permutation(n_pages))
+    width = max(-(-L // page_size) for L in lengths)
+    table = np.full((len(lengths), width), -1, dtype=np.int32)
+    for s, L in enumerate(lengths):
+        for j in range(-(-L // page_size)):
+            pg = int(free.pop())
+            table[s, j] = pg
+            lo, hi = j * page_size, min(L, (j + 1) * page_size)
+            kc[pg, :, :hi - lo] = k[s][lo:hi].transpose(1, 0, 2)
+            vc[pg, :, :hi - lo] = v[s][lo:hi].transpose(1, 0, 2)
+    return dev(kc, DT[dtype]), dev(vc, DT[dtype]), dev(table)
+
+
+def attention_case(dtype, H, G, hd, page_size, lengths, n_new, window, seed, plant=None):
+    """Requests with ``lengths`` cached tokens, the last ``n_new`` of each being this
+    step's queries.  Returns (got, want) for all queries."""
+    from kllm_b200 import kernels
+    rng = np.random.default_rng(seed)
+    ks, vs, qs, pos, req, want = [], [], [], [], [], []
+    for s, (L, nn) in enumerate(zip(lengths, n_new)):
+        k = rng.standard_normal((L, G, hd)).astype(np.float32)
+        v = rng.standard_normal((L, G, hd)).astype(np.float32)
+        q = rng.standard_normal((L, H, hd)).astype(np.float32)
+        if plant:
+            plant(s, q, k, v)
+        ks.append(k); vs.append(v)
+        full = plain.attention(as_stored(q, dtype).reshape(L, H * hd), as_stored(k, dtype).reshape(L, G * hd),
+                               as_stored(v, dtype).reshape(L, G * hd), H, G, hd, window=window)
+        want.append(full[L - nn:])
+        qs.append(q[L - nn:].reshape(nn, H * hd))
+        pos.extend(range(L - nn, L)); req.extend([s] * nn)
+    kc, vc, table = paged(ks, vs, page_size, sum(-(-L // page_size) for L in lengths) + 3, rng, dtype, lengths)
+    q = dev(np.concatenate(qs), DT[dtype])
+    out = torch.empty_like(q)
+    kernels.attention_generic(out, q, kc, vc, dev(np.array(pos, np.int32)), dev(np.array(req, np.int32)), table,
+                              H, G, hd, window or 0, 1.0 / math.sqrt(hd))
+    return out, np.concatenate(want)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,G,hd,page", [(6, 2, 80, 8), (5, 5, 48, 16), (7, 1, 16, 3), (2, 1, 256, 32)])
+def test_attention_shapes_pages_and_mixed_query_lengths(dtype, H, G, hd, page):
+    lengths, n_new = [70, 1, 33, 129], [70, 1, 2, 1]      # a whole prompt, a first token, a portion, a decode
+    got, want = attention_case(dtype, H, G, hd, page, lengths, n_new, None, seed=H * hd)
+    assert not torch.isnan(got).any(), "a slot beyond a request's length was read"
+    close(got, want, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_finds_one_far_key_among_hundreds(dtype):
+    H, G, hd, L = 4, 2, 32, 700
+    far = 3
+
+    def plant(s, q, k, v):
+        q[-1] *= 0.05
+        k[far, 1] = 8.0 * np.sign(q[-1, 2])              # kv head 1 serves heads 2, 3; key 3 lines up with head 2
+        q[-1, 2] = 3.0 * np.sign(q[-1, 2])
+
+    got, want = attention_case(dtype, H, G, hd, 16, [L], [1], None, seed=7, plant=plant)
+    close(got, want, dtype)
+    w = want.reshape(1, H, hd)
+    assert np.abs(w[0, 2]).max() > 0.5                       # the far key's value dominates head 2
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window", [1, 5, 16, 17, 64])
+def test_attention_window_edge(dtype, window):
+    H, G, hd, L = 2, 1, 16, 90
+
+    def plant(s, q, k, v):
+        # the key just outside the last query's window would swamp everything if it were seen
+        outside = L - 1 - window
+        if s == 0 and outside >= 0:
+            k[outside, 0] = 50.0 * q[-1, 0] / np.abs(q[-1, 0]).max()
+            v[outside, 0] = 1e4
+
+    got, want = attention_case(dtype, H, G, hd, 8, [L, 40], [L, 3], window, seed=window, plant=plant)
+    close(got, want, dtype)
+    assert float(got[L - 1].float().abs().max()) < 100.0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("rot", [48, 16, None])
+def test_rope_append(dtype, rot):
+    from kllm_b200 import kernels
+    rng = np.random.default_rng(3)
+    H, G, hd, page, max_pos, theta = 5, 5, 48, 8, 300, 5e5
+    positions = np.array([0, 1, 7, 8, 250, 299, 64], dtype=np.int32)
+    req = np.array([0, 0, 0, 0, 1, 1, 2], dtype=np.int32)
+    n = len(positions)
+    qkv = rng.standard_normal((n, (H + 2 * G) * hd)).astype(np.float32)
+    table = np.full((3, 40), -1, dtype=np.int32)
+    pages = rng.permutation(60)
+    for s in range(3):
+        table[s] = pages[s * 20:s * 20 + 20].repeat(2)[:40] if False else np.resize(pages[s * 20:(s + 1) * 20], 40)
+    table[:, 20:] = -1
+    table[1, 20:38] = np.arange(100, 118)               # request 1 reaches position 299: 38 pages
+    kc = torch.full((120, G, page, hd), float("nan"), dtype=DT[dtype], device="cuda")
+    vc = torch.full_like(kc, float("nan"))
+    t = dev(qkv, DT[dtype])
+    q, k, v = t[:, :H * hd], t[:, H * hd:(H + G) * hd], t[:, (H + G) * hd:]
+    cos_sin = None
+    if rot:
+        j = np.arange(rot // 2, dtype=np.float64)
+        ang = np.arange(max_pos, dtype=np.float64)[:, None] * theta ** (-2.0 * j / rot)
+        cos_sin = dev(np.concatenate([np.cos(ang), np.sin(ang)], 1).astype(np.float32))
+    kernels.rope_append(q, k, v, cos_sin, dev(positions), dev(req), dev(table), kc, vc, H, G, hd)
+    s = as_stored(qkv, dtype)
+
+    def rotated(x, heads):
+        x = x.reshape(n, heads, hd).copy()
+        if rot:
+            x[:, :, :rot] = plain.rope(x[:, :, :rot].reshape(n, heads * rot), positions, heads, rot, theta).reshape(n, heads, rot)
+        return x
+
+    close(q, rotated(s[:, :H * hd], H).reshape(n, H * hd), dtype, "q")
+    kw, vw = rotated(s[:, H * hd:(H + G) * hd], G), s[:, (H + G) * hd:].reshape(n, G, hd)
+    written = torch.zeros(120 * page, dtype=torch.bool)
+    for i in range(n):
+        pg, slot = table[req[i], positions[i] // page], positions[i] % page
+        close(kc[pg, :, slot], kw[i], dtype, f"k of token {i}")
+        close(vc[pg, :, slot], vw[i], dtype, f"v of token {i}")
+        written[pg * page + slot] = True
+    untouched = torch.isnan(kc.float()).all(dim=3).all(dim=1).reshape(-1).cpu()
+    assert torch.equal(untouched, ~written), "a slot other than the tokens' own was written"
+
+
+def test_rope_q_only_leaves_no_cache_write():
+    from kllm_b200 import kernels
+    q = torch.randn(3, 2 * 16, device="cuda")
+    q0 = q.clone()
+    cs = torch.cat([torch.ones(10, 8), torch.zeros(10, 8)], 1).cuda()
+    kernels.rope_append(q, q, q, cs, dev(np.array([1, 2, 3], np.int32)), dev(np.zeros(3, np.int32)), None, None, None, 2, 1, 16)
+    assert torch.equal(q, q0)               # cos 1, sin 0: identity
+
+
+def test_sampling_greedy_first_maximum_and_temperature():
+    from kllm_b200 import kernels
+    rng = np.random.default_rng(5)
+    V = 1000 + 3
+    z = rng.standard_normal((6, V)).astype(np.float32)
+    z[0, 17] = z[0, 900] = 9.0                     # a tie: the first wins
+    z[1, V - 1] = 12.0                             # the last element
+    z[2, :] = -1.0                                 # all equal: index 0
+    out = torch.empty(6, dtype=torch.int32, device="cuda")
+    kernels.sample(out, dev(z), None, None)
+    assert out.tolist()[:3] == [17, V - 1, 0]
+    assert out.tolist() == [plain.argmax_first(r) for r in z]
+    # temperature: the chosen index brackets u in the CDF of softmax(z / T)
+    temps = np.array([0.8, 0.0, 1.5, 0.3, 1.0, 2.0], dtype=np.float32)
+    for u in (0.0, 0.123, 0.5, 0.87, 0.999999):
+        us = np.full(6, u, dtype=np.float32)
+        kernels.sample(out, dev(z), dev(temps), dev(us))
+        got = out.tolist()
+        for r in range(6):
+            if temps[r] <= 0:
+                assert got[r] == plain.argmax_first(z[r])
+                continue
+            cdf = np.cumsum(plain.temperature_probs(z[r], temps[r]))
+            i = got[r]
+            lo = cdf[i - 1] if i else 0.0
+            assert lo - 1e-5 <= u <= cdf[i] + 1e-5, (r, u, i, lo, cdf[i])
+    # many draws follow the distribution
+    zz = np.array([[2.0, 1.0, 0.0, -1.0, 3.0]], dtype=np.float32).repeat(4000, 0)
+    us = ((np.arange(4000) + 0.5) / 4000).astype(np.float32)
+    out = torch.empty(4000, dtype=torch.int32, device="cuda")
+    kernels.sample(out, dev(zz), dev(np.full(4000, 0.7, np.float32)), dev(us))
+    freq = np.bincount(out.cpu().numpy(), minlength=5) / 4000
+    assert np.abs(freq - plain.temperature_probs(zz[0], 0.7)).max() < 2e-3
+
+
+def test_linear_is_true_float32_and_bf16_accumulates_in_float32():
+    from kllm_b200 import kernels
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal((33, 1000)).astype(np.float32)
+    w = rng.standard_normal((77, 1000)).astype(np.float32)
+    y = kernels.linear(dev(x), dev(w))
+    want = x.astype(np.float64) @ w.astype(np.float64).T
+    assert np.abs(y.cpu().numpy() - want).max() < 2e-4          # TF32 would be off by ~3e-2 here
+    yb = kernels.linear(dev(x, torch.bfloat16), dev(w, torch.bfloat16), out_dtype=torch.float32)
+    wb = plain.round_bf16(x).astype(np.float64) @ plain.round_bf16(w).astype(np.float64).T
+    assert yb.dtype == torch.float32 and np.abs(yb.cpu().numpy() - wb).max() < 2e-3
+
+
+def test_kernels_refuse_what_they_cannot_take():
+    from kllm_b200 import kernels
+    x = torch.zeros(2, 8)
+    with pytest.raises(kernels.KernelError, match="CUDA"):
+        kernels.add_rmsnorm(x, None, x.clone(), torch.ones(8), 1e-5)
+    q = torch.zeros(1, 2 * 272, device="cuda")
+    kc = torch.zeros(1, 1, 4, 272, device="cuda")
+    z = torch.zeros(1, dtype=torch.int32, device="cuda")
+    with pytest.raises(kernels.KernelError, match="head size"):
+        kernels.attention_generic(torch.empty_like(q), q, kc, kc, z, z, z.view(1, 1), 2, 1, 272, 0, 1.0)
+    with pytest.raises(kernels.KernelError, match="float32 or bfloat16"):
+        kernels.silu_mul(torch.zeros(1, 4, device="cuda", dtype=torch.float16),
+                         torch.zeros(1, 4, device="cuda", dtype=torch.float16),
+                         torch.zeros(1, 4, device="cuda", dtype=torch.float16))

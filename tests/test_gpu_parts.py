@@ -1,0 +1,301 @@
+"""Each part alone, built from its PartSpec with weights bound from a dict, against
+the plain formulas; a model whose layers differ, run twice or share a cache; and a
+toy architecture with a stateful mixer of its own, defined here and registered
+without touching the framework."""
+import math
+from dataclasses import dataclass
+
+import numpy as np
+import pytest
+import torch
+
+from plain import llama_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL = {"float32": 1e-5, "bfloat16": 2e-2}
+
+
+def close(got, want, dtype, what=""):
+    got = got.detach().float().cpu().numpy().astype(np.float64)
+    scale = max(1e-9, np.abs(want).max())
+    err = np.abs(got - want).max()
+    assert err <= TOL[dtype] * scale, f"{what}: {err:.3e} > {TOL[dtype]:.0e} * {scale:.3e}"
+
+
+def stored(a, dtype):
+    return (plain.round_bf16(a) if dtype == "bfloat16" else np.asarray(a, np.float32)).astype(np.float64)
+
+
+def env_for(dtype, hidden, max_position=64):
+    from kllm_b200.parts.spec import BuildEnv
+    return BuildEnv(dtype=DT[dtype], device=torch.device("cuda"), hidden_size=hidden, max_position=max_position)
+
+
+def bind(part, weights, dtype):
+    tensors = {}
+    for s in part.tensor_specs():
+        if s.name in weights:
+            t = torch.from_numpy(weights[s.name]).cuda()
+            tensors[s.name] = t.to(DT[dtype]) if s.store == "compute" else t
+    part.bind(tensors)
+
+
+def one_request_context(n, start=0):
+    """A StepContext of one request bringing n tokens at positions start.., with a
+    block table over pages 0..; built through the real cache manager."""
+    from kllm_b200.parts.context import StepContext
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device="cuda")
+    return StepContext(n_tokens=n, n_requests=1, token_ids=i32([0] * n), positions=i32(list(range(start, start + n))),
+                       token_req=i32([0] * n), q_start=i32([0, n]), start_pos=i32([start]), ctx_len=i32([start + n]),
+                       state_slots=i32([0]), block_tables={}, want_rows=i32(list(range(n))), n_want=n,
+                       host_n_new=[n], host_start_pos=[start], max_new=n, max_ctx=start + n, all_single=n == 1)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_norm_part(dtype):
+    from kllm_b200.parts.spec import PartSpec, part_factory
+    rng = np.random.default_rng(0)
+    d = 72
+    part = part_factory("norm", "rmsnorm")(PartSpec("rmsnorm", "n", {"width": d, "eps": 1e-3}), env_for(dtype, d))
+    gain = (1 + 0.2 * rng.standard_normal(d)).astype(np.float32)
+    bind(part, {"n.weight": gain}, dtype)
+    assert part.gain.dtype == torch.float32
+    x0 = rng.standard_normal((5, d)).astype(np.float32)
+    res = rng.standard_normal((5, d)).astype(np.float32)
+    x = torch.from_numpy(x0).cuda()
+    out = part.forward(x, torch.from_numpy(res).cuda().to(DT[dtype]))
+    assert out.dtype == DT[dtype]
+    close(out, plain.rmsnorm(x0 + stored(res, dtype), gain, 1e-3), dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_feed_forward_part(dtype):
+    from kllm_b200.parts.spec import PartSpec, part_factory
+    rng = np.random.default_rng(1)
+    d, f = 40, 108
+    part = part_factory("feed_forward", "gated_mlp")(
+        PartSpec("gated_mlp", "ff", {"hidden": d, "intermediate": f, "activation": "silu"}), env_for(dtype, d))
+    w = {f"ff.{k}_proj.weight": (rng.standard_normal(s) * 0.3).astype(np.float32)
+         for k, s in (("gate", (f, d)), ("up", (f, d)), ("down", (d, f)))}
+    bind(part, w, dtype)
+    x = rng.standard_normal((7, d)).astype(np.float32)
+    out = part.forward(torch.from_numpy(x).cuda().to(DT[dtype]), None)
+    rnd = plain.round_act_bf16 if dtype == "bfloat16" else (lambda a: a)
+    ws = {k: stored(v, dtype) for k, v in w.items()}
+    want = plain.swiglu(stored(x, dtype), ws["ff.gate_proj.weight"], ws["ff.up_proj.weight"],
+                        ws["ff.down_proj.weight"], rnd)
+    close(out, want, dtype)
+    with pytest.raises(ValueError, match="activation"):
+        part_factory("feed_forward", "gated_mlp")(
+            PartSpec("gated_mlp", "ff", {"hidden": d, "intermediate": f, "activation": "relu"}), env_for(dtype, d))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window", [None, 6])
+def test_attention_part_in_two_portions(dtype, window):
+    from kllm_b200.cache import CacheManager
+    from kllm_b200.parts.spec import PartSpec, part_factory
+    rng = np.random.default_rng(2)
+    d, H, G, hd, n = 48, 6, 3, 16, 21
+    spec = PartSpec("paged_attention", "a", {
+        "hidden": d, "n_heads": H, "n_kv_heads": G, "head_dim": hd, "window": window,
+        "position": PartSpec("rotary", "", {"head_dim": hd, "theta": 777.0})})
+    part = part_factory("mixer", "paged_attention")(spec, env_for(dtype, d))
+    w = {f"a.{k}_proj.weight": (rng.standard_normal(s) * 0.4).astype(np.float32)
+         for k, s in (("q", (H * hd, d)), ("k", (G * hd, d)), ("v", (G * hd, d)), ("o", (d, H * hd)))}
+    bind(part, w, dtype)
+    cache = CacheManager([part.cache_need()], page_size=4, num_pages=9, max_requests=2, dtype=DT[dtype], device="cuda")
+    assert cache.groups[0].window == window
+    req = cache.open()
+    x = rng.standard_normal((n, d)).astype(np.float32)
+    xt = torch.from_numpy(x).cuda().to(DT[dtype])
+    outs, start = [], 0
+    for cnt in (13, 8):
+        cache.reserve(req, cnt)
+        ctx = one_request_context(cnt, start)
+        table = torch.full((1, 8), -1, dtype=torch.int32)
+        table[0, :len(req.tables[0])] = torch.tensor(req.tables[0])
+        lc = cache.layer_caches({0: table.cuda()})[0]
+        outs.append(part.forward(xt[start:start + cnt], ctx, lc))
+        cache.commit(req, cnt)
+        start += cnt
+    cfg = {"head_dim": hd, "num_attention_heads": H, "num_key_value_heads": G, "rope_theta": 777.0,
+           "sliding_window": window}
+    ws = {"L.self_attn." + k[2:]: stored(v, dtype) for k, v in w.items()}
+    rnd = plain.round_act_bf16 if dtype == "bfloat16" else (lambda a: a)
+    want = plain.attention_block(stored(x, dtype), ws, "L", cfg, np.arange(n), rnd)
+    close(torch.cat(outs), want, dtype)
+    if window:
+        assert req.tables[0][0] == -1          # the window has passed the first page
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embedding_and_head_parts(dtype):
+    from kllm_b200.parts.spec import PartSpec, part_factory
+    rng = np.random.default_rng(3)
+    V, d = 53, 24
+    table = rng.standard_normal((V, d)).astype(np.float32)
+    emb = part_factory("embedding", "token_embedding")(PartSpec("token_embedding", "e", {"vocab": V, "width": d}), env_for(dtype, d))
+    head = part_factory("head", "linear_head")(PartSpec("linear_head", "h", {"vocab": V, "width": d, "tied_to": "e.weight"}), env_for(dtype, d))
+    t = {"e.weight": torch.from_numpy(table).cuda().to(DT[dtype])}
+    emb.bind(t)
+    head.bind(t)
+    ids = torch.tensor([52, 0, 7], dtype=torch.int32, device="cuda")
+    x = emb.forward(ids)
+    assert x.dtype == torch.float32 and np.array_equal(x.cpu().numpy().astype(np.float64), stored(table, dtype)[[52, 0, 7]])
+    logits = head.forward(x.to(DT[dtype]))
+    assert logits.dtype == torch.float32
+    close(logits, stored(table, dtype)[[52, 0, 7]] @ stored(table, dtype).T, dtype)
+
+
+# ---- a toy architecture defined in the test -----------------------------------
+
+class RunningMeanMixer:
+    """out_t = W . mean(x_0..x_t): needs the sum of a request's inputs so far and
+    their count, i.e. per-request state of fixed size, and no pages."""
+
+    def __init__(self, spec, env):
+        self.d = spec.params["hidden"]
+        self.name = spec.prefix + ".mix.weight"
+        self.dtype = env.dtype
+
+    def tensor_specs(self):
+        from kllm_b200.parts.spec import TensorSpec
+        return [TensorSpec(self.name, (self.d, self.d))]
+
+    def bind(self, tensors):
+        self.w = tensors[self.name]
+
+    def cache_need(self):
+        from kllm_b200.parts.spec import StateNeed
+        return StateNeed((self.d + 1,), "float32")
+
+    def forward(self, xn, ctx, cache):
+        out = torch.empty_like(xn)
+        row = 0
+        slots = ctx.state_slots.tolist()
+        for s, n in enumerate(ctx.host_n_new):
+            st = cache.state[slots[s]]
+            x = xn[row:row + n].float()
+            sums = st[:self.d] + torch.cumsum(x, dim=0)
+            counts = st[self.d] + torch.arange(1, n + 1, device=x.device, dtype=torch.float32)
+            out[row:row + n] = ((sums / counts[:, None]) @ self.w.float().t()).to(self.dtype)
+            st[:self.d] = sums[-1]
+            st[self.d] = counts[-1]
+            row += n
+        return out
+
+
+def toy_spec(cfg):
+    from kllm_b200.parts.spec import BlockSpec, LayerCall, ModelSpec, PartSpec
+    d = cfg.hidden
+    norm = {"width": d, "eps": 1e-5}
+    rotary = PartSpec("rotary", "", {"head_dim": 16, "theta": 100.0})
+    ff = lambda p: PartSpec("gated_mlp", p + ".mlp", {"hidden": d, "intermediate": 2 * d, "activation": "silu"})
+    blocks = [
+        BlockSpec("pre_norm", "layers.0", PartSpec("toy_running_mean", "layers.0", {"hidden": d}), ff("layers.0"),
+                  PartSpec("rmsnorm", "layers.0.n1", dict(norm)), PartSpec("rmsnorm", "layers.0.n2", dict(norm))),
+        BlockSpec("pre_norm", "layers.1", PartSpec("paged_attention", "layers.1.attn", {
+            "hidden": d, "n_heads": 2, "n_kv_heads": 1, "head_dim": 16, "window": None, "position": rotary}),
+            ff("layers.1"), PartSpec("rmsnorm", "layers.1.n1", dict(norm)), PartSpec("rmsnorm", "layers.1.n2", dict(norm))),
+    ]
+    # layer 0, layer 1, layer 0 again with a state of its own, layer 1 again reading the keys it wrote before
+    schedule = [LayerCall(0, 0), LayerCall(1, 1), LayerCall(0, 2), LayerCall(1, 1, writes_cache=False)]
+    return ModelSpec(hidden_size=d, vocab_size=cfg.vocab, max_position=64,
+                     embedding=PartSpec("token_embedding", "emb", {"vocab": cfg.vocab, "width": d}),
+                     blocks=blocks, schedule=schedule, final_norm=PartSpec("rmsnorm", "final", dict(norm)),
+                     head=PartSpec("linear_head", "head", {"vocab": cfg.vocab, "width": d, "tied_to": "emb.weight"}))
+
+
+def plain_toy(w, ids, d):
+    """The toy model on whole sequences, in float64, without any cache."""
+    n = len(ids)
+    x = plain.embed(w["emb.weight"], ids)
+
+    def layer0(x):
+        xn = plain.rmsnorm(x, w["layers.0.n1.weight"], 1e-5)
+        mean = np.cumsum(xn, 0) / np.arange(1, n + 1)[:, None]
+        x = x + mean @ plain.f64(w["layers.0.mix.weight"]).T
+        xn = plain.rmsnorm(x, w["layers.0.n2.weight"], 1e-5)
+        return x + plain.swiglu(xn, w["layers.0.mlp.gate_proj.weight"], w["layers.0.mlp.up_proj.weight"],
+                                w["layers.0.mlp.down_proj.weight"])
+
+    def layer1(x, kv=None):
+        xn = plain.rmsnorm(x, w["layers.1.n1.weight"], 1e-5)
+        p = "layers.1.attn."
+        q = plain.rope(xn @ plain.f64(w[p + "q_proj.weight"]).T, np.arange(n), 2, 16, 100.0)
+        if kv is None:
+            k = plain.rope(xn @ plain.f64(w[p + "k_proj.weight"]).T, np.arange(n), 1, 16, 100.0)
+            kv = (k, xn @ plain.f64(w[p + "v_proj.weight"]).T)
+        x = x + plain.attention(q, kv[0], kv[1], 2, 1, 16) @ plain.f64(w[p + "o_proj.weight"]).T
+        xn = plain.rmsnorm(x, w["layers.1.n2.weight"], 1e-5)
+        return x + plain.swiglu(xn, w["layers.1.mlp.gate_proj.weight"], w["layers.1.mlp.up_proj.weight"],
+                                w["layers.1.mlp.down_proj.weight"]), kv
+
+    x = layer0(x)
+    x, kv = layer1(x)
+    x = layer0(x)
+    x, _ = layer1(x, kv)
+    return plain.rmsnorm(x, w["final.weight"], 1e-5) @ plain.f64(w["emb.weight"]).T
+
+
+def test_toy_architecture_with_a_stateful_mixer(tmp_path):
+    """Registered, built, loaded and stepped through the unchanged framework: parts
+    registry, architecture registry, loader, cache manager (state slots beside
+    pages), step function with portions and two live requests."""
+    import json
+    from kllm_b200.config import ModelConfig, register_architecture
+    from kllm_b200.engine import Engine, Options, StepEntry
+    from kllm_b200.parts.spec import register_part
+    from kllm_b200.weights import save_tensors
+
+    @dataclass(frozen=True)
+    class ToyConfig(ModelConfig):
+        hidden: int = 32
+        vocab: int = 40
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(architecture=d["architectures"][0], hidden=d["hidden"], vocab=d["vocab"])
+
+    register_part("mixer", "toy_running_mean", RunningMeanMixer)
+    register_architecture("ToyRunningMeanLM", ToyConfig, toy_spec)
+
+    d = 32
+    rng = np.random.default_rng(4)
+    mat = lambda r, c: (rng.standard_normal((r, c)) * 0.25).astype(np.float32)
+    w = {"emb.weight": mat(40, d), "final.weight": np.ones(d, np.float32)}
+    for l in (0, 1):
+        w.update({f"layers.{l}.n1.weight": (1 + 0.1 * rng.standard_normal(d)).astype(np.float32),
+                  f"layers.{l}.n2.weight": np.ones(d, np.float32),
+                  f"layers.{l}.mlp.gate_proj.weight": mat(2 * d, d), f"layers.{l}.mlp.up_proj.weight": mat(2 * d, d),
+                  f"layers.{l}.mlp.down_proj.weight": mat(d, 2 * d)})
+    w["layers.0.mix.weight"] = mat(d, d)
+    w.update({"layers.1.attn.q_proj.weight": mat(32, d) * 4, "layers.1.attn.k_proj.weight": mat(16, d) * 4,
+              "layers.1.attn.v_proj.weight": mat(16, d), "layers.1.attn.o_proj.weight": mat(d, 32)})
+    model_dir = tmp_path / "toy"
+    model_dir.mkdir()
+    (model_dir / "config.json").write_text(json.dumps({"architectures": ["ToyRunningMeanLM"], "hidden": d, "vocab": 40}))
+    save_tensors(str(model_dir / "model.safetensors"), {k: torch.from_numpy(v) for k, v in w.items()})
+
+    eng = Engine(str(model_dir), Options(dtype="float32", max_seq=64, block_size=4, num_blocks=12, max_batch=2))
+    assert eng.model.n_cache_slots == 3 and len(eng.cache.groups) == 1 and sorted(eng.cache.state) == [0, 2]
+    a_ids = rng.integers(0, 40, 19).tolist()
+    b_ids = rng.integers(0, 40, 11).tolist()
+    a, b = eng.cache.open(), eng.cache.open()
+    got_a, got_b = [], []
+    # a: 7 | 1 | 9 | 2 ; b joins later: 4 | 6 | 1
+    l1 = eng.step([StepEntry(a, a_ids[:7], range(7))]); got_a.append(l1)
+    l2 = eng.step([StepEntry(a, a_ids[7:8], [0]), StepEntry(b, b_ids[:4], range(4))]); got_a.append(l2[:1]); got_b.append(l2[1:])
+    l3 = eng.step([StepEntry(b, b_ids[4:10], range(6)), StepEntry(a, a_ids[8:17], range(9))]); got_b.append(l3[:6]); got_a.append(l3[6:])
+    l4 = eng.step([StepEntry(a, a_ids[17:], range(2)), StepEntry(b, b_ids[10:], [0])]); got_a.append(l4[:2]); got_b.append(l4[2:])
+    close(torch.cat(got_a), plain_toy(w, a_ids, d), "float32", "request a")
+    close(torch.cat(got_b), plain_toy(w, b_ids, d), "float32", "request b")
+    # a new request in a's slot starts from zero state
+    eng.cache.close(a)
+    c = eng.cache.open()
+    assert c.state_slot == a.state_slot
+    close(eng.step([StepEntry(c, b_ids, range(11))]), plain_toy(w, b_ids, d), "float32", "reused state slot")
+    eng.close()
