@@ -1,0 +1,262 @@
+#!/usr/bin/env python3
+"""Throughput of the engine on one GPU: decoded tokens a second.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W]
+
+Default run: the layer sizes of TinyLlama-1.1B (22 layers, hidden 2048, 32 heads
+over 4 kv heads of 64, feed-forward 5632, vocabulary 32000) with random bfloat16
+weights, 8 requests decoding at a context of 2048 tokens.  A "step" is one decode
+step of the whole batch.  One JSON line is printed:
+
+  value      decoded tokens a second, K steps between two CUDA events on the
+             launching stream (device time, after W warm-up steps)
+  e2e        the same through the public Python API (Scheduler.step): every step
+             copies its inputs from pinned host memory and reads its tokens back
+  prefill    one prompt of 2048 tokens in one step, with the fraction of the
+             bfloat16 tensor peak that its flops reach
+  roofline   the decode step against HBM bandwidth: every weight once plus the
+             cache of the live requests, over the step's time
+  points     decode at batch 1 and at batch 64
+
+Weights are random and token ids synthetic (there is neither a checkpoint nor a
+dataset here).  Every decode step reads about 2.4 GB, far more than the 126 MB of
+L2, so nothing is flushed between steps.  ``--impl reference`` would run the
+reference project itself; it is a Go program with a CUDA backend and cannot be
+installed here, so that arm says so and exits 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+TINYLLAMA = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 22, "hidden_size": 2048, "num_attention_heads": 32, "num_key_value_heads": 4,
+    "head_dim": 64, "intermediate_size": 5632, "vocab_size": 32000, "rope_theta": 10000.0,
+    "rms_norm_eps": 1e-5, "max_position_embeddings": 2048, "tie_word_embeddings": False,
+}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            d = json.load(f)
+        out = {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+        if "bf16_tflops_sustained" in d:
+            out["bf16_tflops_sustained"] = float(d["bf16_tflops_sustained"])
+        return out
+    except Exception:
+        return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.rows = []
+        self.proc = None
+        exe = shutil.which("nvidia-smi")
+        if exe:
+            self.proc = subprocess.Popen([exe, f"--id={device}", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self, t0: float, t1: float):
+        rows = [r for t, r in self.rows if t0 <= t <= t1 and len(r) >= 6] or [r for _, r in self.rows if len(r) >= 6]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        mhz = sorted(int(float(r[0])) for r in rows)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in rows)]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": int(float(rows[0][1])), "reasons": reasons,
+                "samples": len(rows)}
+
+
+def model_bytes_and_flops(cfg, layers):
+    d, f, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    qd = cfg["num_attention_heads"] * cfg["head_dim"]
+    kd = cfg["num_key_value_heads"] * cfg["head_dim"]
+    per_layer = d * (qd + 2 * kd) + qd * d + 3 * d * f           # matrix elements of one layer
+    return per_layer, per_layer * layers + v * d                   # head counted once, embedding rows negligible
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=2048)
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0: all)")
+    ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and the prefill")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a Go program with a CUDA backend; pip reports 'not installable: neither "
+                          "setup.py nor pyproject.toml' and no Go toolchain exists here"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(3, args.warmup)
+
+    import torch
+    from kllm_b200 import kernels
+    from kllm_b200.engine import Engine, Options, Scheduler
+    from kllm_b200.weights import write_random_model
+
+    cfg = dict(TINYLLAMA)
+    layers_full = cfg["num_hidden_layers"]
+    layers = args.layers or layers_full
+    cfg["num_hidden_layers"] = layers
+    B, ctx, K, W = args.batch, args.context, args.steps, args.warmup
+    pk = peaks()
+    tmp = tempfile.mkdtemp(prefix="kllm_b200_bench_")
+    try:
+        t_w = time.time()
+        write_random_model(tmp, cfg, seed=4, dtype=torch.bfloat16)
+        print(f"[bench] random weights written in {time.time() - t_w:.1f} s", file=sys.stderr, flush=True)
+        page = 64
+        max_b = max(B, 64 if not args.no_points else B)
+        pages = max_b * (-(-ctx // page)) + 8
+        eng = Engine(tmp, Options(dtype="bfloat16", max_seq=ctx, block_size=page, num_blocks=pages,
+                                  max_batch=max_b, max_step_tokens=max(2048, max_b)))
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+
+    g = torch.Generator().manual_seed(1)
+
+    def prompts(n, length):
+        return torch.randint(0, cfg["vocab_size"], (n, length), generator=g).tolist()
+
+    def decode_run(batch, steps, warm, sample_clocks=False):
+        """Prefill ``batch`` requests so that the last timed step lands on context
+        ``ctx``; returns (device ms per step, e2e ms per step, launches, h2d, d2h, clocks)."""
+        total = 2 * (steps + warm)
+        plen = ctx - total - 1
+        sched = Scheduler(eng)
+        for p in prompts(batch, plen):
+            sched.submit(p, total + 1)
+        while any(r.fed < len(r.prompt) for r in list(sched.running) + list(sched.waiting)):
+            sched.step()
+        for _ in range(warm):
+            sched.step()
+        torch.cuda.synchronize()
+        clocks = ClockSampler(eng.options.device) if sample_clocks else None
+        # device-timed
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = kernels.launches
+        t0 = time.time()
+        ev0.record()
+        for _ in range(steps):
+            sched.step()
+        ev1.record()
+        torch.cuda.synchronize()
+        t1 = time.time()
+        dev_ms = ev0.elapsed_time(ev1) / steps
+        launches = (kernels.launches - l0) // steps
+        # end to end: wall clock around the public API, synchronised on both sides
+        for _ in range(warm):
+            sched.step()
+        torch.cuda.synchronize()
+        w0 = time.perf_counter()
+        for _ in range(steps):
+            sched.step()
+        torch.cuda.synchronize()
+        e2e_ms = (time.perf_counter() - w0) * 1e3 / steps
+        csum = None
+        if clocks:
+            time.sleep(0.15)
+            clocks.stop()
+            csum = clocks.summary(t0, t1)
+        h2d = eng.runner.last_h2d_bytes
+        sched.stop()
+        return dev_ms, e2e_ms, launches, h2d, batch * 4, csum
+
+    with torch.no_grad():
+        dev_ms, e2e_ms, launches, h2d, d2h, clocks = decode_run(B, K, W, sample_clocks=True)
+        per_layer, weight_elems = model_bytes_and_flops(cfg, layers)
+        kv_bytes = B * ctx * eng.cache.bytes_per_token_full()
+        step_bytes = 2 * weight_elems + kv_bytes
+        achieved = step_bytes / (dev_ms * 1e-3) / 1e9
+        out = {
+            "metric": "decode tok/s at batch 8 (TinyLlama 1.1B shape, context 2048)",
+            "value": round(B / (dev_ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+            "ms_per_step": round(dev_ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic token ids, random weights (seed 4)",
+            "config": {"model": "TinyLlama-1.1B shape", "global_batch": B, "seq_len": ctx, "parallelism": "single GPU",
+                       "layers": layers, "layers_of_config": layers_full, "hidden": cfg["hidden_size"],
+                       "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                       "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
+                       "vocab": cfg["vocab_size"], "page_size": 64, "l2": "step reads 2.4 GB > 126 MB L2, no flush",
+                       "peaks": pk["source"]},
+            "clocks": clocks,
+            "e2e": {"value": round(B / (e2e_ms * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": launches * K,
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": step_bytes},
+        }
+        if not args.no_points:
+            T = 2048
+            sched = Scheduler(eng)
+            from kllm_b200.engine import StepEntry
+            ids = prompts(1, T)[0]
+            times = []
+            for _ in range(4):
+                req = eng.cache.open()
+                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                ev0.record()
+                eng.runner.run([StepEntry(req, ids, [T - 1])])
+                ev1.record()
+                torch.cuda.synchronize()
+                times.append(ev0.elapsed_time(ev1))
+                eng.cache.close(req)
+            ms = min(times[1:])
+            qd = cfg["num_attention_heads"] * cfg["head_dim"]
+            flops = 2 * T * (per_layer * layers) + 2 * cfg["vocab_size"] * cfg["hidden_size"] \
+                + 2 * T * T * qd * layers          # causal attention: QK^T and PV over half the square
+            out["prefill"] = {"value": round(T / (ms * 1e-3), 1), "tokens": T, "ms": round(ms, 3),
+                              "frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+            pts = {}
+            for b in (1, 64):
+                dms, _, _, _, _, _ = decode_run(b, max(8, K // 2), 3)
+                pts[f"decode_b{b}"] = round(b / (dms * 1e-3), 1)
+            out["points"] = pts
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

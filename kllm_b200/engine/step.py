@@ -48,6 +48,7 @@ class StepRunner:
         self.device = model.device
         self.steps = 0
         self.tokens_run = 0
+        self.last_h2d_bytes = 0     # bytes of the last step's host-to-device copy
 
     # ---- validation --------------------------------------------------------
     def validate(self, entries: Sequence[StepEntry]) -> None:
@@ -114,6 +115,7 @@ class StepRunner:
                 tab[si, :len(t)] = t
             h[offs[8 + gi]:offs[9 + gi]] = tab.reshape(-1)
         dev = host.to(self.device, non_blocking=True)
+        self.last_h2d_bytes = host.numel() * 4
 
         def part(i):
             return dev[int(offs[i]):int(offs[i + 1])]
