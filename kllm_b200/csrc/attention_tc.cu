@@ -1,0 +1,523 @@
+// Causal grouped-query attention over the paged cache on tensor cores, bfloat16
+// operands with float32 accumulation, one library per head size (compiled with
+// -DKLLM_HD=<head size>, a multiple of 16 up to 128).
+//
+// Two kernels share the tile loader and the softmax recurrence:
+//
+//  * decode: one query token per CTA and kv head.  The `group` = heads / kv heads
+//    query heads that share a kv head form the rows of one 16-row MMA tile (so
+//    group <= 16), every key and value is read once for all of them.  The keys of
+//    the token are cut into `num_splits` ranges, one CTA each; inside a CTA the
+//    four warps take interleaved 16-key slices of every 64-key tile and keep a
+//    running (max, sum, output) of their own, merged once at the end in a fixed
+//    order.  With more than one split the CTA writes an unnormalised partial
+//    result and `attn_combine_kernel` merges the splits, again in a fixed order.
+//
+//  * prefill: a CTA takes up to 64 rows = (tokens of one request's portion) x
+//    (heads of one group), each warp 16 of them, and walks the keys from the first
+//    visible one to the last token's own position in 64-key tiles that all warps
+//    share.  Portions of prompts and single tokens may be mixed in one launch; a
+//    CTA finds its request from the prefix sums of the portions' lengths.
+//
+// Keys and values reach shared memory through cp.async (16-byte pieces, three
+// stages), rows padded by 16 bytes so that ldmatrix is free of bank conflicts for
+// every head size.  Scores, the running maximum, the sum and the output are
+// float32; probabilities are rounded to bfloat16 for the second product only.
+// Slots of a page beyond a request's length are never read: rows past the last
+// key are zero-filled instead of loaded.  The math is the reference's
+// (backend/model.cu:343-408): keys [max(0, p + 1 - window), p], scale after the
+// dot product, one division by the sum at the end.
+#include "common.cuh"
+
+#ifndef KLLM_HD
+#error "compile with -DKLLM_HD=<head size>"
+#endif
+
+KLLM_EXPORT_LAST_ERROR(attention_tc)
+
+namespace {
+
+constexpr int HD = KLLM_HD;
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 128, "head size must be a multiple of 16 up to 128");
+constexpr int KSTEPS = HD / 16;          // MMA k-steps over the head dims (scores)
+constexpr int DTILES = HD / 8;           // 8-wide output tiles over the head dims
+constexpr int CHUNKS = HD / 8;           // 16-byte pieces of a key row
+constexpr int TILE = 64;                 // keys per shared-memory tile
+constexpr int ROW = HD + 8;              // padded row, in elements (16 bytes of padding)
+constexpr int STAGES = 3;
+constexpr int THREADS = 128;
+constexpr int STAGE_ELEMS = 2 * TILE * ROW;                       // K tile then V tile
+constexpr int SMEM_BYTES = STAGES * STAGE_ELEMS * 2;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    const int bytes = valid ? 16 : 0;    // 0: the 16 bytes are filled with zeros, nothing is read
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Keys key0 .. key0+63 of kv head g into one stage (K tile, then V tile).  Rows at
+// or past `hi` are zero-filled.
+__device__ __forceinline__ void load_tile(bf16* stage, const bf16* __restrict__ kcache,
+                                          const bf16* __restrict__ vcache, const int* __restrict__ table,
+                                          int key0, int hi, int g, int n_kv, int page_size) {
+    bf16* sk = stage;
+    bf16* sv = stage + TILE * ROW;
+    for (int c = threadIdx.x; c < TILE * CHUNKS; c += THREADS) {
+        const int row = c / CHUNKS, ch = c - row * CHUNKS;
+        const int key = key0 + row;
+        const bool valid = key < hi;
+        int64_t off = 0;
+        if (valid) {
+            const int lp = key / page_size;
+            const int page = table[lp];
+            off = (((int64_t)page * n_kv + g) * page_size + (key - lp * page_size)) * HD + ch * 8;
+        }
+        cp_async16(sk + row * ROW + ch * 8, kcache + off, valid);
+        cp_async16(sv + row * ROW + ch * 8, vcache + off, valid);
+    }
+}
+
+// Scores of 16 rows against keys [16*slice, 16*slice+16) of a K tile.
+__device__ __forceinline__ void scores16(float (&s)[2][4], const uint32_t (&qa)[KSTEPS][4], const bf16* sk,
+                                         int slice, int lane) {
+#pragma unroll
+    for (int i = 0; i < 2; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) s[i][j] = 0.f;
+    const int mi = lane >> 3;
+    const bf16* base = sk + (16 * slice + (mi >> 1) * 8 + (lane & 7)) * ROW + (mi & 1) * 8;
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ks++) {
+        uint32_t b[4];
+        ldmatrix_x4(b, base + ks * 16);
+        mma_bf16(s[0], qa[ks], b[0], b[1]);
+        mma_bf16(s[1], qa[ks], b[2], b[3]);
+    }
+}
+
+// o += P (16 rows x 16 keys, bfloat16 fragments) times the values of keys
+// [16*slice, 16*slice+16) of a V tile.
+__device__ __forceinline__ void accumulate16(float (&o)[DTILES][4], const uint32_t (&pa)[4], const bf16* sv,
+                                             int slice, int lane) {
+    const int mi = lane >> 3;
+    const bf16* base = sv + (16 * slice + (mi & 1) * 8 + (lane & 7)) * ROW + (mi >> 1) * 8;
+#pragma unroll
+    for (int dp = 0; dp < HD / 16; dp++) {
+        uint32_t v[4];
+        ldmatrix_x4_trans(v, base + dp * 16);
+        mma_bf16(o[2 * dp], pa, v[0], v[1]);
+        mma_bf16(o[2 * dp + 1], pa, v[2], v[3]);
+    }
+}
+
+// ---- decode -------------------------------------------------------------------
+
+__global__ void __launch_bounds__(THREADS)
+attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+                   const bf16* __restrict__ q, int64_t q_stride, const bf16* __restrict__ kcache,
+                   const bf16* __restrict__ vcache, const int* __restrict__ positions,
+                   const int* __restrict__ token_req, const int* __restrict__ block_table, int max_blocks,
+                   int n_heads, int n_kv, int page_size, int window, float scale_log2e, int num_splits) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* smem = reinterpret_cast<bf16*>(smem_raw);
+    const int split = blockIdx.x, g = blockIdx.y, t = blockIdx.z;
+    const int gs = n_heads / n_kv;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tq = lane & 3;
+    const int len = positions[t] + 1;
+    const int start = (window > 0 && len > window) ? len - window : 0;
+    const int total = len - start;
+    const int chunk = (((total + num_splits - 1) / num_splits) + TILE - 1) / TILE * TILE;
+    const int lo = start + split * chunk;
+    const int hi = min(len, lo + chunk);
+    const int* table = block_table + (int64_t)token_req[t] * max_blocks;
+    const int ntiles = lo < hi ? (hi - lo + TILE - 1) / TILE : 0;
+
+    uint32_t qa[KSTEPS][4];
+    {
+        const bf16* qb = q + (int64_t)t * q_stride + (int64_t)g * gs * HD;
+        const bool v0 = gid < gs, v1 = gid + 8 < gs;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ks++) {
+            const int c = ks * 16 + 2 * tq;
+            qa[ks][0] = v0 ? *reinterpret_cast<const uint32_t*>(qb + gid * HD + c) : 0u;
+            qa[ks][1] = v1 ? *reinterpret_cast<const uint32_t*>(qb + (gid + 8) * HD + c) : 0u;
+            qa[ks][2] = v0 ? *reinterpret_cast<const uint32_t*>(qb + gid * HD + c + 8) : 0u;
+            qa[ks][3] = v1 ? *reinterpret_cast<const uint32_t*>(qb + (gid + 8) * HD + c + 8) : 0u;
+        }
+    }
+    float o[DTILES][4];
+#pragma unroll
+    for (int i = 0; i < DTILES; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) o[i][j] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; s++) {
+        if (s < ntiles) load_tile(smem + s * STAGE_ELEMS, kcache, vcache, table, lo + s * TILE, hi, g, n_kv, page_size);
+        cp_async_commit();
+    }
+    for (int i = 0; i < ntiles; i++) {
+        cp_async_wait<STAGES - 2>();
+        __syncthreads();
+        const int nxt = i + STAGES - 1;
+        if (nxt < ntiles)
+            load_tile(smem + (nxt % STAGES) * STAGE_ELEMS, kcache, vcache, table, lo + nxt * TILE, hi, g, n_kv, page_size);
+        cp_async_commit();
+        const bf16* sk = smem + (i % STAGES) * STAGE_ELEMS;
+        const bf16* sv = sk + TILE * ROW;
+        const int key_base = lo + i * TILE + 16 * warp;
+        if (key_base < hi) {
+            float s[2][4];
+            scores16(s, qa, sk, warp, lane);
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    if (key_base + nt * 8 + 2 * tq + (j & 1) >= hi) s[nt][j] = -INFINITY;
+            float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+            float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);   // finite: key_base itself is visible
+            const float c0 = exp2f((m0 - n0) * scale_log2e), c1 = exp2f((m1 - n1) * scale_log2e);
+            m0 = n0; m1 = n1;
+            float p[2][4];
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++) {
+                p[nt][0] = exp2f((s[nt][0] - n0) * scale_log2e);
+                p[nt][1] = exp2f((s[nt][1] - n0) * scale_log2e);
+                p[nt][2] = exp2f((s[nt][2] - n1) * scale_log2e);
+                p[nt][3] = exp2f((s[nt][3] - n1) * scale_log2e);
+            }
+            l0 = l0 * c0 + (p[0][0] + p[0][1] + p[1][0] + p[1][1]);
+            l1 = l1 * c1 + (p[0][2] + p[0][3] + p[1][2] + p[1][3]);
+#pragma unroll
+            for (int i2 = 0; i2 < DTILES; i2++) { o[i2][0] *= c0; o[i2][1] *= c0; o[i2][2] *= c1; o[i2][3] *= c1; }
+            uint32_t pa[4] = {pack_bf16(p[0][0], p[0][1]), pack_bf16(p[0][2], p[0][3]),
+                              pack_bf16(p[1][0], p[1][1]), pack_bf16(p[1][2], p[1][3])};
+            accumulate16(o, pa, sv, warp, lane);
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+    // merge the four warps, in warp order
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    float* sm_m = reinterpret_cast<float*>(smem_raw);       // [4][16]
+    float* sm_l = sm_m + 64;                                // [4][16]
+    float* sm_o = sm_l + 64;                                // [4][16][HD]
+    if (tq == 0) {
+        sm_m[warp * 16 + gid] = m0; sm_m[warp * 16 + gid + 8] = m1;
+        sm_l[warp * 16 + gid] = l0; sm_l[warp * 16 + gid + 8] = l1;
+    }
+#pragma unroll
+    for (int dt = 0; dt < DTILES; dt++) {
+        float* r0 = sm_o + (warp * 16 + gid) * HD + dt * 8 + 2 * tq;
+        float* r1 = sm_o + (warp * 16 + gid + 8) * HD + dt * 8 + 2 * tq;
+        r0[0] = o[dt][0]; r0[1] = o[dt][1]; r1[0] = o[dt][2]; r1[1] = o[dt][3];
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < gs * HD; e += THREADS) {
+        const int r = e / HD, d = e - r * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; w++) M = fmaxf(M, sm_m[w * 16 + r]);
+        float L = 0.f, O = 0.f;
+        if (M > -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                const float f = exp2f((sm_m[w * 16 + r] - M) * scale_log2e);   // 0 for a warp without keys
+                L += sm_l[w * 16 + r] * f;
+                O += sm_o[(w * 16 + r) * HD + d] * f;
+            }
+        }
+        const int h = g * gs + r;
+        if (num_splits == 1) {
+            out[(int64_t)t * n_heads * HD + (int64_t)h * HD + d] = __float2bfloat16_rn(O / L);
+        } else {
+            const int64_t slot = ((int64_t)t * n_heads + h) * num_splits + split;
+            part_o[slot * HD + d] = O;
+            if (d == 0) { part_ml[slot * 2] = M * scale_log2e; part_ml[slot * 2 + 1] = L; }
+        }
+    }
+}
+
+// Merge the splits of the decode kernel, in split order: one block per (token, head).
+__global__ void attn_combine_kernel(bf16* __restrict__ out, const float* __restrict__ part_o,
+                                    const float* __restrict__ part_ml, int num_splits) {
+    const int64_t th = blockIdx.x;
+    const float* ml = part_ml + th * num_splits * 2;
+    float M = -INFINITY;
+    for (int j = 0; j < num_splits; j++) M = fmaxf(M, ml[2 * j]);
+    float L = 0.f;
+    for (int j = 0; j < num_splits; j++) L += ml[2 * j + 1] * exp2f(ml[2 * j] - M);
+    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+        float O = 0.f;
+        for (int j = 0; j < num_splits; j++)
+            O += part_o[(th * num_splits + j) * HD + d] * exp2f(ml[2 * j] - M);
+        out[th * HD + d] = __float2bfloat16_rn(O / L);
+    }
+}
+
+// ---- prefill ------------------------------------------------------------------
+
+__global__ void __launch_bounds__(THREADS)
+attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t q_stride,
+                    const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
+                    const int* __restrict__ q_start, const int* __restrict__ start_pos,
+                    const int* __restrict__ block_table, int max_blocks, int n_requests, int n_heads,
+                    int n_kv, int page_size, int window, float scale_log2e, int tokens_per_tile) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* smem = reinterpret_cast<bf16*>(smem_raw);
+    __shared__ int s_req, s_tok0;
+    const int g = blockIdx.y;
+    const int gs = n_heads / n_kv;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tq = lane & 3;
+    if (threadIdx.x == 0) {
+        int tile = blockIdx.x, req = -1, tok0 = 0;
+        for (int s = 0; s < n_requests; s++) {
+            const int n = q_start[s + 1] - q_start[s];
+            const int nt = (n + tokens_per_tile - 1) / tokens_per_tile;
+            if (tile < nt) { req = s; tok0 = q_start[s] + tile * tokens_per_tile; break; }
+            tile -= nt;
+        }
+        s_req = req; s_tok0 = tok0;
+    }
+    __syncthreads();
+    const int req = s_req;
+    if (req < 0) return;                       // the grid is an upper bound on the tiles
+    const int tok0 = s_tok0;
+    const int q_end = q_start[req + 1];
+    const int n_tok = min(tokens_per_tile, q_end - tok0);
+    const int pos0 = start_pos[req] + (tok0 - q_start[req]);      // position of the tile's first token
+    const int lo = (window > 0 && pos0 + 1 > window) ? pos0 + 1 - window : 0;
+    const int hi = pos0 + n_tok;                                   // last token's position + 1
+    const int* table = block_table + (int64_t)req * max_blocks;
+    const int ntiles = (hi - lo + TILE - 1) / TILE;
+
+    // this thread's two rows: (token, head of the group)
+    const int r0 = 16 * warp + gid, r1 = r0 + 8;
+    const int t0 = r0 / gs, h0 = r0 - t0 * gs, t1 = r1 / gs, h1 = r1 - t1 * gs;
+    const bool v0 = t0 < n_tok, v1 = t1 < n_tok;
+    const int p0 = v0 ? pos0 + t0 : -1, p1 = v1 ? pos0 + t1 : -1;   // -1: no key is visible
+    const int w0 = (window > 0) ? p0 + 1 - window : 0, w1 = (window > 0) ? p1 + 1 - window : 0;
+    // key range that this warp's rows can see at all
+    const int wt_first = (16 * warp) / gs, wt_last = min(n_tok - 1, (16 * warp + 15) / gs);
+    const bool warp_active = wt_first < n_tok;
+    const int warp_hi = pos0 + wt_last + 1;
+    const int warp_full_below = pos0 + wt_first;                    // keys <= this are causal for every row
+
+    uint32_t qa[KSTEPS][4];
+    {
+        const bf16* q0 = q + (int64_t)(tok0 + t0) * q_stride + (int64_t)(g * gs + h0) * HD;
+        const bf16* q1 = q + (int64_t)(tok0 + t1) * q_stride + (int64_t)(g * gs + h1) * HD;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ks++) {
+            const int c = ks * 16 + 2 * tq;
+            qa[ks][0] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + c) : 0u;
+            qa[ks][1] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + c) : 0u;
+            qa[ks][2] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + c + 8) : 0u;
+            qa[ks][3] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + c + 8) : 0u;
+        }
+    }
+    float o[DTILES][4];
+#pragma unroll
+    for (int i = 0; i < DTILES; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) o[i][j] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; s++) {
+        if (s < ntiles) load_tile(smem + s * STAGE_ELEMS, kcache, vcache, table, lo + s * TILE, hi, g, n_kv, page_size);
+        cp_async_commit();
+    }
+    for (int i = 0; i < ntiles; i++) {
+        cp_async_wait<STAGES - 2>();
+        __syncthreads();
+        const int nxt = i + STAGES - 1;
+        if (nxt < ntiles)
+            load_tile(smem + (nxt % STAGES) * STAGE_ELEMS, kcache, vcache, table, lo + nxt * TILE, hi, g, n_kv, page_size);
+        cp_async_commit();
+        const bf16* sk = smem + (i % STAGES) * STAGE_ELEMS;
+        const bf16* sv = sk + TILE * ROW;
+        const int key0 = lo + i * TILE;
+        if (!warp_active || key0 >= warp_hi) continue;             // nothing of this tile is visible to the warp
+        const bool need_mask = window > 0 || key0 + TILE - 1 > warp_full_below;
+        float s[8][4];
+#pragma unroll
+        for (int sl = 0; sl < 4; sl++) {
+            float s2[2][4];
+            scores16(s2, qa, sk, sl, lane);
+#pragma unroll
+            for (int j = 0; j < 4; j++) { s[2 * sl][j] = s2[0][j]; s[2 * sl + 1][j] = s2[1][j]; }
+        }
+        if (need_mask) {
+#pragma unroll
+            for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    const int key = key0 + nt * 8 + 2 * tq + j;
+                    if (key > p0 || key < w0) s[nt][j] = -INFINITY;
+                    if (key > p1 || key < w1) s[nt][2 + j] = -INFINITY;
+                }
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++) {
+            mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
+            mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+        // a row that has seen no key yet keeps max -inf: subtract 0 instead, all its p are exp2(-inf) = 0
+        const float b0 = (n0 == -INFINITY) ? 0.f : n0, b1 = (n1 == -INFINITY) ? 0.f : n1;
+        const float c0 = exp2f((m0 - b0) * scale_log2e), c1 = exp2f((m1 - b1) * scale_log2e);
+        m0 = n0; m1 = n1;
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++) {
+            s[nt][0] = exp2f((s[nt][0] - b0) * scale_log2e);
+            s[nt][1] = exp2f((s[nt][1] - b0) * scale_log2e);
+            s[nt][2] = exp2f((s[nt][2] - b1) * scale_log2e);
+            s[nt][3] = exp2f((s[nt][3] - b1) * scale_log2e);
+            sum0 += s[nt][0] + s[nt][1];
+            sum1 += s[nt][2] + s[nt][3];
+        }
+        l0 = l0 * c0 + sum0;
+        l1 = l1 * c1 + sum1;
+#pragma unroll
+        for (int i2 = 0; i2 < DTILES; i2++) { o[i2][0] *= c0; o[i2][1] *= c0; o[i2][2] *= c1; o[i2][3] *= c1; }
+#pragma unroll
+        for (int sl = 0; sl < 4; sl++) {
+            uint32_t pa[4] = {pack_bf16(s[2 * sl][0], s[2 * sl][1]), pack_bf16(s[2 * sl][2], s[2 * sl][3]),
+                              pack_bf16(s[2 * sl + 1][0], s[2 * sl + 1][1]), pack_bf16(s[2 * sl + 1][2], s[2 * sl + 1][3])};
+            accumulate16(o, pa, sv, sl, lane);
+        }
+    }
+    cp_async_wait<0>();
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float i0 = 1.f / l0, i1 = 1.f / l1;
+    if (v0) {
+        bf16* orow = out + (int64_t)(tok0 + t0) * n_heads * HD + (int64_t)(g * gs + h0) * HD;
+#pragma unroll
+        for (int dt = 0; dt < DTILES; dt++)
+            *reinterpret_cast<uint32_t*>(orow + dt * 8 + 2 * tq) = pack_bf16(o[dt][0] * i0, o[dt][1] * i0);
+    }
+    if (v1) {
+        bf16* orow = out + (int64_t)(tok0 + t1) * n_heads * HD + (int64_t)(g * gs + h1) * HD;
+#pragma unroll
+        for (int dt = 0; dt < DTILES; dt++)
+            *reinterpret_cast<uint32_t*>(orow + dt * 8 + 2 * tq) = pack_bf16(o[dt][2] * i1, o[dt][3] * i1);
+    }
+}
+
+bool g_attr_set = false;
+
+int set_attributes() {
+    if (g_attr_set) return 0;
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) {
+        snprintf(g_kllm_err, sizeof(g_kllm_err), "attention: cannot get %d bytes of shared memory: %s", SMEM_BYTES,
+                 cudaGetErrorString(e));
+        return (int)e;
+    }
+    g_attr_set = true;
+    return 0;
+}
+
+int check_common(int n_heads, int n_kv, int hd, int page_size, const void* q, int64_t q_stride) {
+    if (hd != HD) KLLM_FAIL("attention: this library was built for head size %d, not %d", HD, hd);
+    if (n_kv <= 0 || n_heads % n_kv) KLLM_FAIL("attention: %d heads over %d kv heads", n_heads, n_kv);
+    if (page_size <= 0) KLLM_FAIL("attention: page size %d", page_size);
+    if (((uintptr_t)q & 3) || (q_stride & 1)) KLLM_FAIL("attention: q must be 4-byte aligned with an even row stride");
+    return 0;
+}
+
+}  // namespace
+
+extern "C" int kllm_attention_tc_head_dim() { return HD; }
+
+// Decode form: every token on its own (any batch is valid, one token per request
+// is what it is made for).  part_o [n_tokens, n_heads, num_splits, HD] float32 and
+// part_ml [n_tokens, n_heads, num_splits, 2] float32 are scratch for num_splits > 1.
+extern "C" int kllm_attention_decode(void* out, void* part_o, void* part_ml, const void* q, int64_t q_stride,
+                                     const void* kcache, const void* vcache, const int* positions,
+                                     const int* token_req, const int* block_table, int max_blocks,
+                                     int n_tokens, int n_heads, int n_kv, int hd, int page_size, int window,
+                                     float scale, int num_splits, void* stream) {
+    if (n_tokens <= 0) return 0;
+    int rc = check_common(n_heads, n_kv, hd, page_size, q, q_stride);
+    if (rc) return rc;
+    if (n_heads / n_kv > 16) KLLM_FAIL("attention decode: %d heads per kv head, at most 16", n_heads / n_kv);
+    if (num_splits < 1 || (num_splits > 1 && (!part_o || !part_ml))) KLLM_FAIL("attention decode: bad split arguments");
+    if (n_tokens > 65535 || n_kv > 65535) KLLM_FAIL("attention decode: grid too large");
+    if ((rc = set_attributes())) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    const float sl2e = scale * 1.4426950408889634f;
+    dim3 grid(num_splits, n_kv, n_tokens);
+    attn_decode_kernel<<<grid, THREADS, SMEM_BYTES, s>>>(
+        (bf16*)out, (float*)part_o, (float*)part_ml, (const bf16*)q, q_stride, (const bf16*)kcache,
+        (const bf16*)vcache, positions, token_req, block_table, max_blocks, n_heads, n_kv, page_size, window, sl2e,
+        num_splits);
+    if (num_splits > 1)
+        attn_combine_kernel<<<n_tokens * n_heads, HD < 64 ? 32 : 64, 0, s>>>((bf16*)out, (const float*)part_o,
+                                                                          (const float*)part_ml, num_splits);
+    KLLM_LAUNCH_STATUS();
+}
+
+// Prefill form: requests' portions q_start[s]..q_start[s+1] (prefix sums, [n_requests+1])
+// starting at cache position start_pos[s].
+extern "C" int kllm_attention_prefill(void* out, const void* q, int64_t q_stride, const void* kcache,
+                                      const void* vcache, const int* q_start, const int* start_pos,
+                                      const int* block_table, int max_blocks, int n_tokens, int n_requests,
+                                      int n_heads, int n_kv, int hd, int page_size, int window, float scale,
+                                      void* stream) {
+    if (n_tokens <= 0) return 0;
+    int rc = check_common(n_heads, n_kv, hd, page_size, q, q_stride);
+    if (rc) return rc;
+    const int gs = n_heads / n_kv;
+    if (gs > 64) KLLM_FAIL("attention prefill: %d heads per kv head, at most 64", gs);
+    if ((rc = set_attributes())) return rc;
+    const int tpt = 64 / gs;
+    const int max_tiles = n_tokens / tpt + n_requests;          // >= sum of ceil(n_s / tpt)
+    if (n_kv > 65535) KLLM_FAIL("attention prefill: grid too large");
+    const float sl2e = scale * 1.4426950408889634f;
+    dim3 grid(max_tiles, n_kv);
+    attn_prefill_kernel<<<grid, THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(
+        (bf16*)out, (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache, q_start, start_pos,
+        block_table, max_blocks, n_requests, n_heads, n_kv, page_size, window, sl2e, tpt);
+    KLLM_LAUNCH_STATUS();
+}

@@ -69,12 +69,21 @@ def build_dir() -> str:
     raise KernelBuildError(f"no writable build folder among {cands}")
 
 
-def _digest(name: str) -> str:
+def _define_flags(defines) -> List[str]:
+    return [f"-D{k}={v}" for k, v in sorted((defines or {}).items())]
+
+
+def _variant(name: str, defines) -> str:
+    """File stem of a library: the source name plus its compile-time definitions."""
+    return name + "".join(f"-{k}{v}" for k, v in sorted((defines or {}).items()))
+
+
+def _digest(name: str, defines=None) -> str:
     h = hashlib.sha256()
     for f in [name + ".cu"] + HEADERS:
         with open(os.path.join(CSRC, f), "rb") as fh:
             h.update(fh.read())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(NVCC_FLAGS + _define_flags(defines)).encode())
     return h.hexdigest()[:16]
 
 
@@ -88,21 +97,23 @@ def _find_built(name: str, digest: str):
     return None
 
 
-def compile_library(name: str, verbose: bool = True) -> str:
-    """Compile ``<name>.cu`` if no current build exists; return the .so path."""
+def compile_library(name: str, verbose: bool = True, defines=None) -> str:
+    """Compile ``<name>.cu`` (with ``-D`` definitions, if any) unless a current
+    build exists; return the .so path."""
     src = os.path.join(CSRC, name + ".cu")
     if not os.path.isfile(src):
         raise KernelBuildError(f"kernel source {src} is missing")
-    digest = _digest(name)
-    built = _find_built(name, digest)
+    digest = _digest(name, defines)
+    name_v = _variant(name, defines)
+    built = _find_built(name_v, digest)
     if built:
         return built
     out_dir = build_dir()
-    out = os.path.join(out_dir, f"{name}-{digest}.so")
+    out = os.path.join(out_dir, f"{name_v}-{digest}.so")
     tmp = out + f".tmp{os.getpid()}"
-    cmd = [find_nvcc()] + NVCC_FLAGS + ["-I", CSRC, "-o", tmp, src]
+    cmd = [find_nvcc()] + NVCC_FLAGS + _define_flags(defines) + ["-I", CSRC, "-o", tmp, src]
     if verbose:
-        print(f"[kllm_b200] compiling {name}.cu for sm_100a (first use) ...", file=sys.stderr, flush=True)
+        print(f"[kllm_b200] compiling {name_v} ({name}.cu) for sm_100a (first use) ...", file=sys.stderr, flush=True)
     t0 = time.time()
     proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     done = threading.Event()
@@ -110,7 +121,7 @@ def compile_library(name: str, verbose: bool = True) -> str:
     def _tick():
         while not done.wait(10.0):
             if verbose:
-                print(f"[kllm_b200] ... still compiling {name}.cu ({time.time() - t0:.0f} s)",
+                print(f"[kllm_b200] ... still compiling {name_v} ({time.time() - t0:.0f} s)",
                       file=sys.stderr, flush=True)
 
     ticker = threading.Thread(target=_tick, daemon=True)
@@ -124,10 +135,11 @@ def compile_library(name: str, verbose: bool = True) -> str:
             os.unlink(tmp)
         except OSError:
             pass
-        raise KernelBuildError(f"nvcc failed for {name}.cu (exit {proc.returncode}):\n{log}")
+        raise KernelBuildError(f"nvcc failed for {name_v} (exit {proc.returncode}):\n{log}")
     os.replace(tmp, out)
-    for f in os.listdir(out_dir):  # builds of older sources of the same library
-        if f.startswith(name + "-") and f.endswith(".so") and f != os.path.basename(out):
+    stale = len(name_v) + 1 + 16 + 3          # "<variant>-<16 hex>.so": builds of older sources
+    for f in os.listdir(out_dir):
+        if f.startswith(name_v + "-") and f.endswith(".so") and len(f) == stale and f != os.path.basename(out):
             try:
                 os.unlink(os.path.join(out_dir, f))
             except OSError:
@@ -138,25 +150,36 @@ def compile_library(name: str, verbose: bool = True) -> str:
     return out
 
 
-def load_library(name: str) -> ctypes.CDLL:
-    """The loaded library of ``<name>.cu``, compiled now if needed."""
-    lib = _loaded.get(name)
+def load_library(name: str, defines=None) -> ctypes.CDLL:
+    """The loaded library of ``<name>.cu`` (one per set of definitions), compiled
+    now if needed."""
+    key = _variant(name, defines)
+    lib = _loaded.get(key)
     if lib is not None:
         return lib
     with _lock:
-        lib = _loaded.get(name)
+        lib = _loaded.get(key)
         if lib is None:
-            path = compile_library(name)
+            path = compile_library(name, defines=defines)
             try:
                 lib = ctypes.CDLL(path)
             except OSError as e:
                 raise KernelBuildError(f"cannot load {path}: {e}") from None
-            _loaded[name] = lib
+            _loaded[key] = lib
     return lib
 
 
+# Libraries that are built once per value of a compile-time size: build_all()
+# compiles every allowed value, a running process only the one its model has.
+VARIANTS = {"attention_tc": [{"KLLM_HD": hd} for hd in range(16, 129, 16)]}
+
+
 def build_all(verbose: bool = True) -> List[str]:
-    return [compile_library(n, verbose=verbose) for n in sources()]
+    out = []
+    for n in sources():
+        for defines in VARIANTS.get(n, [None]):
+            out.append(compile_library(n, verbose=verbose, defines=defines))
+    return out
 
 
 if __name__ == "__main__":

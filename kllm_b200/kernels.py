@@ -165,6 +165,85 @@ def attention_generic(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, 
     _check(lib, "attention_generic", rc)
 
 
+TC_HEAD_DIMS = tuple(range(16, 129, 16))     # head sizes of the tensor-core attention library
+SM_COUNT = 148
+
+
+def decode_splits(n_tokens: int, n_kv: int, ctx_bound: int) -> int:
+    """Into how many key ranges the decode kernel cuts a token's context: enough
+    CTAs for two per SM, none shorter than 128 keys."""
+    base = max(1, n_tokens * n_kv)
+    return max(1, min(-(-2 * SM_COUNT // base), -(-ctx_bound // 128), 32))
+
+
+def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, ctx,
+              block_table: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, window: int,
+              scale: float) -> None:
+    """Causal GQA attention of the step's tokens over the paged cache, by the
+    kernel that fits: bfloat16 with a head size in TC_HEAD_DIMS runs on tensor cores
+    (the decode form when every request brings one token, else the prefill form);
+    float32, other head sizes or very wide groups run the generic kernel."""
+    group = n_heads // max(1, n_kv)
+    tc = q.dtype == torch.bfloat16 and head_dim in TC_HEAD_DIMS
+    if tc and ctx.all_single and group <= 16:
+        return attention_decode(out, q, kcache, vcache, ctx.positions, ctx.token_req, block_table, n_heads,
+                                n_kv, head_dim, window, scale,
+                                decode_splits(ctx.n_tokens, n_kv, ctx.split_bound or ctx.max_ctx))
+    if tc and group <= 64:
+        return attention_prefill(out, q, kcache, vcache, ctx.q_start, ctx.start_pos, block_table,
+                                 ctx.n_requests, n_heads, n_kv, head_dim, window, scale)
+    return attention_generic(out, q, kcache, vcache, ctx.positions, ctx.token_req, block_table, n_heads, n_kv,
+                             head_dim, window, scale)
+
+
+def _check_attention(out, q, kcache, vcache, block_table, n_kv, head_dim):
+    if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16:
+        raise KernelError("tensor-core attention takes bfloat16 operands")
+    if q.stride(1) != 1 or not out.is_contiguous() or not kcache.is_contiguous() or not vcache.is_contiguous():
+        raise KernelError("attention: out and caches contiguous, q rows dense")
+    if kcache.shape[1] != n_kv or kcache.shape[3] != head_dim or kcache.shape != vcache.shape:
+        raise KernelError("attention: cache layout must be [pages, n_kv, page_size, head_dim]")
+    _i32(block_table, "block_table")
+
+
+def attention_decode(out, q, kcache, vcache, positions, token_req, block_table, n_heads, n_kv, head_dim,
+                     window, scale, num_splits: int) -> None:
+    """Tensor-core decode attention: every token attends on its own, its keys cut
+    into ``num_splits`` ranges that are merged in a fixed order."""
+    _cuda(out, q, kcache, vcache, positions, token_req, block_table)
+    _check_attention(out, q, kcache, vcache, block_table, n_kv, head_dim)
+    _i32(positions, "positions"); _i32(token_req, "token_req")
+    n = q.shape[0]
+    part_o = part_ml = None
+    if num_splits > 1:
+        part_o = torch.empty((n, n_heads, num_splits, head_dim), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((n, n_heads, num_splits, 2), dtype=torch.float32, device=q.device)
+    lib = load_library("attention_tc", {"KLLM_HD": head_dim})
+    rc = lib.kllm_attention_decode(_p(out), _p(part_o), _p(part_ml), _p(q), ctypes.c_int64(q.stride(0)),
+                                   _p(kcache), _p(vcache), _p(positions), _p(token_req), _p(block_table),
+                                   block_table.shape[1], n, n_heads, n_kv, head_dim, kcache.shape[2],
+                                   int(window or 0), ctypes.c_float(scale), int(num_splits), _stream())
+    _check(lib, "attention_tc", rc)
+    global launches
+    if num_splits > 1:
+        launches += 1       # the combine kernel
+
+
+def attention_prefill(out, q, kcache, vcache, q_start, start_pos, block_table, n_requests, n_heads, n_kv,
+                      head_dim, window, scale) -> None:
+    """Tensor-core attention of portions: request s brings rows q_start[s]..q_start[s+1]
+    that start at cache position start_pos[s]."""
+    _cuda(out, q, kcache, vcache, q_start, start_pos, block_table)
+    _check_attention(out, q, kcache, vcache, block_table, n_kv, head_dim)
+    _i32(q_start, "q_start"); _i32(start_pos, "start_pos")
+    lib = load_library("attention_tc", {"KLLM_HD": head_dim})
+    rc = lib.kllm_attention_prefill(_p(out), _p(q), ctypes.c_int64(q.stride(0)), _p(kcache), _p(vcache),
+                                    _p(q_start), _p(start_pos), _p(block_table), block_table.shape[1],
+                                    q.shape[0], int(n_requests), n_heads, n_kv, head_dim, kcache.shape[2],
+                                    int(window or 0), ctypes.c_float(scale), _stream())
+    _check(lib, "attention_tc", rc)
+
+
 def silu_mul(out: torch.Tensor, gate: torch.Tensor, up: torch.Tensor) -> None:
     """out = silu(gate) * up; 2-D operands with dense rows (strided rows allowed)."""
     _cuda(out, gate, up)

@@ -84,9 +84,8 @@ class PagedAttention:
             kernels.rope_append(q, k, v, None, ctx.positions, ctx.token_req, cache.block_table,
                                 cache.k, cache.v, self.n_heads, self.n_kv, self.head_dim)
         attn = torch.empty((n, self.q_dim), dtype=self.dtype, device=xn.device)
-        kernels.attention_generic(attn, q, cache.k, cache.v, ctx.positions, ctx.token_req,
-                                  cache.block_table, self.n_heads, self.n_kv, self.head_dim,
-                                  self.window or 0, self.scale)
+        kernels.attention(attn, q, cache.k, cache.v, ctx, cache.block_table, self.n_heads, self.n_kv,
+                          self.head_dim, self.window or 0, self.scale)
         return kernels.linear(attn, self.w_o)
 
 

@@ -38,6 +38,7 @@ class StepContext:
     max_new: int = 0
     max_ctx: int = 0
     all_single: bool = False   # every request brings exactly one token
+    split_bound: int = 0       # context bound that fixes launch shapes (0: use max_ctx)
 
 
 @dataclass

@@ -82,9 +82,15 @@ def plain_logits(weights: dict, cfg: dict, ids, dtype: str) -> np.ndarray:
     return plain.forward(rounded_weights(weights), cfg, ids, rnd=plain.round_act_bf16)
 
 
+WORST = {}      # dtype -> (largest error / tolerance seen in this run, where)
+
+
 def assert_close(got: np.ndarray, want: np.ndarray, dtype: str, what: str = ""):
     scale = max(1e-6, float(np.abs(want).max()))
     err = float(np.abs(got.astype(np.float64) - want).max())
+    ratio = err / (TOL[dtype] * scale)
+    if ratio > WORST.get(dtype, (0.0, ""))[0]:
+        WORST[dtype] = (ratio, what)
     assert err <= TOL[dtype] * scale, (
         f"{what}: max |diff| {err:.3e} exceeds {TOL[dtype]:.0e} * {scale:.3e} "
         f"(first bad row {int(np.argmax(np.abs(got - want).max(axis=-1)))})")

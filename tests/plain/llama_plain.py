@@ -49,13 +49,16 @@ def rope(x, positions, n_heads, head_dim, theta):
     return out.reshape(t, n_heads * head_dim)
 
 
-def attention(q, k, v, n_heads, n_kv_heads, head_dim, window=None, scale=None):
+def attention(q, k, v, n_heads, n_kv_heads, head_dim, window=None, scale=None, rnd_p=None):
     """Causal grouped-query attention of a whole sequence.
 
     Per (token t, head h): kv head g = h // (H/G); keys 0..t (or the last
     ``window`` of them); score = (q . k) * 1/sqrt(hd); max-subtracted softmax;
     weighted sum of values (backend/model.cu:343-408, scale at :1063-1064, window
-    start at :361-362; tools/gen_reference_numpy_moe.py:103-118).
+    start at :361-362; tools/gen_reference_numpy_moe.py:103-118).  ``rnd_p`` rounds
+    the unnormalised probabilities exp(s - max) before they meet the values, as an
+    engine does that feeds them to a reduced-precision matrix unit; the sum that
+    divides is taken of the unrounded ones.
     """
     q, k, v = f64(q), f64(k), f64(v)
     t = q.shape[0]
@@ -76,8 +79,10 @@ def attention(q, k, v, n_heads, n_kv_heads, head_dim, window=None, scale=None):
         sc = np.where(mask, sc, -np.inf)
         sc = sc - sc.max(axis=1, keepdims=True)
         p = np.exp(sc)
-        p /= p.sum(axis=1, keepdims=True)
-        out[:, h * head_dim:(h + 1) * head_dim] = p @ vh
+        total = p.sum(axis=1, keepdims=True)
+        if rnd_p is not None:
+            p = rnd_p(p)
+        out[:, h * head_dim:(h + 1) * head_dim] = (p @ vh) / total
     return out
 
 
@@ -109,7 +114,8 @@ def attention_block(x, w, prefix, cfg, positions, rnd=_same):
     v = rnd(x @ f64(w[prefix + ".self_attn.v_proj.weight"]).T)
     q = rnd(rope(q, positions, nh, hd, cfg["rope_theta"]))
     k = rnd(rope(k, positions, nkv, hd, cfg["rope_theta"]))
-    a = rnd(attention(q, k, v, nh, nkv, hd, window=cfg.get("sliding_window")))
+    a = rnd(attention(q, k, v, nh, nkv, hd, window=cfg.get("sliding_window"),
+                      rnd_p=None if rnd is _same else rnd))
     return rnd(a @ f64(w[prefix + ".self_attn.o_proj.weight"]).T)
 
 

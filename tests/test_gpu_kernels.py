@@ -114,9 +114,12 @@ def paged(k, v, page_size, n_pages, rng, dtype, lengths):
     return dev(kc, DT[dtype]), dev(vc, DT[dtype]), dev(table)
 
 
-def attention_case(dtype, H, G, hd, page_size, lengths, n_new, window, seed, plant=None):
+def attention_case(dtype, H, G, hd, page_size, lengths, n_new, window, seed, plant=None, kernel="generic",
+                   splits=1):
     """Requests with ``lengths`` cached tokens, the last ``n_new`` of each being this
-    step's queries.  Returns (got, want) for all queries."""
+    step's queries.  Returns (got, want) for all queries.  ``kernel``: generic, decode
+    (tensor cores, every token on its own, keys cut into ``splits`` ranges) or
+    prefill (tensor cores, portions)."""
     from kllm_b200 import kernels
     rng = np.random.default_rng(seed)
     ks, vs, qs, pos, req, want = [], [], [], [], [], []
@@ -135,8 +138,18 @@ def attention_case(dtype, H, G, hd, page_size, lengths, n_new, window, seed, pla
     kc, vc, table = paged(ks, vs, page_size, sum(-(-L // page_size) for L in lengths) + 3, rng, dtype, lengths)
     q = dev(np.concatenate(qs), DT[dtype])
     out = torch.empty_like(q)
-    kernels.attention_generic(out, q, kc, vc, dev(np.array(pos, np.int32)), dev(np.array(req, np.int32)), table,
-                              H, G, hd, window or 0, 1.0 / math.sqrt(hd))
+    scale = 1.0 / math.sqrt(hd)
+    if kernel == "generic":
+        kernels.attention_generic(out, q, kc, vc, dev(np.array(pos, np.int32)), dev(np.array(req, np.int32)), table,
+                                  H, G, hd, window or 0, scale)
+    elif kernel == "decode":
+        kernels.attention_decode(out, q, kc, vc, dev(np.array(pos, np.int32)), dev(np.array(req, np.int32)), table,
+                                 H, G, hd, window or 0, scale, splits)
+    else:
+        q_start = np.concatenate([[0], np.cumsum(n_new)]).astype(np.int32)
+        start_pos = np.array([L - nn for L, nn in zip(lengths, n_new)], dtype=np.int32)
+        kernels.attention_prefill(out, q, kc, vc, dev(q_start), dev(start_pos), table, len(lengths), H, G, hd,
+                                  window or 0, scale)
     return out, np.concatenate(want)
 
 
@@ -147,6 +160,65 @@ def test_attention_shapes_pages_and_mixed_query_lengths(dtype, H, G, hd, page):
     got, want = attention_case(dtype, H, G, hd, page, lengths, n_new, None, seed=H * hd)
     assert not torch.isnan(got).any(), "a slot beyond a request's length was read"
     close(got, want, dtype)
+
+
+TC_SHAPES = [(8, 2, 64, 16), (6, 2, 80, 8), (5, 5, 48, 16), (7, 1, 16, 3), (32, 4, 128, 64), (3, 1, 32, 16),
+             (16, 1, 112, 5), (4, 4, 96, 32)]
+
+
+@pytest.mark.parametrize("H,G,hd,page", TC_SHAPES)
+@pytest.mark.parametrize("kernel,splits", [("decode", 1), ("decode", 3), ("decode", 8), ("prefill", 1)])
+def test_tensor_core_attention_shapes_pages_and_mixed_query_lengths(kernel, splits, H, G, hd, page):
+    lengths, n_new = [70, 1, 33, 129, 300], [70, 1, 2, 1, 64]
+    got, want = attention_case("bfloat16", H, G, hd, page, lengths, n_new, None, seed=H * hd, kernel=kernel,
+                               splits=splits)
+    assert not torch.isnan(got.float()).any(), "a slot beyond a request's length was read"
+    close(got, want, "bfloat16")
+
+
+@pytest.mark.parametrize("kernel,splits", [("decode", 1), ("decode", 5), ("prefill", 1)])
+@pytest.mark.parametrize("window", [1, 5, 64, 65, 200])
+def test_tensor_core_attention_window_edge(kernel, splits, window):
+    H, G, hd, L = 4, 2, 64, 330
+
+    def plant(s, q, k, v):
+        outside = L - 1 - window
+        if s == 0 and outside >= 0:
+            k[outside, :] = 50.0 * q[-1, 0] / np.abs(q[-1, 0]).max()
+            v[outside, :] = 1e4
+
+    got, want = attention_case("bfloat16", H, G, hd, 16, [L, 40, 129], [L, 3, 1], window, seed=window, plant=plant,
+                               kernel=kernel, splits=splits)
+    close(got, want, "bfloat16")
+    assert float(got[L - 1].float().abs().max()) < 100.0
+
+
+@pytest.mark.parametrize("kernel,splits", [("decode", 1), ("decode", 4), ("prefill", 1)])
+def test_tensor_core_attention_finds_one_far_key(kernel, splits):
+    H, G, hd, L = 4, 2, 64, 900
+    far = 3
+
+    def plant(s, q, k, v):
+        q[-1] *= 0.05
+        k[far, 1] = 8.0 * np.sign(q[-1, 2])
+        q[-1, 2] = 3.0 * np.sign(q[-1, 2])
+
+    got, want = attention_case("bfloat16", H, G, hd, 16, [L], [1], None, seed=7, plant=plant, kernel=kernel,
+                               splits=splits)
+    close(got, want, "bfloat16")
+    assert np.abs(want.reshape(1, H, hd)[0, 2]).max() > 0.5
+
+
+def test_tensor_core_attention_refusals():
+    from kllm_b200 import kernels
+    q = torch.zeros(1, 34 * 64, device="cuda", dtype=torch.bfloat16)
+    kc = torch.zeros(2, 2, 16, 64, device="cuda", dtype=torch.bfloat16)
+    z = torch.zeros(1, dtype=torch.int32, device="cuda")
+    with pytest.raises(kernels.KernelError, match="at most 16"):
+        kernels.attention_decode(torch.empty_like(q), q, kc, kc, z, z, z.view(1, 1), 34, 2, 64, 0, 1.0, 1)
+    with pytest.raises(kernels.KernelError, match="bfloat16"):
+        kernels.attention_decode(torch.empty_like(q).float(), q.float(), kc.float(), kc.float(), z, z, z.view(1, 1),
+                                 34, 2, 64, 0, 1.0, 1)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
