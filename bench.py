@@ -160,15 +160,20 @@ def main():
         return torch.randint(0, cfg["vocab_size"], (n, length), generator=g).tolist()
 
     def decode_run(batch, steps, warm, sample_clocks=False):
-        """Prefill ``batch`` requests so that the last timed step lands on context
-        ``ctx``; returns (device ms per step, e2e ms per step, launches, h2d, d2h, clocks)."""
-        total = 2 * (steps + warm)
-        plen = ctx - total - 1
+        """Prefill ``batch`` requests and decode them together so that the furthest
+        one ends at context ``ctx``.  Prompts are prefilled one a step while earlier
+        requests already decode, so the requests' contexts differ by up to ``batch``
+        tokens; all of them stay live through both timed regions.  Returns (device ms
+        per step, e2e ms per step, launches, h2d, d2h, clocks, cached tokens in the
+        middle of the device-timed region)."""
+        total = 2 * (steps + warm) + batch + 2
+        plen = ctx - total
         sched = Scheduler(eng)
         for p in prompts(batch, plen):
-            sched.submit(p, total + 1)
+            sched.submit(p, total)
         while any(r.fed < len(r.prompt) for r in list(sched.running) + list(sched.waiting)):
             sched.step()
+        assert len(sched.running) == batch
         for _ in range(warm):
             sched.step()
         torch.cuda.synchronize()
@@ -185,6 +190,8 @@ def main():
         t1 = time.time()
         dev_ms = ev0.elapsed_time(ev1) / steps
         launches = (kernels.launches - l0) // steps
+        assert len(sched.running) == batch, "a request ended inside the timed region"
+        cached = sum(r.cache.length for r in sched.running) - batch * steps // 2
         # end to end: wall clock around the public API, synchronised on both sides
         for _ in range(warm):
             sched.step()
@@ -199,14 +206,15 @@ def main():
             time.sleep(0.15)
             clocks.stop()
             csum = clocks.summary(t0, t1)
+        assert len(sched.running) == batch, "a request ended inside the timed region"
         h2d = eng.runner.last_h2d_bytes
         sched.stop()
-        return dev_ms, e2e_ms, launches, h2d, batch * 4, csum
+        return dev_ms, e2e_ms, launches, h2d, batch * 4, csum, cached
 
     with torch.no_grad():
-        dev_ms, e2e_ms, launches, h2d, d2h, clocks = decode_run(B, K, W, sample_clocks=True)
+        dev_ms, e2e_ms, launches, h2d, d2h, clocks, cached = decode_run(B, K, W, sample_clocks=True)
         per_layer, weight_elems = model_bytes_and_flops(cfg, layers)
-        kv_bytes = B * ctx * eng.cache.bytes_per_token_full()
+        kv_bytes = cached * eng.cache.bytes_per_token_full()
         step_bytes = 2 * weight_elems + kv_bytes
         achieved = step_bytes / (dev_ms * 1e-3) / 1e9
         out = {
@@ -225,7 +233,8 @@ def main():
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches * K,
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                         "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": step_bytes},
+                         "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": step_bytes,
+                         "mean_context": cached // B},
         }
         if not args.no_points:
             T = 2048
@@ -251,7 +260,7 @@ def main():
                               "frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
             pts = {}
             for b in (1, 64):
-                dms, _, _, _, _, _ = decode_run(b, max(8, K // 2), 3)
+                dms = decode_run(b, max(8, K // 2), 3)[0]
                 pts[f"decode_b{b}"] = round(b / (dms * 1e-3), 1)
             out["points"] = pts
     print(json.dumps(out))

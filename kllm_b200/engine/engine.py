@@ -37,6 +37,7 @@ class Options:
     max_step_tokens: int = 0      # token budget of one step; 0: max_seq
     max_batch: int = 8            # most requests in one step
     dtype: str = "bfloat16"       # "bfloat16" (serving) or "float32" (true 32-bit)
+    cuda_graphs: bool = True      # replay decode steps as CUDA graphs
 
     def fill(self) -> "Options":
         o = Options(**self.__dict__)
@@ -97,7 +98,8 @@ class Engine:
             del tensors
             self.cache = CacheManager(self.model.cache_needs(), opts.block_size, opts.num_blocks,
                                       max_requests=opts.max_batch, dtype=self.dtype, device=self.device)
-        self.runner = StepRunner(self.model, self.cache, opts.max_step_tokens, opts.max_batch, opts.max_seq)
+        self.runner = StepRunner(self.model, self.cache, opts.max_step_tokens, opts.max_batch, opts.max_seq,
+                                 use_graphs=opts.cuda_graphs)
         self.sampler = Sampler(self.device)
         self.eos_token_ids = tuple(self.spec.eos_token_ids)
 

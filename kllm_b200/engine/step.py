@@ -36,9 +36,88 @@ class StepEntry:
     want: Sequence[int] = ()      # places among ``tokens`` whose logits are wanted
 
 
+class GraphedDecode:
+    """One decode step of a fixed batch size as a CUDA graph.
+
+    A decode step of B requests launches over a hundred small kernels; replayed as
+    one graph they cost one launch.  The graph reads the step's description (token
+    ids, positions, block tables, state slots) from device buffers at fixed
+    addresses that are refilled before every replay, and leaves the logits of all B
+    tokens in a buffer of its own.  Launch shapes are fixed at capture: the block
+    table is as wide as the longest sequence allows and the decode attention cuts
+    every context as if it had that length.  The first step of a batch size runs
+    eagerly on the same buffers (which also warms up every library), the capture
+    follows without executing anything, and later steps replay.
+    """
+
+    def __init__(self, runner: "StepRunner", batch: int):
+        self.runner = runner
+        self.batch = batch
+        cache, dev = runner.cache, runner.device
+        self.width = max(1, -(-runner.max_seq // cache.page_size))
+        B = batch
+        sizes = [B, B, B, B + 1, B, B, B, B] + [B * self.width for _ in cache.groups]
+        self.offs = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
+        total = int(self.offs[-1])
+        self.host = torch.empty(total, dtype=torch.int32, pin_memory=True)
+        self.h = self.host.numpy()
+        self.dev = torch.zeros(total, dtype=torch.int32, device=dev)
+        o = self.offs
+        self.h[:] = 0
+        self.h[o[2]:o[3]] = np.arange(B)            # token_req: token i belongs to request i
+        self.h[o[3]:o[4]] = np.arange(B + 1)        # q_start
+        self.h[o[7]:o[8]] = np.arange(B)            # every row is wanted
+        part = lambda i: self.dev[int(o[i]):int(o[i + 1])]
+        tables = {gi: part(8 + gi).view(B, self.width) for gi in range(len(cache.groups))}
+        self.ctx = StepContext(
+            n_tokens=B, n_requests=B, token_ids=part(0), positions=part(1), token_req=part(2), q_start=part(3),
+            start_pos=part(4), ctx_len=part(5), state_slots=part(6), block_tables=tables, want_rows=part(7),
+            n_want=B, host_n_new=[1] * B, host_start_pos=[0] * B, max_new=1, max_ctx=runner.max_seq,
+            all_single=True, split_bound=runner.max_seq)
+        self.caches = cache.layer_caches(tables)
+        self.graph = None
+        self.logits = None
+        self.launches = 0
+
+    def fill(self, entries: Sequence["StepEntry"]) -> None:
+        o, h, B, W = self.offs, self.h, self.batch, self.width
+        h[o[0]:o[1]] = [int(e.tokens[0]) for e in entries]
+        start = [e.request.length for e in entries]
+        h[o[1]:o[2]] = start
+        h[o[4]:o[5]] = start
+        h[o[5]:o[6]] = [s + 1 for s in start]
+        h[o[6]:o[7]] = [e.request.state_slot for e in entries]
+        for gi in range(len(self.runner.cache.groups)):
+            tab = h[o[8 + gi]:o[9 + gi]].reshape(B, W)
+            for si, e in enumerate(entries):
+                t = e.request.tables[gi]
+                tab[si, :len(t)] = t
+        self.dev.copy_(self.host, non_blocking=True)
+        self.runner.last_h2d_bytes = self.host.numel() * 4
+
+    def run(self, entries: Sequence["StepEntry"]) -> torch.Tensor:
+        from .. import kernels
+        self.fill(entries)
+        model = self.runner.model
+        if self.graph is None:
+            before = kernels.launches
+            logits = model.forward(self.ctx, self.caches)          # this step, eagerly
+            self.launches = kernels.launches - before
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self.logits = model.forward(self.ctx, self.caches)
+            kernels.launches = before + self.launches              # recording launched nothing
+            self.graph = graph
+            return logits
+        self.graph.replay()
+        kernels.launches += self.launches
+        return self.logits
+
+
 class StepRunner:
     def __init__(self, model: DecoderModel, cache: CacheManager, max_step_tokens: int,
-                 max_batch: int, max_seq: int):
+                 max_batch: int, max_seq: int, use_graphs: bool = True):
         self.model = model
         self.cache = cache
         self.max_step_tokens = int(max_step_tokens)
@@ -49,6 +128,8 @@ class StepRunner:
         self.steps = 0
         self.tokens_run = 0
         self.last_h2d_bytes = 0     # bytes of the last step's host-to-device copy
+        self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
+        self.graphs = {}            # batch size -> GraphedDecode
 
     # ---- validation --------------------------------------------------------
     def validate(self, entries: Sequence[StepEntry]) -> None:
@@ -131,7 +212,8 @@ class StepRunner:
     # ---- run ---------------------------------------------------------------
     def run(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Logits float32 [wanted, vocab] on the device, in the order of the entries
-        and of each entry's ``want``; None if nothing is wanted.  Raises ``StepError``
+        and of each entry's ``want``; None if nothing is wanted.  They stay valid until
+        the next step (a replayed decode step reuses its buffer).  Raises ``StepError``
         for an invalid batch and ``OutOfPages`` when the cache cannot hold it; in both
         cases nothing has changed."""
         self.validate(entries)
@@ -142,8 +224,14 @@ class StepRunner:
         for r, n in wants:
             self.cache.reserve(r, n)
         try:
-            ctx = self.build_context(entries)
-            logits = self.model.forward(ctx, self.cache.layer_caches(ctx.block_tables))
+            if self.use_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+                g = self.graphs.get(len(entries))
+                if g is None:
+                    g = self.graphs[len(entries)] = GraphedDecode(self, len(entries))
+                logits = g.run(entries)
+            else:
+                ctx = self.build_context(entries)
+                logits = self.model.forward(ctx, self.cache.layer_caches(ctx.block_tables))
         except Exception:
             for r, _ in wants:
                 self.cache.trim_reservation(r)

@@ -43,7 +43,7 @@ def check_choices(w, cfg, dtype, prompt, generated, temperature=0.0, seed=0, rid
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_greedy_through_the_entry_point(tmp_path, name, dtype):
     import kllm_b200
-    cfg, w = make_weights(name)
+    cfg, w = make_weights(name, dtype)
     d = write_model_dir(str(tmp_path / "m"), cfg, w)
     prompts = prompts_for(cfg, [5, 17, 31, 64] if name == "A" else [1, 3, 40, 100], seed=1)
     steps = 16 if name == "A" else 24
@@ -88,7 +88,7 @@ def test_temperature_is_reproducible_and_independent_of_batching(tmp_path):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_temperature_draws_are_valid_in_both_dtypes(tmp_path, dtype):
     import kllm_b200
-    cfg, w = make_weights("A")
+    cfg, w = make_weights("A", dtype)
     d = write_model_dir(str(tmp_path / "m"), cfg, w)
     p = prompts_for(cfg, [9], seed=8)[0]
     out = kllm_b200.generate(d, p, steps=20, max_seq=128, dtype=dtype, temperature=1.3, seed=5)
@@ -99,7 +99,7 @@ def test_temperature_draws_are_valid_in_both_dtypes(tmp_path, dtype):
 def test_long_decoding_and_first_tokens(tmp_path, dtype):
     """One token of prompt, then token by token to the end of the position range."""
     from kllm_b200.engine import Engine, Options, StepEntry
-    cfg, w = make_weights("B")
+    cfg, w = make_weights("B", dtype)
     d = write_model_dir(str(tmp_path / "m"), cfg, w)
     ids = prompts_for(cfg, [256], seed=11)[0]
     eng = Engine(d, Options(dtype=dtype, max_seq=256, block_size=16, num_blocks=16, max_batch=2))

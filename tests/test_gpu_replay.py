@@ -70,7 +70,7 @@ def build_trace(seqs, sizes, seed):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_replay_all_ways(tmp_path, name, dtype):
-    cfg, w = make_weights(name)
+    cfg, w = make_weights(name, dtype)
     d = write_model_dir(str(tmp_path / "model"), cfg, w)
     seqs = prompts_for(cfg, LENGTHS[name], seed=3)
     tb = build_trace(seqs, SIZES[name], seed=5)

@@ -14,7 +14,7 @@ LENGTHS = {"A": [5, 17, 31, 64], "B": [1, 3, 40, 100, 128, 200]}
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_whole_prompts(tmp_path, name, dtype):
     from kllm_b200.engine import Engine, Options, StepEntry
-    cfg, w = make_weights(name)
+    cfg, w = make_weights(name, dtype)
     d = write_model_dir(str(tmp_path / name), cfg, w)
     eng = Engine(d, Options(dtype=dtype, max_seq=cfg["max_position_embeddings"], block_size=16,
                             num_blocks=32, max_batch=4))
