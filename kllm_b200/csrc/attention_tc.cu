@@ -28,6 +28,7 @@
 // (backend/model.cu:343-408): keys [max(0, p + 1 - window), p], scale after the
 // dot product, one division by the sum at the end.
 #include "common.cuh"
+#include "attention_tc_static.h"
 
 #ifndef KLLM_HD
 #error "compile with -DKLLM_HD=<head size>"
@@ -496,6 +497,58 @@ extern "C" int kllm_attention_decode(void* out, void* part_o, void* part_ml, con
         attn_combine_kernel<<<n_tokens * n_heads, HD < 64 ? 32 : 64, 0, s>>>((bf16*)out, (const float*)part_o,
                                                                           (const float*)part_ml, num_splits);
     KLLM_LAUNCH_STATUS();
+}
+
+// ---- the entry point that allocates nothing (see attention_tc_static.h) ----------
+//
+// In host code the name of a __device__ array is only a handle for the runtime, not
+// an address a kernel could use; the device address is asked for once per device.
+static __device__ __align__(256) float g_static_scratch[KLLM_ATTN_STATIC_SCRATCH_FLOATS];
+static constexpr int kMaxDevices = 64;
+static float* g_static_scratch_addr[kMaxDevices] = {};
+
+extern "C" int kllm_attention_decode_static(void* out, const void* q, int64_t q_stride, const void* kcache,
+                                            const void* vcache, const int* positions, const int* token_req,
+                                            const int* block_table, int max_blocks, int n_tokens, int n_heads,
+                                            int n_kv, int hd, int page_size, int window, float scale,
+                                            int num_splits, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (num_splits < 1) KLLM_FAIL("attention decode (static scratch): num_splits %d", num_splits);
+    float* part_o = nullptr;
+    float* part_ml = nullptr;
+    if (num_splits > 1) {
+        const int64_t slots = (int64_t)n_tokens * n_heads * num_splits;
+        const int64_t need = slots * (HD + 2);
+        if (need > (int64_t)KLLM_ATTN_STATIC_SCRATCH_FLOATS)
+            KLLM_FAIL("attention decode (static scratch): %d tokens x %d heads x %d splits need %lld floats of "
+                      "scratch, the built-in array holds %d; use fewer splits or the entry point that takes "
+                      "scratch buffers", n_tokens, n_heads, num_splits, (long long)need,
+                      KLLM_ATTN_STATIC_SCRATCH_FLOATS);
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) {
+            snprintf(g_kllm_err, sizeof(g_kllm_err), "attention decode (static scratch): cudaGetDevice: %s",
+                     cudaGetErrorString(e));
+            return (int)e;
+        }
+        if (dev < 0 || dev >= kMaxDevices) KLLM_FAIL("attention: device ordinal %d not supported", dev);
+        if (g_static_scratch_addr[dev] == nullptr) {
+            float* p = nullptr;
+            e = cudaGetSymbolAddress((void**)&p, g_static_scratch);
+            if (e != cudaSuccess || p == nullptr) {
+                snprintf(g_kllm_err, sizeof(g_kllm_err),
+                         "attention decode (static scratch): cudaGetSymbolAddress on device %d: %s", dev,
+                         cudaGetErrorString(e));
+                return e != cudaSuccess ? (int)e : KLLM_ERR_ARG;
+            }
+            g_static_scratch_addr[dev] = p;
+        }
+        part_o = g_static_scratch_addr[dev];
+        part_ml = part_o + slots * HD;
+    }
+    return kllm_attention_decode(out, part_o, part_ml, q, q_stride, kcache, vcache, positions, token_req,
+                                 block_table, max_blocks, n_tokens, n_heads, n_kv, hd, page_size, window, scale,
+                                 num_splits, stream);
 }
 
 // Prefill form: requests' portions q_start[s]..q_start[s+1] (prefix sums, [n_requests+1])
