@@ -1,17 +1,18 @@
 // Gated activation of the feed-forward: out = act(gate) * up, act = SiLU,
 // computed in float32 (reference backend/model.cu:477-483:
 // g / (1 + expf(-g)) * u).  gate and up may be the two halves of one fused
-// projection output: each has its own row stride.
+// projection output: each has its own row stride.  They may be float32 beside a
+// bfloat16 out, so that the activation sees the projection's unrounded result.
 #include "common.cuh"
 
 KLLM_EXPORT_LAST_ERROR(activation)
 
 namespace {
 
-template <typename T>
+template <typename T, typename I>
 __global__ void silu_mul_kernel(T* __restrict__ out, int64_t out_stride,
-                                const T* __restrict__ gate, int64_t gate_stride,
-                                const T* __restrict__ up, int64_t up_stride, int n, int f) {
+                                const I* __restrict__ gate, int64_t gate_stride,
+                                const I* __restrict__ up, int64_t up_stride, int n, int f) {
     const int64_t total = (int64_t)n * f;
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (int64_t)gridDim.x * blockDim.x) {
@@ -25,21 +26,25 @@ __global__ void silu_mul_kernel(T* __restrict__ out, int64_t out_stride,
 
 }  // namespace
 
+// dtype: element type of out; in_dtype: element type of gate and up.
 extern "C" int kllm_silu_mul(void* out, int64_t out_stride, const void* gate, int64_t gate_stride,
-                             const void* up, int64_t up_stride, int n, int f, int dtype,
+                             const void* up, int64_t up_stride, int n, int f, int dtype, int in_dtype,
                              void* stream) {
     if (n <= 0 || f <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const int64_t total = (int64_t)n * f;
     int64_t blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    if (dtype == KLLM_F32)
-        silu_mul_kernel<float><<<(unsigned)blocks, 256, 0, s>>>(
+    if (dtype == KLLM_F32 && in_dtype == KLLM_F32)
+        silu_mul_kernel<float, float><<<(unsigned)blocks, 256, 0, s>>>(
             (float*)out, out_stride, (const float*)gate, gate_stride, (const float*)up, up_stride, n, f);
-    else if (dtype == KLLM_BF16)
-        silu_mul_kernel<bf16><<<(unsigned)blocks, 256, 0, s>>>(
+    else if (dtype == KLLM_BF16 && in_dtype == KLLM_BF16)
+        silu_mul_kernel<bf16, bf16><<<(unsigned)blocks, 256, 0, s>>>(
             (bf16*)out, out_stride, (const bf16*)gate, gate_stride, (const bf16*)up, up_stride, n, f);
+    else if (dtype == KLLM_BF16 && in_dtype == KLLM_F32)
+        silu_mul_kernel<bf16, float><<<(unsigned)blocks, 256, 0, s>>>(
+            (bf16*)out, out_stride, (const float*)gate, gate_stride, (const float*)up, up_stride, n, f);
     else
-        KLLM_FAIL("silu_mul: unknown element type %d", dtype);
+        KLLM_FAIL("silu_mul: element types %d (out) and %d (in) are not supported together", dtype, in_dtype);
     KLLM_LAUNCH_STATUS();
 }

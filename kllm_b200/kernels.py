@@ -97,8 +97,9 @@ def add_rmsnorm(x: torch.Tensor, res: Optional[torch.Tensor], out: torch.Tensor,
     d = x.shape[1]
     if x.dtype != torch.float32 or gain.dtype != torch.float32 or not x.is_contiguous() or not out.is_contiguous():
         raise KernelError("add_rmsnorm: x and gain must be float32, contiguous")
-    if res is not None and (res.dtype != out.dtype or not res.is_contiguous() or res.shape != x.shape):
-        raise KernelError("add_rmsnorm: res must match x in shape and out in dtype")
+    if res is not None and (res.dtype not in (out.dtype, torch.float32) or not res.is_contiguous()
+                            or res.shape != x.shape):
+        raise KernelError("add_rmsnorm: res must match x in shape and be float32 or of out's dtype")
     if gain.numel() != d or out.shape[1] != d:
         raise KernelError("add_rmsnorm: widths do not agree")
     n_rows = out.shape[0]
@@ -108,7 +109,8 @@ def add_rmsnorm(x: torch.Tensor, res: Optional[torch.Tensor], out: torch.Tensor,
         raise KernelError("add_rmsnorm: rows and out do not agree")
     lib = load_library("norm")
     rc = lib.kllm_add_rmsnorm(_p(x), _p(res), _p(out), _p(gain), _p(rows), n_rows, d,
-                              ctypes.c_float(eps), dtype_code(out.dtype), _stream())
+                              ctypes.c_float(eps), dtype_code(out.dtype),
+                              dtype_code(res.dtype if res is not None else out.dtype), _stream())
     _check(lib, "norm", rc)
 
 
@@ -245,15 +247,19 @@ def attention_prefill(out, q, kcache, vcache, q_start, start_pos, block_table, n
 
 
 def silu_mul(out: torch.Tensor, gate: torch.Tensor, up: torch.Tensor) -> None:
-    """out = silu(gate) * up; 2-D operands with dense rows (strided rows allowed)."""
+    """out = silu(gate) * up; 2-D operands with dense rows (strided rows allowed);
+    gate and up share a dtype, float32 or out's."""
     _cuda(out, gate, up)
     for t in (out, gate, up):
-        if t.stride(1) != 1 or t.dtype != out.dtype:
-            raise KernelError("silu_mul: operands must share a dtype and have dense rows")
+        if t.stride(1) != 1:
+            raise KernelError("silu_mul: operands must have dense rows")
+    if gate.dtype != up.dtype or gate.dtype not in (out.dtype, torch.float32):
+        raise KernelError("silu_mul: gate and up must share a dtype, float32 or out's")
     n, f = out.shape
     lib = load_library("activation")
     rc = lib.kllm_silu_mul(_p(out), ctypes.c_int64(out.stride(0)), _p(gate), ctypes.c_int64(gate.stride(0)),
-                           _p(up), ctypes.c_int64(up.stride(0)), n, f, dtype_code(out.dtype), _stream())
+                           _p(up), ctypes.c_int64(up.stride(0)), n, f, dtype_code(out.dtype),
+                           dtype_code(gate.dtype), _stream())
     _check(lib, "activation", rc)
 
 
@@ -271,6 +277,71 @@ def sample(out: torch.Tensor, logits: torch.Tensor, temperature: Optional[torch.
     rc = lib.kllm_sample(_p(out), _p(logits), ctypes.c_int64(logits.stride(0)), logits.shape[0],
                          logits.shape[1], _p(temperature), _p(uniform), _stream())
     _check(lib, "sampling", rc)
+
+
+SKINNY_MAX_ROWS = 16
+_PRO = {"bf16": 0, "norm": 1}
+_EPI = {"bf16": 0, "f32": 1, "add": 2, "swiglu": 3}
+
+
+def skinny_fits(n: int, k: int, dtype: torch.dtype) -> bool:
+    """Whether the weight-streaming product takes n rows of width k in this dtype."""
+    if dtype != torch.bfloat16 or not (1 <= n <= SKINNY_MAX_ROWS) or k < 32 or k % 32:
+        return False
+    nt = 1 if n <= 8 else 2
+    row = k + (32 if (k * 2) % 128 == 0 else 0)
+    return 8 * nt * row * 2 + 8 * 16 * 8 * nt * 4 <= 227 * 1024
+
+
+def skinny_gemm(weight: torch.Tensor, *, x: Optional[torch.Tensor] = None, x_f32: Optional[torch.Tensor] = None,
+                gain: Optional[torch.Tensor] = None, eps: float = 0.0, rows: Optional[torch.Tensor] = None,
+                n_rows: Optional[int] = None, weight_up: Optional[torch.Tensor] = None, epilogue: str = "bf16",
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = X @ weight^T for at most 16 rows, the weights streamed once (csrc/skinny_gemm.cu).
+
+    X is either ``x`` (bfloat16 [n, K]) or rmsnorm(``x_f32``) * ``gain`` computed inside
+    the kernel (rows ``rows`` of x_f32 when given).  ``epilogue``: "bf16" / "f32" store
+    y [n, N]; "add" adds y into the float32 ``out``; "swiglu" takes ``weight`` as gate and
+    ``weight_up`` as up matrix and stores silu(gate) * up as bfloat16 [n, N].
+    """
+    _cuda(weight, x, x_f32, gain, rows, weight_up, out)
+    N, K = weight.shape
+    if weight.dtype != torch.bfloat16 or not weight.is_contiguous():
+        raise KernelError("skinny_gemm: the weight must be contiguous bfloat16")
+    if x is not None:
+        pro, n = 0, x.shape[0]
+        if x.dtype != torch.bfloat16 or x.stride(1) != 1 or x.shape[1] != K:
+            raise KernelError("skinny_gemm: x must be bfloat16 [n, K] with dense rows")
+    else:
+        pro = 1
+        _i32(rows, "rows")
+        n = rows.numel() if rows is not None else x_f32.shape[0]
+        if n_rows is not None:
+            n = n_rows
+        if x_f32.dtype != torch.float32 or not x_f32.is_contiguous() or x_f32.shape[1] != K \
+                or gain.dtype != torch.float32 or gain.numel() != K:
+            raise KernelError("skinny_gemm: x_f32 [rows, K] and gain [K] must be contiguous float32")
+    if not skinny_fits(n, K, torch.bfloat16):
+        raise KernelError(f"skinny_gemm: {n} rows of width {K} are not supported")
+    epi = _EPI[epilogue]
+    if epilogue == "swiglu" and (weight_up is None or weight_up.shape != weight.shape or not weight_up.is_contiguous()
+                                 or weight_up.dtype != torch.bfloat16):
+        raise KernelError("skinny_gemm: swiglu needs an up matrix like the gate matrix")
+    if out is None:
+        if epilogue == "add":
+            raise KernelError("skinny_gemm: 'add' needs the matrix to add into")
+        out = torch.empty((n, N), dtype=torch.float32 if epilogue == "f32" else torch.bfloat16, device=weight.device)
+    want = torch.float32 if epilogue in ("f32", "add") else torch.bfloat16
+    if out.dtype != want or out.stride(1) != 1 or out.shape[0] < n or out.shape[1] != N:
+        raise KernelError("skinny_gemm: out has the wrong dtype or shape")
+    lib = load_library("skinny_gemm")
+    y16 = out if want == torch.bfloat16 else None
+    y32 = out if want == torch.float32 else None
+    rc = lib.kllm_skinny_gemm(_p(weight), _p(weight_up), N, K, n, _p(x),
+                              ctypes.c_int64(x.stride(0) if x is not None else 0), _p(x_f32), _p(gain), _p(rows),
+                              ctypes.c_float(eps), _p(y16), _p(y32), ctypes.c_int64(out.stride(0)), pro, epi, _stream())
+    _check(lib, "skinny_gemm", rc)
+    return out
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,

@@ -11,8 +11,14 @@ one product.
 
 Interface of a mixer part:
   ``cache_need()`` -> PagedKVNeed | StateNeed | None
-  ``forward(xn, ctx, cache) -> [n, hidden]`` in the model dtype, xn being the normed
-  input [n, hidden]; the residual sum is the block's business.
+  ``forward(xn, ctx, cache) -> [n, hidden]`` in float32 or the model dtype, xn being
+  the normed input [n, hidden]; the residual sum is the block's business.
+  Optional: ``forward_residual(x, norm, ctx, cache) -> bool`` takes the float32
+  residual stream itself, applies ``norm`` inside its first kernel and adds its
+  result into x; it returns False when it cannot (sizes, dtype, kind of norm) and
+  the block then takes the general route.  Here it serves steps of a few tokens
+  (decode): both projections become weight-streaming products with the norm as
+  prologue and the residual sum as epilogue (csrc/skinny_gemm.cu).
 The new keys and values of a step are written to the pages before attention runs,
 so a query sees the keys of its own portion through the cache, like every other
 key (reference :1096-1102).
@@ -68,25 +74,43 @@ class PagedAttention:
     def cache_need(self):
         return PagedKVNeed(self.n_kv, self.head_dim, self.window)
 
-    def forward(self, xn, ctx, cache):
-        n = xn.shape[0]
-        if cache.writes:
-            qkv = kernels.linear(xn, self.w_qkv)
-            q = qkv[:, :self.q_dim]
-            k = qkv[:, self.q_dim:self.q_dim + self.kv_dim]
-            v = qkv[:, self.q_dim + self.kv_dim:]
-        else:  # reads keys and values that another layer call wrote
-            q = kernels.linear(xn, self.w_qkv[:self.q_dim])
-            k = v = q
+    def _split(self, qkv, writes):
+        q = qkv[:, :self.q_dim]
+        if not writes:
+            return q, q, q
+        return q, qkv[:, self.q_dim:self.q_dim + self.kv_dim], qkv[:, self.q_dim + self.kv_dim:]
+
+    def _attend(self, q, k, v, ctx, cache):
+        n = q.shape[0]
         if self.position is not None:
             self.position.apply(q, k, v, ctx, cache, self.n_heads, self.n_kv)
         elif cache.writes:
             kernels.rope_append(q, k, v, None, ctx.positions, ctx.token_req, cache.block_table,
                                 cache.k, cache.v, self.n_heads, self.n_kv, self.head_dim)
-        attn = torch.empty((n, self.q_dim), dtype=self.dtype, device=xn.device)
+        attn = torch.empty((n, self.q_dim), dtype=self.dtype, device=q.device)
         kernels.attention(attn, q, cache.k, cache.v, ctx, cache.block_table, self.n_heads, self.n_kv,
                           self.head_dim, self.window or 0, self.scale)
-        return kernels.linear(attn, self.w_o)
+        return attn
+
+    def forward(self, xn, ctx, cache):
+        # a layer that reads another layer's cache projects its queries only
+        w = self.w_qkv if cache.writes else self.w_qkv[:self.q_dim]
+        q, k, v = self._split(kernels.linear(xn, w), cache.writes)
+        attn = self._attend(q, k, v, ctx, cache)
+        # float32 out: the result goes into the residual stream unrounded
+        return kernels.linear(attn, self.w_o, out_dtype=torch.float32)
+
+    def forward_residual(self, x, norm, ctx, cache):
+        n = x.shape[0]
+        if not (getattr(norm, "fusable_rmsnorm", False) and kernels.skinny_fits(n, self.hidden, self.dtype)
+                and kernels.skinny_fits(n, self.q_dim, self.dtype)):
+            return False
+        w = self.w_qkv if cache.writes else self.w_qkv[:self.q_dim]
+        qkv = kernels.skinny_gemm(w, x_f32=x, gain=norm.gain, eps=norm.eps, epilogue="bf16")
+        q, k, v = self._split(qkv, cache.writes)
+        attn = self._attend(q, k, v, ctx, cache)
+        kernels.skinny_gemm(self.w_o, x=attn, epilogue="add", out=x)
+        return True
 
 
 register_part("mixer", "paged_attention", PagedAttention)

@@ -6,8 +6,12 @@ first norm, or the model's final norm), as the reference does
 (backend/model.cu:1068-1072, 1083-1089, 1105, 1117).
 
 Interface of a block: ``forward(x, pending, ctx, cache) -> pending'``.  x is the
-float32 residual stream, updated in place; ``pending`` (model dtype, or None) is
-what is still to be added to x.
+float32 residual stream, updated in place; ``pending`` (float32 or model dtype, or
+None) is what is still to be added to x.
+
+A mixer or feed-forward may offer ``forward_residual`` (norm and residual sum inside
+its own kernels); the block tries it whenever nothing is pending and falls back to
+norm -> part -> pending otherwise.  Both routes compute the same sums.
 """
 from __future__ import annotations
 
@@ -32,9 +36,16 @@ class PreNormBlock:
             p.bind(tensors)
 
     def forward(self, x, pending, ctx, cache):
-        xn = self.mixer_norm.forward(x, pending)
-        mixed = self.mixer.forward(xn, ctx, cache)
-        xn = self.ff_norm.forward(x, mixed)
+        fused = getattr(self.mixer, "forward_residual", None)
+        if pending is None and fused is not None and fused(x, self.mixer_norm, ctx, cache):
+            pending = None
+        else:
+            xn = self.mixer_norm.forward(x, pending)
+            pending = self.mixer.forward(xn, ctx, cache)
+        fused = getattr(self.feed_forward, "forward_residual", None)
+        if pending is None and fused is not None and fused(x, self.ff_norm, ctx):
+            return None
+        xn = self.ff_norm.forward(x, pending)
         return self.feed_forward.forward(xn, ctx)
 
 

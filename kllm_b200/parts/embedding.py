@@ -54,6 +54,14 @@ class LinearHead:
     def forward(self, xn):
         return kernels.linear(xn, self.weight, out_dtype=torch.float32)
 
+    def forward_normed(self, x, norm, rows):
+        """Logits of rows ``rows`` of the float32 residual stream with ``norm`` applied
+        inside the product, or None when that route does not fit."""
+        n = rows.numel()
+        if not (getattr(norm, "fusable_rmsnorm", False) and kernels.skinny_fits(n, self.width, self.weight.dtype)):
+            return None
+        return kernels.skinny_gemm(self.weight, x_f32=x, gain=norm.gain, eps=norm.eps, rows=rows, epilogue="f32")
+
 
 register_part("embedding", "token_embedding", TokenEmbedding)
 register_part("head", "linear_head", LinearHead)

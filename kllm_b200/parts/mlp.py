@@ -5,8 +5,14 @@ params: ``hidden``, ``intermediate``, ``activation`` ("silu").  Tensors:
 no bias (reference backend/model.cu:1112-1115, activation :477-483).  Gate and up
 are stacked into one [2f, d] matrix at bind time so both are one product.
 
-Interface of a feed-forward part: ``forward(xn, ctx) -> [n, hidden]`` in the model
-dtype.
+Optional ``forward_residual(x, norm, ctx) -> bool``: as for mixers, the part reads
+the float32 residual stream, applies ``norm`` inside its first kernel and adds its
+result into x, or returns False.  Here, for steps of a few tokens, the gate/up
+product carries the norm as prologue and the activation as epilogue, the down
+product adds into x (csrc/skinny_gemm.cu).
+
+Interface of a feed-forward part: ``forward(xn, ctx) -> [n, hidden]`` in float32 or
+the model dtype.
 """
 from __future__ import annotations
 
@@ -40,10 +46,23 @@ class GatedMLP:
         self.w_down = tensors[f"{self.prefix}.down_proj.weight"]
 
     def forward(self, xn, ctx):
-        gu = kernels.linear(xn, self.w_gate_up)
+        # gate and up stay float32 until the activation has been applied; the down
+        # projection's float32 result goes into the residual stream unrounded
+        gu = kernels.linear(xn, self.w_gate_up, out_dtype=torch.float32)
         act = torch.empty((xn.shape[0], self.inter), dtype=self.dtype, device=xn.device)
         kernels.silu_mul(act, gu[:, :self.inter], gu[:, self.inter:])
-        return kernels.linear(act, self.w_down)
+        return kernels.linear(act, self.w_down, out_dtype=torch.float32)
+
+
+    def forward_residual(self, x, norm, ctx):
+        n = x.shape[0]
+        if not (getattr(norm, "fusable_rmsnorm", False) and kernels.skinny_fits(n, self.hidden, self.dtype)
+                and kernels.skinny_fits(n, self.inter, self.dtype)):
+            return False
+        act = kernels.skinny_gemm(self.w_gate_up[:self.inter], weight_up=self.w_gate_up[self.inter:], x_f32=x,
+                                  gain=norm.gain, eps=norm.eps, epilogue="swiglu")
+        kernels.skinny_gemm(self.w_down, x=act, epilogue="add", out=x)
+        return True
 
 
 register_part("feed_forward", "gated_mlp", GatedMLP)

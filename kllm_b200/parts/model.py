@@ -93,5 +93,9 @@ class DecoderModel:
             pending = self.blocks[call.block].forward(x, pending, ctx, cache)
         if ctx.n_want == 0:
             return None
+        if pending is None and hasattr(self.head, "forward_normed"):
+            logits = self.head.forward_normed(x, self.final_norm, ctx.want_rows)
+            if logits is not None:
+                return logits
         xn = self.final_norm.forward(x, pending, rows=ctx.want_rows)
         return self.head.forward(xn)

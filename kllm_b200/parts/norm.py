@@ -4,9 +4,13 @@ params: ``width``, ``eps``.  Tensor: ``<prefix>.weight`` [width], kept in float3
 (reference backend/model.cu:101-122, 144-165; the gain is used as stored, no 1 + w).
 Interface of a norm part:
 ``forward(x, res, rows=None) -> out``: x is the float32 residual stream [n, width];
-``res`` (model dtype, or None) is added into x first and x is written back; the
+``res`` (float32 or model dtype, or None) is added into x first and x is written back; the
 result is in the model dtype.  With ``rows`` only those rows are normalised and x
 is left as it is.
+
+A part that can apply this norm inside its own kernel (see ``forward_residual`` of
+the attention and feed-forward parts) recognises it by ``fusable_rmsnorm`` and
+reads ``gain`` and ``eps``.
 """
 from __future__ import annotations
 
@@ -17,6 +21,8 @@ from .spec import BuildEnv, PartSpec, TensorSpec, register_part
 
 
 class RMSNorm:
+    fusable_rmsnorm = True
+
     def __init__(self, spec: PartSpec, env: BuildEnv):
         self.width = int(spec.params["width"])
         self.eps = float(spec.params["eps"])

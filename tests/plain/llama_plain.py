@@ -95,9 +95,9 @@ def swiglu(x, w_gate, w_up, w_down, rnd=None):
     """down( silu(x Wg^T) * (x Wu^T) ) (backend/model.cu:1112-1115)."""
     rnd = rnd or (lambda a: a)
     x = f64(x)
-    g = rnd(x @ f64(w_gate).T)
-    u = rnd(x @ f64(w_up).T)
-    return rnd(rnd(silu(g) * u) @ f64(w_down).T)
+    g = x @ f64(w_gate).T              # gate, up and the result are float32 in the
+    u = x @ f64(w_up).T                # engine; only the activation's output is stored
+    return rnd(silu(g) * u) @ f64(w_down).T
 
 
 def _same(a):
@@ -116,7 +116,7 @@ def attention_block(x, w, prefix, cfg, positions, rnd=_same):
     k = rnd(rope(k, positions, nkv, hd, cfg["rope_theta"]))
     a = rnd(attention(q, k, v, nh, nkv, hd, window=cfg.get("sliding_window"),
                       rnd_p=None if rnd is _same else rnd))
-    return rnd(a @ f64(w[prefix + ".self_attn.o_proj.weight"]).T)
+    return a @ f64(w[prefix + ".self_attn.o_proj.weight"]).T     # float32 into the residual stream
 
 
 def decoder_layer(x, w, layer, cfg, positions, rnd=_same):

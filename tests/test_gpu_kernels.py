@@ -357,6 +357,48 @@ def test_linear_is_true_float32_and_bf16_accumulates_in_float32():
     assert yb.dtype == torch.float32 and np.abs(yb.cpu().numpy() - wb).max() < 2e-3
 
 
+@pytest.mark.parametrize("n", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(48, 64), (2560, 2048), (100, 96), (2048, 5632), (33, 4096)])
+def test_skinny_gemm_prologues_and_epilogues(n, N, K):
+    from kllm_b200 import kernels
+    rng = np.random.default_rng(n * 1000 + N)
+    w = (rng.standard_normal((N, K)) * 0.05).astype(np.float32)
+    w2 = (rng.standard_normal((N, K)) * 0.05).astype(np.float32)
+    x = rng.standard_normal((n, K)).astype(np.float32)
+    ws, w2s, xs = as_stored(w, "bfloat16"), as_stored(w2, "bfloat16"), as_stored(x, "bfloat16")
+    wt, w2t, xt = dev(w, torch.bfloat16), dev(w2, torch.bfloat16), dev(x, torch.bfloat16)
+    want = xs @ ws.T
+    close(kernels.skinny_gemm(wt, x=xt, epilogue="bf16"), want, "bfloat16", "bf16 store")
+    close(kernels.skinny_gemm(wt, x=xt, epilogue="f32"), want, "float32", "f32 store")
+    base = rng.standard_normal((n, N)).astype(np.float32)
+    acc = dev(base)
+    kernels.skinny_gemm(wt, x=xt, epilogue="add", out=acc)
+    close(acc, base.astype(np.float64) + want, "float32", "residual add")
+    g, u = xs @ ws.T, xs @ w2s.T
+    close(kernels.skinny_gemm(wt, x=xt, weight_up=w2t, epilogue="swiglu"), plain.silu(g) * u, "bfloat16", "swiglu")
+    # norm prologue, on gathered rows of a larger float32 matrix
+    big = (rng.standard_normal((n + 5, K)) * 2).astype(np.float32)
+    gain = (1 + 0.2 * rng.standard_normal(K)).astype(np.float32)
+    rows = rng.permutation(n + 5)[:n].astype(np.int32)
+    xn = plain.round_act_bf16(plain.rmsnorm(big[rows], gain, 1e-5))
+    got = kernels.skinny_gemm(wt, x_f32=dev(big), gain=dev(gain), eps=1e-5, rows=dev(rows), epilogue="f32")
+    close(got, xn @ ws.T, "bfloat16", "norm prologue (a rounding of xn may flip)")
+    got = kernels.skinny_gemm(wt, x_f32=dev(big[:n].copy()), gain=dev(gain), eps=1e-5, epilogue="bf16")
+    close(got, plain.round_act_bf16(plain.rmsnorm(big[:n], gain, 1e-5)) @ ws.T, "bfloat16", "norm prologue, no gather")
+
+
+def test_skinny_gemm_refusals():
+    from kllm_b200 import kernels
+    w = torch.zeros(16, 40, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(kernels.KernelError, match="not supported"):
+        kernels.skinny_gemm(w, x=torch.zeros(2, 40, device="cuda", dtype=torch.bfloat16))
+    w = torch.zeros(16, 64, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(kernels.KernelError, match="not supported"):
+        kernels.skinny_gemm(w, x=torch.zeros(17, 64, device="cuda", dtype=torch.bfloat16))
+    assert not kernels.skinny_fits(8, 64, torch.float32) and kernels.skinny_fits(16, 5632, torch.bfloat16)
+    assert not kernels.skinny_fits(16, 14336, torch.bfloat16)
+
+
 def test_kernels_refuse_what_they_cannot_take():
     from kllm_b200 import kernels
     x = torch.zeros(2, 8)
