@@ -13,6 +13,8 @@ template <typename T, typename I>
 __global__ void silu_mul_kernel(T* __restrict__ out, int64_t out_stride,
                                 const I* __restrict__ gate, int64_t gate_stride,
                                 const I* __restrict__ up, int64_t up_stride, int n, int f) {
+    griddep_wait();
+    griddep_launch();
     const int64_t total = (int64_t)n * f;
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (int64_t)gridDim.x * blockDim.x) {
@@ -36,13 +38,13 @@ extern "C" int kllm_silu_mul(void* out, int64_t out_stride, const void* gate, in
     int64_t blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (dtype == KLLM_F32 && in_dtype == KLLM_F32)
-        silu_mul_kernel<float, float><<<(unsigned)blocks, 256, 0, s>>>(
+        kllm_launch((silu_mul_kernel<float, float>), dim3((unsigned)blocks), dim3(256), 0, s, 
             (float*)out, out_stride, (const float*)gate, gate_stride, (const float*)up, up_stride, n, f);
     else if (dtype == KLLM_BF16 && in_dtype == KLLM_BF16)
-        silu_mul_kernel<bf16, bf16><<<(unsigned)blocks, 256, 0, s>>>(
+        kllm_launch((silu_mul_kernel<bf16, bf16>), dim3((unsigned)blocks), dim3(256), 0, s, 
             (bf16*)out, out_stride, (const bf16*)gate, gate_stride, (const bf16*)up, up_stride, n, f);
     else if (dtype == KLLM_BF16 && in_dtype == KLLM_F32)
-        silu_mul_kernel<bf16, float><<<(unsigned)blocks, 256, 0, s>>>(
+        kllm_launch((silu_mul_kernel<bf16, float>), dim3((unsigned)blocks), dim3(256), 0, s, 
             (bf16*)out, out_stride, (const float*)gate, gate_stride, (const float*)up, up_stride, n, f);
     else
         KLLM_FAIL("silu_mul: element types %d (out) and %d (in) are not supported together", dtype, in_dtype);

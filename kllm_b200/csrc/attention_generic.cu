@@ -30,6 +30,8 @@ attn_generic_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_stri
                     const int* __restrict__ block_table, int max_blocks, int n_tokens,
                     int n_heads, int n_kv, int hd, int page_size, int window, float scale) {
     __shared__ float qs[kWarps][kMaxHd];
+    griddep_wait();
+    griddep_launch();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t item = (int64_t)blockIdx.x * kWarps + warp;
     if (item >= (int64_t)n_tokens * n_heads) return;
@@ -109,12 +111,12 @@ extern "C" int kllm_attention_generic(void* out, const void* q, int64_t q_stride
     const int64_t items = (int64_t)n_tokens * n_heads;
     const unsigned grid = (unsigned)((items + kWarps - 1) / kWarps);
     if (dtype == KLLM_F32)
-        attn_generic_kernel<float><<<grid, kWarps * 32, 0, s>>>(
+        kllm_launch((attn_generic_kernel<float>), dim3(grid), dim3(kWarps * 32), 0, s, 
             (float*)out, (const float*)q, q_stride, (const float*)kcache, (const float*)vcache,
             positions, token_req, block_table, max_blocks, n_tokens, n_heads, n_kv, hd, page_size,
             window, scale);
     else if (dtype == KLLM_BF16)
-        attn_generic_kernel<bf16><<<grid, kWarps * 32, 0, s>>>(
+        kllm_launch((attn_generic_kernel<bf16>), dim3(grid), dim3(kWarps * 32), 0, s, 
             (bf16*)out, (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache,
             positions, token_req, block_table, max_blocks, n_tokens, n_heads, n_kv, hd, page_size,
             window, scale);

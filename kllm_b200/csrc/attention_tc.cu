@@ -12,6 +12,13 @@
 //    running (max, sum, output) of their own, merged once at the end in a fixed
 //    order.  With more than one split the CTA writes an unnormalised partial
 //    result and `attn_combine_kernel` merges the splits, again in a fixed order.
+//    The fused form of this kernel (`kllm_attention_decode_fused`) also does the
+//    step's rotary encoding and cache write: every CTA rotates its copy of the
+//    query in registers, the CTA whose key range ends at the token itself rotates
+//    the new key and stores it and the new value into the page before it loads
+//    that tile, and the last CTA of a (token, kv head) to finish merges the splits
+//    (it is found with one atomic counter; the merge itself runs in split order,
+//    so the result does not depend on who is last).  One launch replaces three.
 //
 //  * prefill: a CTA takes up to 64 rows = (tokens of one request's portion) x
 //    (heads of one group), each warp 16 of them, and walks the keys from the first
@@ -20,7 +27,7 @@
 //    CTA finds its request from the prefix sums of the portions' lengths.
 //
 // Keys and values reach shared memory through cp.async (16-byte pieces, three
-// stages), rows padded by 16 bytes so that ldmatrix is free of bank conflicts for
+// to five stages), rows padded by 16 bytes so that ldmatrix is free of bank conflicts for
 // every head size.  Scores, the running maximum, the sum and the output are
 // float32; probabilities are rounded to bfloat16 for the second product only.
 // Slots of a page beyond a request's length are never read: rows past the last
@@ -45,10 +52,16 @@ constexpr int DTILES = HD / 8;           // 8-wide output tiles over the head di
 constexpr int CHUNKS = HD / 8;           // 16-byte pieces of a key row
 constexpr int TILE = 64;                 // keys per shared-memory tile
 constexpr int ROW = HD + 8;              // padded row, in elements (16 bytes of padding)
-constexpr int STAGES = 3;
 constexpr int THREADS = 128;
 constexpr int STAGE_ELEMS = 2 * TILE * ROW;                       // K tile then V tile
-constexpr int SMEM_BYTES = STAGES * STAGE_ELEMS * 2;
+// Decode CTAs are few and each walks a short key range: the deeper the pipeline,
+// the more of the range is in flight at once (with 5 stages a range of 256 keys is
+// requested whole before the first tile is used).  Prefill keeps 3 stages and more
+// CTAs per SM.
+constexpr int DEC_STAGES = HD <= 64 ? 5 : (HD <= 96 ? 4 : 3);
+constexpr int PRE_STAGES = 3;
+constexpr int DEC_SMEM_BYTES = DEC_STAGES * STAGE_ELEMS * 2;
+constexpr int PRE_SMEM_BYTES = PRE_STAGES * STAGE_ELEMS * 2;
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -136,14 +149,34 @@ __device__ __forceinline__ void accumulate16(float (&o)[DTILES][4], const uint32
 
 // ---- decode -------------------------------------------------------------------
 
+// What the fused form needs beside the plain one: this step's k and v rows, the
+// cos/sin table of a full-width rotary encoding [max_position, HD], and one counter
+// per (token, kv head), zero before the first launch and zero again after each.
+struct DecodeFusion {
+    const bf16* k_new;
+    int64_t k_stride;
+    const bf16* v_new;
+    int64_t v_stride;
+    const float* cos_sin;
+    unsigned int* counters;
+};
+
+template <bool FUSED>
 __global__ void __launch_bounds__(THREADS)
 attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
-                   const bf16* __restrict__ q, int64_t q_stride, const bf16* __restrict__ kcache,
-                   const bf16* __restrict__ vcache, const int* __restrict__ positions,
+                   const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__ kcache,
+                   bf16* __restrict__ vcache, const int* __restrict__ positions,
                    const int* __restrict__ token_req, const int* __restrict__ block_table, int max_blocks,
-                   int n_heads, int n_kv, int page_size, int window, float scale_log2e, int num_splits) {
+                   int n_heads, int n_kv, int page_size, int window, float scale_log2e, int num_splits,
+                   const DecodeFusion fu) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
+    __shared__ int s_is_last;
+    __shared__ bf16 s_newkv[2 * HD];       // the writer CTA's rotated new key, then the new value
+    // Plain form: the kernel before this one wrote this step's keys into the pages.
+    // Fused form: nobody but this kernel writes this layer's pages, so their tiles may
+    // be requested while the projection kernel before it is still finishing.
+    if (!FUSED) { griddep_wait(); griddep_launch(); }
     const int split = blockIdx.x, g = blockIdx.y, t = blockIdx.z;
     const int gs = n_heads / n_kv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tq = lane & 3;
@@ -155,6 +188,14 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
     const int hi = min(len, lo + chunk);
     const int* table = block_table + (int64_t)token_req[t] * max_blocks;
     const int ntiles = lo < hi ? (hi - lo + TILE - 1) / TILE : 0;
+
+    // the tiles do not depend on the query: start them first
+#pragma unroll
+    for (int s = 0; s < DEC_STAGES - 1; s++) {
+        if (s < ntiles) load_tile(smem + s * STAGE_ELEMS, kcache, vcache, table, lo + s * TILE, hi, g, n_kv, page_size);
+        cp_async_commit();
+    }
+    if (FUSED) { griddep_wait(); griddep_launch(); }
 
     uint32_t qa[KSTEPS][4];
     {
@@ -169,6 +210,47 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
             qa[ks][3] = v1 ? *reinterpret_cast<const uint32_t*>(qb + (gid + 8) * HD + c + 8) : 0u;
         }
     }
+    // The CTA whose range holds the token's own position owns the new key and value:
+    // it stores them into the page for later steps and, instead of reading them back,
+    // writes them over their row of the shared-memory tile once that tile has landed.
+    const int p_new = len - 1;
+    const bool writer = FUSED && lo <= p_new && p_new < hi;
+    if (FUSED) {
+        // rotate_half on the query fragments: dims d and d + HD/2 sit in the same
+        // register slot of k-steps ks and ks + KSTEPS/2 (rotation in float32, stored
+        // as bfloat16 like the separate kernel does; reference backend/model.cu:170-184)
+        const float* cs = fu.cos_sin + (int64_t)p_new * HD;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS / 2; ks++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int j = ks * 16 + 2 * tq + (i >= 2 ? 8 : 0);
+                const float c0 = cs[j], c1 = cs[j + 1], s0 = cs[HD / 2 + j], s1 = cs[HD / 2 + j + 1];
+                const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&qa[ks][i]);
+                const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&qa[ks + KSTEPS / 2][i]);
+                const float a0 = __low2float(a), a1 = __high2float(a), b0 = __low2float(b), b1 = __high2float(b);
+                qa[ks][i] = pack_bf16(a0 * c0 - b0 * s0, a1 * c1 - b1 * s1);
+                qa[ks + KSTEPS / 2][i] = pack_bf16(b0 * c0 + a0 * s0, b1 * c1 + a1 * s1);
+            }
+        if (writer) {
+            const int lp = p_new / page_size;
+            const int64_t dst = (((int64_t)table[lp] * n_kv + g) * page_size + (p_new - lp * page_size)) * HD;
+            const bf16* kr = fu.k_new + (int64_t)t * fu.k_stride + (int64_t)g * HD;
+            const bf16* vr = fu.v_new + (int64_t)t * fu.v_stride + (int64_t)g * HD;
+            for (int j = threadIdx.x; j < HD / 2; j += THREADS) {
+                const float c = cs[j], sn = cs[HD / 2 + j];
+                const float a = __bfloat162float(kr[j]), b = __bfloat162float(kr[j + HD / 2]);
+                const bf16 k0 = __float2bfloat16_rn(a * c - b * sn), k1 = __float2bfloat16_rn(b * c + a * sn);
+                kcache[dst + j] = k0; kcache[dst + j + HD / 2] = k1;
+                s_newkv[j] = k0; s_newkv[j + HD / 2] = k1;
+            }
+            for (int j = threadIdx.x; j < HD; j += THREADS) {
+                const bf16 vv = vr[j];
+                vcache[dst + j] = vv;
+                s_newkv[HD + j] = vv;
+            }
+        }
+    }
     float o[DTILES][4];
 #pragma unroll
     for (int i = 0; i < DTILES; i++)
@@ -176,20 +258,23 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
         for (int j = 0; j < 4; j++) o[i][j] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-#pragma unroll
-    for (int s = 0; s < STAGES - 1; s++) {
-        if (s < ntiles) load_tile(smem + s * STAGE_ELEMS, kcache, vcache, table, lo + s * TILE, hi, g, n_kv, page_size);
-        cp_async_commit();
-    }
     for (int i = 0; i < ntiles; i++) {
-        cp_async_wait<STAGES - 2>();
+        cp_async_wait<DEC_STAGES - 2>();
         __syncthreads();
-        const int nxt = i + STAGES - 1;
+        const int nxt = i + DEC_STAGES - 1;
         if (nxt < ntiles)
-            load_tile(smem + (nxt % STAGES) * STAGE_ELEMS, kcache, vcache, table, lo + nxt * TILE, hi, g, n_kv, page_size);
+            load_tile(smem + (nxt % DEC_STAGES) * STAGE_ELEMS, kcache, vcache, table, lo + nxt * TILE, hi, g, n_kv, page_size);
         cp_async_commit();
-        const bf16* sk = smem + (i % STAGES) * STAGE_ELEMS;
-        const bf16* sv = sk + TILE * ROW;
+        bf16* sk = smem + (i % DEC_STAGES) * STAGE_ELEMS;
+        bf16* sv = sk + TILE * ROW;
+        if (writer && i == ntiles - 1) {       // the token's own row: whatever the page held there is replaced
+            const int row = p_new - (lo + i * TILE);
+            for (int j = threadIdx.x; j < HD; j += THREADS) {
+                sk[row * ROW + j] = s_newkv[j];
+                sv[row * ROW + j] = s_newkv[HD + j];
+            }
+            __syncthreads();
+        }
         const int key_base = lo + i * TILE + 16 * warp;
         if (key_base < hi) {
             float s[2][4];
@@ -267,11 +352,42 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
             if (d == 0) { part_ml[slot * 2] = M * scale_log2e; part_ml[slot * 2 + 1] = L; }
         }
     }
+    if (FUSED && num_splits > 1) {
+        // the last CTA of this (token, kv head) to get here merges all splits
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const unsigned int prev = atomicAdd(fu.counters + (int64_t)t * n_kv + g, 1u);
+            s_is_last = (prev == (unsigned int)num_splits - 1u);
+            if (s_is_last) fu.counters[(int64_t)t * n_kv + g] = 0u;      // ready for the next launch
+        }
+        __syncthreads();
+        if (!s_is_last) return;
+        __threadfence();
+        for (int e = threadIdx.x; e < gs * HD; e += THREADS) {
+            const int r = e / HD, d = e - r * HD;
+            const int64_t th = (int64_t)t * n_heads + g * gs + r;
+            const float* ml = part_ml + th * num_splits * 2;
+            float M = -INFINITY;
+#pragma unroll 4
+            for (int j = 0; j < num_splits; j++) M = fmaxf(M, __ldcg(ml + 2 * j));
+            float L = 0.f, O = 0.f;
+#pragma unroll 4
+            for (int j = 0; j < num_splits; j++) {
+                const float f = exp2f(__ldcg(ml + 2 * j) - M);
+                L += __ldcg(ml + 2 * j + 1) * f;
+                O += __ldcg(part_o + (th * num_splits + j) * HD + d) * f;
+            }
+            out[th * HD + d] = __float2bfloat16_rn(O / L);
+        }
+    }
 }
 
 // Merge the splits of the decode kernel, in split order: one block per (token, head).
 __global__ void attn_combine_kernel(bf16* __restrict__ out, const float* __restrict__ part_o,
                                     const float* __restrict__ part_ml, int num_splits) {
+    griddep_wait();
+    griddep_launch();
     const int64_t th = blockIdx.x;
     const float* ml = part_ml + th * num_splits * 2;
     float M = -INFINITY;
@@ -297,6 +413,8 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t 
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
     __shared__ int s_req, s_tok0;
+    griddep_wait();
+    griddep_launch();
     const int g = blockIdx.y;
     const int gs = n_heads / n_kv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tq = lane & 3;
@@ -355,18 +473,18 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t 
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
 #pragma unroll
-    for (int s = 0; s < STAGES - 1; s++) {
+    for (int s = 0; s < PRE_STAGES - 1; s++) {
         if (s < ntiles) load_tile(smem + s * STAGE_ELEMS, kcache, vcache, table, lo + s * TILE, hi, g, n_kv, page_size);
         cp_async_commit();
     }
     for (int i = 0; i < ntiles; i++) {
-        cp_async_wait<STAGES - 2>();
+        cp_async_wait<PRE_STAGES - 2>();
         __syncthreads();
-        const int nxt = i + STAGES - 1;
+        const int nxt = i + PRE_STAGES - 1;
         if (nxt < ntiles)
-            load_tile(smem + (nxt % STAGES) * STAGE_ELEMS, kcache, vcache, table, lo + nxt * TILE, hi, g, n_kv, page_size);
+            load_tile(smem + (nxt % PRE_STAGES) * STAGE_ELEMS, kcache, vcache, table, lo + nxt * TILE, hi, g, n_kv, page_size);
         cp_async_commit();
-        const bf16* sk = smem + (i % STAGES) * STAGE_ELEMS;
+        const bf16* sk = smem + (i % PRE_STAGES) * STAGE_ELEMS;
         const bf16* sv = sk + TILE * ROW;
         const int key0 = lo + i * TILE;
         if (!warp_active || key0 >= warp_hi) continue;             // nothing of this tile is visible to the warp
@@ -447,11 +565,13 @@ bool g_attr_set = false;
 
 int set_attributes() {
     if (g_attr_set) return 0;
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM_BYTES);
     if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        e = cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM_BYTES);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PRE_SMEM_BYTES);
     if (e != cudaSuccess) {
-        snprintf(g_kllm_err, sizeof(g_kllm_err), "attention: cannot get %d bytes of shared memory: %s", SMEM_BYTES,
+        snprintf(g_kllm_err, sizeof(g_kllm_err), "attention: cannot get %d bytes of shared memory: %s", DEC_SMEM_BYTES,
                  cudaGetErrorString(e));
         return (int)e;
     }
@@ -489,13 +609,43 @@ extern "C" int kllm_attention_decode(void* out, void* part_o, void* part_ml, con
     cudaStream_t s = (cudaStream_t)stream;
     const float sl2e = scale * 1.4426950408889634f;
     dim3 grid(num_splits, n_kv, n_tokens);
-    attn_decode_kernel<<<grid, THREADS, SMEM_BYTES, s>>>(
-        (bf16*)out, (float*)part_o, (float*)part_ml, (const bf16*)q, q_stride, (const bf16*)kcache,
-        (const bf16*)vcache, positions, token_req, block_table, max_blocks, n_heads, n_kv, page_size, window, sl2e,
-        num_splits);
+    kllm_launch((attn_decode_kernel<false>), dim3(grid), dim3(THREADS), DEC_SMEM_BYTES, s, 
+        (bf16*)out, (float*)part_o, (float*)part_ml, (const bf16*)q, q_stride, (bf16*)kcache,
+        (bf16*)vcache, positions, token_req, block_table, max_blocks, n_heads, n_kv, page_size, window, sl2e,
+        num_splits, DecodeFusion{});
     if (num_splits > 1)
-        attn_combine_kernel<<<n_tokens * n_heads, HD < 64 ? 32 : 64, 0, s>>>((bf16*)out, (const float*)part_o,
+        kllm_launch((attn_combine_kernel), dim3(n_tokens * n_heads), dim3(HD < 64 ? 32 : 64), 0, s, (bf16*)out, (const float*)part_o,
                                                                           (const float*)part_ml, num_splits);
+    KLLM_LAUNCH_STATUS();
+}
+
+// Decode form with the step's rotary encoding, cache write and split merge inside
+// (one token per request).  q [n, n_heads*HD], k_new and v_new [n, n_kv*HD] are this
+// step's projections, unrotated; cos_sin [max_position, HD] (cos | sin); counters
+// [n_tokens * n_kv] unsigned, all zero (the kernel leaves them zero).
+extern "C" int kllm_attention_decode_fused(void* out, void* part_o, void* part_ml, void* counters, const void* q,
+                                           int64_t q_stride, const void* k_new, int64_t k_stride,
+                                           const void* v_new, int64_t v_stride, const float* cos_sin,
+                                           void* kcache, void* vcache, const int* positions,
+                                           const int* token_req, const int* block_table, int max_blocks,
+                                           int n_tokens, int n_heads, int n_kv, int hd, int page_size, int window,
+                                           float scale, int num_splits, void* stream) {
+    if (n_tokens <= 0) return 0;
+    int rc = check_common(n_heads, n_kv, hd, page_size, q, q_stride);
+    if (rc) return rc;
+    if (KSTEPS % 2) KLLM_FAIL("attention decode (fused): head size %d is not a multiple of 32", HD);
+    if (n_heads / n_kv > 16) KLLM_FAIL("attention decode: %d heads per kv head, at most 16", n_heads / n_kv);
+    if (num_splits < 1 || (num_splits > 1 && (!part_o || !part_ml || !counters)))
+        KLLM_FAIL("attention decode (fused): bad split arguments");
+    if (!k_new || !v_new || !cos_sin) KLLM_FAIL("attention decode (fused): k, v and the cos/sin table are needed");
+    if (n_tokens > 65535 || n_kv > 65535) KLLM_FAIL("attention decode: grid too large");
+    if ((rc = set_attributes())) return rc;
+    const float sl2e = scale * 1.4426950408889634f;
+    DecodeFusion fu{(const bf16*)k_new, k_stride, (const bf16*)v_new, v_stride, cos_sin, (unsigned int*)counters};
+    dim3 grid(num_splits, n_kv, n_tokens);
+    kllm_launch((attn_decode_kernel<true>), dim3(grid), dim3(THREADS), DEC_SMEM_BYTES, (cudaStream_t)stream, 
+        (bf16*)out, (float*)part_o, (float*)part_ml, (const bf16*)q, q_stride, (bf16*)kcache, (bf16*)vcache,
+        positions, token_req, block_table, max_blocks, n_heads, n_kv, page_size, window, sl2e, num_splits, fu);
     KLLM_LAUNCH_STATUS();
 }
 
@@ -569,7 +719,7 @@ extern "C" int kllm_attention_prefill(void* out, const void* q, int64_t q_stride
     if (n_kv > 65535) KLLM_FAIL("attention prefill: grid too large");
     const float sl2e = scale * 1.4426950408889634f;
     dim3 grid(max_tiles, n_kv);
-    attn_prefill_kernel<<<grid, THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(
+    kllm_launch((attn_prefill_kernel), dim3(grid), dim3(THREADS), PRE_SMEM_BYTES, (cudaStream_t)stream, 
         (bf16*)out, (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache, q_start, start_pos,
         block_table, max_blocks, n_requests, n_heads, n_kv, page_size, window, sl2e, tpt);
     KLLM_LAUNCH_STATUS();

@@ -10,6 +10,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #define KLLM_F32 0
 #define KLLM_BF16 1
@@ -37,6 +38,44 @@ static thread_local char g_kllm_err[512];
 
 #define KLLM_EXPORT_LAST_ERROR(libname)                                 \
     extern "C" const char* kllm_last_error_##libname() { return g_kllm_err; }
+
+// ---- programmatic dependent launch ------------------------------------------
+// Kernels of one step form a chain in which each reads what the one before wrote.
+// Launched with the "programmatic stream serialization" attribute, a kernel may be
+// scheduled while its predecessor is still running; it calls griddep_wait() before
+// its first access to anything a predecessor may write, and griddep_launch() once
+// its successor may start to be scheduled.  What a kernel does before the wait
+// (address arithmetic, prefetching weights or cache pages that no kernel of the
+// chain writes) overlaps the predecessor's tail and the launch latency.  Without
+// the attribute both calls do nothing.  KLLM_B200_PDL=0 in the environment turns
+// the attribute off.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static inline bool kllm_pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("KLLM_B200_PDL");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t kllm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                      cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = kllm_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 typedef __nv_bfloat16 bf16;
 

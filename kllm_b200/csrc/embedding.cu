@@ -14,6 +14,8 @@ namespace {
 template <typename T>
 __global__ void embed_kernel(float* __restrict__ x, const T* __restrict__ table,
                              const int* __restrict__ ids, int d, int vocab) {
+    griddep_wait();
+    griddep_launch();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* xr = x + (int64_t)t * d;
@@ -29,6 +31,8 @@ __global__ void embed_kernel(float* __restrict__ x, const T* __restrict__ table,
 // (role of gather_rows_kernel, reference backend/model.cu:411-417).
 __global__ void gather_rows_kernel(char* __restrict__ out, const char* __restrict__ in,
                                    const int* __restrict__ rows, int64_t row_bytes) {
+    griddep_wait();
+    griddep_launch();
     const int r = blockIdx.x;
     const char* src = in + (int64_t)rows[r] * row_bytes;
     char* dst = out + (int64_t)r * row_bytes;
@@ -49,9 +53,9 @@ extern "C" int kllm_embed(void* x, const void* table, const int* ids, int n, int
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = d >= 1024 ? 256 : 128;
     if (dtype == KLLM_F32)
-        embed_kernel<float><<<n, threads, 0, s>>>((float*)x, (const float*)table, ids, d, vocab);
+        kllm_launch((embed_kernel<float>), dim3(n), dim3(threads), 0, s, (float*)x, (const float*)table, ids, d, vocab);
     else if (dtype == KLLM_BF16)
-        embed_kernel<bf16><<<n, threads, 0, s>>>((float*)x, (const bf16*)table, ids, d, vocab);
+        kllm_launch((embed_kernel<bf16>), dim3(n), dim3(threads), 0, s, (float*)x, (const bf16*)table, ids, d, vocab);
     else
         KLLM_FAIL("embed: unknown element type %d", dtype);
     KLLM_LAUNCH_STATUS();
@@ -60,7 +64,7 @@ extern "C" int kllm_embed(void* x, const void* table, const int* ids, int n, int
 extern "C" int kllm_gather_rows(void* out, const void* in, const int* rows, int n_rows,
                                 int64_t row_bytes, void* stream) {
     if (n_rows <= 0) return 0;
-    gather_rows_kernel<<<n_rows, 256, 0, (cudaStream_t)stream>>>((char*)out, (const char*)in, rows,
+    kllm_launch((gather_rows_kernel), dim3(n_rows), dim3(256), 0, (cudaStream_t)stream, (char*)out, (const char*)in, rows,
                                                                  row_bytes);
     KLLM_LAUNCH_STATUS();
 }

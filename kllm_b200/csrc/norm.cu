@@ -25,6 +25,8 @@ add_rmsnorm_kernel(float* __restrict__ x, const R* __restrict__ res, T* __restri
                    const float* __restrict__ gain, const int* __restrict__ rows,
                    int d, float eps) {
     __shared__ float red[32];
+    griddep_wait();
+    griddep_launch();
     const int r = blockIdx.x;
     const int64_t src = rows ? (int64_t)rows[r] : (int64_t)r;
     float* xr = x + src * d;
@@ -61,13 +63,13 @@ extern "C" int kllm_add_rmsnorm(void* x, const void* res, void* out, const void*
     cudaStream_t s = (cudaStream_t)stream;
     if (res == nullptr) res_dtype = dtype;
     if (dtype == KLLM_F32 && res_dtype == KLLM_F32) {
-        add_rmsnorm_kernel<float, float><<<n_rows, kThreads, 0, s>>>(
+        kllm_launch((add_rmsnorm_kernel<float, float>), dim3(n_rows), dim3(kThreads), 0, s, 
             (float*)x, (const float*)res, (float*)out, (const float*)gain, rows, d, eps);
     } else if (dtype == KLLM_BF16 && res_dtype == KLLM_BF16) {
-        add_rmsnorm_kernel<bf16, bf16><<<n_rows, kThreads, 0, s>>>(
+        kllm_launch((add_rmsnorm_kernel<bf16, bf16>), dim3(n_rows), dim3(kThreads), 0, s, 
             (float*)x, (const bf16*)res, (bf16*)out, (const float*)gain, rows, d, eps);
     } else if (dtype == KLLM_BF16 && res_dtype == KLLM_F32) {
-        add_rmsnorm_kernel<bf16, float><<<n_rows, kThreads, 0, s>>>(
+        kllm_launch((add_rmsnorm_kernel<bf16, float>), dim3(n_rows), dim3(kThreads), 0, s, 
             (float*)x, (const float*)res, (bf16*)out, (const float*)gain, rows, d, eps);
     } else {
         KLLM_FAIL("rmsnorm: element types %d (out) and %d (res) are not supported together", dtype, res_dtype);

@@ -25,6 +25,8 @@ __global__ void rope_append_kernel(T* __restrict__ q, int64_t q_stride,
                                    const int* __restrict__ block_table, int max_blocks,
                                    T* __restrict__ kcache, T* __restrict__ vcache,
                                    int n_heads, int n_kv, int hd, int rot, int page_size) {
+    griddep_wait();
+    griddep_launch();
     const int t = blockIdx.x;
     const int p = positions[t];
     const int half = rot >> 1;
@@ -85,12 +87,12 @@ extern "C" int kllm_rope_append(void* q, int64_t q_stride, const void* k, int64_
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = 128;
     if (dtype == KLLM_F32)
-        rope_append_kernel<float><<<n_tokens, threads, 0, s>>>(
+        kllm_launch((rope_append_kernel<float>), dim3(n_tokens), dim3(threads), 0, s, 
             (float*)q, q_stride, (const float*)k, k_stride, (const float*)v, v_stride, cos_sin,
             positions, token_req, block_table, max_blocks, (float*)kcache, (float*)vcache, n_heads,
             n_kv, hd, rot, page_size);
     else if (dtype == KLLM_BF16)
-        rope_append_kernel<bf16><<<n_tokens, threads, 0, s>>>(
+        kllm_launch((rope_append_kernel<bf16>), dim3(n_tokens), dim3(threads), 0, s, 
             (bf16*)q, q_stride, (const bf16*)k, k_stride, (const bf16*)v, v_stride, cos_sin,
             positions, token_req, block_table, max_blocks, (bf16*)kcache, (bf16*)vcache, n_heads,
             n_kv, hd, rot, page_size);

@@ -24,6 +24,8 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int64_t r
     __shared__ int s_idx[kThreads];
     __shared__ float s_part[kThreads];
     __shared__ int s_choice;
+    griddep_wait();
+    griddep_launch();
     const int r = blockIdx.x, tid = threadIdx.x;
     const float* z = logits + (int64_t)r * row_stride;
     const int seg = (vocab + kThreads - 1) / kThreads;
@@ -98,7 +100,7 @@ extern "C" int kllm_sample(int* out, const float* logits, int64_t row_stride, in
     if (rows <= 0) return 0;
     if (vocab <= 0) KLLM_FAIL("sample: vocabulary %d", vocab);
     if (temperature && !uniform) KLLM_FAIL("sample: temperature given without uniform numbers");
-    sample_kernel<<<rows, kThreads, 0, (cudaStream_t)stream>>>(out, logits, row_stride, vocab,
+    kllm_launch((sample_kernel), dim3(rows), dim3(kThreads), 0, (cudaStream_t)stream, out, logits, row_stride, vocab,
                                                              temperature, uniform);
     KLLM_LAUNCH_STATUS();
 }

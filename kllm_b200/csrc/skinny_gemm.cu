@@ -20,11 +20,11 @@
 //                         (backend/model.cu:477-483, :1112-1114)
 //
 // Layout of the work: a tile is 16 weight rows (for SWIGLU 8 gate rows and the 8 up
-// rows that go with them).  A CTA of 8 warps walks tiles tile = blockIdx.x,
+// rows that go with them).  A CTA of 16 warps, one per SM, walks tiles tile = blockIdx.x,
 // += gridDim.x; inside a tile the warps take the K dimension in interleaved steps
 // of 32 elements, each lane loading 16 contiguous bytes of two weight rows per
 // step.  A lane's 8 consecutive k-values feed two MMAs; the same permutation of k
-// is applied to the activations, so the sum is unchanged.  The eight partial
+// is applied to the activations, so the sum is unchanged.  The sixteen partial
 // tiles are added in warp order through shared memory: no atomics, and every output
 // element belongs to one CTA, so ADD_F32 is race-free and the order of all sums
 // depends on K alone.
@@ -34,9 +34,10 @@ KLLM_EXPORT_LAST_ERROR(skinny_gemm)
 
 namespace {
 
-constexpr int THREADS = 256;
-constexpr int WARPS = 8;
+constexpr int THREADS = 512;       // one CTA per SM: X is prepared once per SM, all 16 warps stream weights
+constexpr int WARPS = 16;
 constexpr int UNROLL = 4;          // k-steps of 32 in flight per lane and buffer
+constexpr int NORM_F4 = 16;        // float4 a lane may hold in the one-pass norm prologue
 
 enum { X_BF16 = 0, X_F32_NORM = 1 };
 enum { STORE_BF16 = 0, STORE_F32 = 1, ADD_F32 = 2, SWIGLU = 3 };
@@ -89,9 +90,9 @@ skinny_gemm_kernel(const Args a) {
     const int n_tiles = (N + ROWS_PER_TILE - 1) / ROWS_PER_TILE;
     const int steps = K / 32;
     const int my_steps = (steps > warp) ? (steps - warp + WARPS - 1) / WARPS : 0;
-    const int nb = (my_steps + UNROLL - 1) / UNROLL;
+    const int nb = max(1, ((steps + WARPS - 1) / WARPS + UNROLL - 1) / UNROLL);   // batches per tile, same for all warps
 
-    // pointers of this lane's two weight rows for a tile (rows past the end repeat the last one)
+    // this lane's two weight rows of a tile (rows past the end repeat the last one)
     auto row_ptrs = [&](int tile, const bf16*& pa, const bf16*& pb) {
         if (EPI == SWIGLU) {
             const int r = min(tile * 8 + g, N - 1);
@@ -102,9 +103,13 @@ skinny_gemm_kernel(const Args a) {
             pb = a.w + (int64_t)min(tile * 16 + g + 8, N - 1) * K + 8 * t;
         }
     };
-    uint4 ca[UNROLL], cb[UNROLL];      // current batch
-    uint4 na[UNROLL], nbuf[UNROLL];    // next batch
-    auto load_batch = [&](uint4 (&ra)[UNROLL], uint4 (&rb)[UNROLL], const bf16* pa, const bf16* pb, int b) {
+    // Two register buffers of UNROLL k-steps each take turns: while one is being
+    // multiplied the other is in flight.  No buffer is ever copied, so nothing waits
+    // for a load before its data is needed.
+    uint4 buf0a[UNROLL], buf0b[UNROLL], buf1a[UNROLL], buf1b[UNROLL];
+    auto load_batch = [&](uint4 (&ra)[UNROLL], uint4 (&rb)[UNROLL], int tile, int b) {
+        const bf16 *pa, *pb;
+        row_ptrs(tile, pa, pb);
 #pragma unroll
         for (int u = 0; u < UNROLL; u++) {
             const int s = b * UNROLL + u;
@@ -112,19 +117,14 @@ skinny_gemm_kernel(const Args a) {
                 const int off = (warp + s * WARPS) * 32;
                 ra[u] = ldg_stream(pa + off);
                 rb[u] = ldg_stream(pb + off);
-            } else {
-                ra[u] = make_uint4(0, 0, 0, 0);
-                rb[u] = make_uint4(0, 0, 0, 0);
             }
         }
     };
 
-    int tile = blockIdx.x;
-    const bf16 *pa = nullptr, *pb = nullptr;
-    if (tile < n_tiles && nb > 0) {          // weights do not depend on X: start them first
-        row_ptrs(tile, pa, pb);
-        load_batch(ca, cb, pa, pb, 0);
-    }
+    int cur_tile = blockIdx.x, cur_b = 0;     // the batch that sits in the buffer used next
+    if (cur_tile < n_tiles) load_batch(buf0a, buf0b, cur_tile, 0);   // weights do not depend on X: start them first
+    griddep_wait();        // X (and, for ADD_F32, the matrix added into) come from the kernels before
+    griddep_launch();
 
     // ---- prologue: X into shared memory as bfloat16, rows past n are zero ----
     if (PRO == X_BF16) {
@@ -136,95 +136,133 @@ skinny_gemm_kernel(const Args a) {
             *reinterpret_cast<uint4*>(xs + r * XS + ch * 8) = v;
         }
     } else {
-        for (int r = warp; r < 8 * NT; r += WARPS) {
-            bf16* dst = xs + r * XS;
-            if (r >= n) {
-                for (int i = lane * 8; i < K; i += 32 * 8) *reinterpret_cast<uint4*>(dst + i) = make_uint4(0, 0, 0, 0);
-                continue;
-            }
-            const float* src = a.x_f32 + (int64_t)(a.rows ? a.rows[r] : r) * K;
-            float ss = 0.f;
-            for (int i = lane * 4; i < K; i += 32 * 4) {
-                const float4 v = *reinterpret_cast<const float4*>(src + i);
-                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        // WARPS / (8*NT) warps share a row: each takes a contiguous part of it, the
+        // parts' sums of squares are added in part order
+        constexpr int PARTS = WARPS / (8 * NT);
+        const int r = warp / PARTS, part = warp - r * PARTS;
+        const int span = K / PARTS;                      // K % 32 == 0 and PARTS <= 2: a multiple of 16
+        const int lo_k = part * span;
+        bf16* dst = xs + r * XS;
+        float* ss_part = red;                            // [8*NT][PARTS], free until the first tile ends
+        const bool live = r < n;
+        const float* src = live ? a.x_f32 + (int64_t)(a.rows ? a.rows[r] : r) * K : nullptr;
+        const bool one_pass = span <= NORM_F4 * 128;
+        float4 v[NORM_F4];
+        float ss = 0.f;
+        if (live) {
+            if (one_pass) {
+#pragma unroll
+                for (int i = 0; i < NORM_F4; i++) {
+                    const int k = lo_k + (i * 32 + lane) * 4;
+                    v[i] = (k < lo_k + span) ? *reinterpret_cast<const float4*>(src + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int i = 0; i < NORM_F4; i++) ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+            } else {
+                for (int k = lo_k + lane * 4; k < lo_k + span; k += 128) {
+                    const float4 w4 = *reinterpret_cast<const float4*>(src + k);
+                    ss += w4.x * w4.x + w4.y * w4.y + w4.z * w4.z + w4.w * w4.w;
+                }
             }
             ss = warp_sum(ss);
-            const float scale = rsqrtf(ss / (float)K + a.eps);
-            for (int i = lane * 4; i < K; i += 32 * 4) {
-                const float4 v = *reinterpret_cast<const float4*>(src + i);
-                const float4 gn = *reinterpret_cast<const float4*>(a.gain + i);
-                __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * scale * gn.x, v.y * scale * gn.y);
-                __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * scale * gn.z, v.w * scale * gn.w);
+            if (lane == 0) ss_part[r * PARTS + part] = ss;
+        }
+        __syncthreads();
+        if (live) {
+            float tot = 0.f;
+#pragma unroll
+            for (int q = 0; q < PARTS; q++) tot += ss_part[r * PARTS + q];
+            const float scale = rsqrtf(tot / (float)K + a.eps);
+            auto put = [&](int k, const float4& w4) {
+                const float4 gn = *reinterpret_cast<const float4*>(a.gain + k);
+                __nv_bfloat162 lo2 = __floats2bfloat162_rn(w4.x * scale * gn.x, w4.y * scale * gn.y);
+                __nv_bfloat162 hi2 = __floats2bfloat162_rn(w4.z * scale * gn.z, w4.w * scale * gn.w);
                 uint2 pk;
-                pk.x = *reinterpret_cast<uint32_t*>(&lo);
-                pk.y = *reinterpret_cast<uint32_t*>(&hi);
-                *reinterpret_cast<uint2*>(dst + i) = pk;
+                pk.x = *reinterpret_cast<uint32_t*>(&lo2);
+                pk.y = *reinterpret_cast<uint32_t*>(&hi2);
+                *reinterpret_cast<uint2*>(dst + k) = pk;
+            };
+            if (one_pass) {
+#pragma unroll
+                for (int i = 0; i < NORM_F4; i++) {
+                    const int k = lo_k + (i * 32 + lane) * 4;
+                    if (k < lo_k + span) put(k, v[i]);
+                }
+            } else {
+                for (int k = lo_k + lane * 4; k < lo_k + span; k += 128) put(k, *reinterpret_cast<const float4*>(src + k));
             }
+        } else {
+            for (int k = lo_k + lane * 8; k < lo_k + span; k += 256) *reinterpret_cast<uint4*>(dst + k) = make_uint4(0, 0, 0, 0);
         }
     }
     __syncthreads();
 
     // ---- tiles ----
-    for (; tile < n_tiles; tile += gridDim.x) {
-        float acc[NT][4];
+    float acc[NT][4];
 #pragma unroll
-        for (int i = 0; i < NT; i++)
+    for (int i = 0; i < NT; i++)
 #pragma unroll
-            for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
-        const int next_tile = tile + gridDim.x;
-        for (int b = 0; b < nb; b++) {
-            if (b + 1 < nb) {
-                load_batch(na, nbuf, pa, pb, b + 1);
-            } else if (next_tile < n_tiles) {
-                row_ptrs(next_tile, pa, pb);
-                load_batch(na, nbuf, pa, pb, 0);
-            }
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+
+    // multiply the batch (cur_tile, cur_b) held in x while the following batch loads into y
+    auto phase = [&](uint4 (&xa)[UNROLL], uint4 (&xb)[UNROLL], uint4 (&ya)[UNROLL], uint4 (&yb)[UNROLL]) {
+        int nxt_tile = cur_tile, nxt_b = cur_b + 1;
+        if (nxt_b == nb) { nxt_b = 0; nxt_tile += gridDim.x; }
+        if (nxt_tile < n_tiles) load_batch(ya, yb, nxt_tile, nxt_b);
 #pragma unroll
-            for (int u = 0; u < UNROLL; u++) {
-                const int s = b * UNROLL + u;
-                if (s < my_steps) {
-                    const int k0 = (warp + s * WARPS) * 32 + 8 * t;
+        for (int u = 0; u < UNROLL; u++) {
+            const int s = cur_b * UNROLL + u;
+            if (s < my_steps) {
+                const int k0 = (warp + s * WARPS) * 32 + 8 * t;
 #pragma unroll
-                    for (int nt = 0; nt < NT; nt++) {
-                        const uint4 xb = *reinterpret_cast<const uint4*>(xs + (nt * 8 + g) * XS + k0);
-                        mma_bf16(acc[nt], ca[u].x, cb[u].x, ca[u].y, cb[u].y, xb.x, xb.y);
-                        mma_bf16(acc[nt], ca[u].z, cb[u].z, ca[u].w, cb[u].w, xb.z, xb.w);
-                    }
+                for (int nt = 0; nt < NT; nt++) {
+                    const uint4 xv = *reinterpret_cast<const uint4*>(xs + (nt * 8 + g) * XS + k0);
+                    mma_bf16(acc[nt], xa[u].x, xb[u].x, xa[u].y, xb[u].y, xv.x, xv.y);
+                    mma_bf16(acc[nt], xa[u].z, xb[u].z, xa[u].w, xb[u].w, xv.z, xv.w);
                 }
             }
-#pragma unroll
-            for (int u = 0; u < UNROLL; u++) { ca[u] = na[u]; cb[u] = nbuf[u]; }
         }
-        // the eight warps' partial tiles, added in warp order
+        if (cur_b == nb - 1) {
+            // the warps' partial tiles, added in warp order
+            const int tile = cur_tile;
 #pragma unroll
-        for (int nt = 0; nt < NT; nt++) {
-            float* r0 = red + ((warp * 16 + g) * 8 * NT) + nt * 8 + 2 * t;
-            float* r1 = red + ((warp * 16 + g + 8) * 8 * NT) + nt * 8 + 2 * t;
-            r0[0] = acc[nt][0]; r0[1] = acc[nt][1]; r1[0] = acc[nt][2]; r1[1] = acc[nt][3];
-        }
-        __syncthreads();
-        constexpr int OUT_ROWS = (EPI == SWIGLU) ? 8 : 16;
-        for (int e = threadIdx.x; e < OUT_ROWS * 8 * NT; e += THREADS) {
-            const int r = e / (8 * NT), c = e - r * (8 * NT);      // weight row in the tile, token
-            const int col = tile * OUT_ROWS + r;
-            if (c >= n || col >= N) continue;
-            float v = 0.f;
-#pragma unroll
-            for (int w = 0; w < WARPS; w++) v += red[(w * 16 + r) * 8 * NT + c];
-            if (EPI == SWIGLU) {
-                float u = 0.f;
-#pragma unroll
-                for (int w = 0; w < WARPS; w++) u += red[(w * 16 + r + 8) * 8 * NT + c];
-                a.y_bf16[(int64_t)c * a.y_stride + col] = __float2bfloat16_rn((v / (1.f + expf(-v))) * u);
-            } else if (EPI == STORE_BF16) {
-                a.y_bf16[(int64_t)c * a.y_stride + col] = __float2bfloat16_rn(v);
-            } else if (EPI == STORE_F32) {
-                a.y_f32[(int64_t)c * a.y_stride + col] = v;
-            } else {
-                a.y_f32[(int64_t)c * a.y_stride + col] += v;
+            for (int nt = 0; nt < NT; nt++) {
+                float* r0 = red + ((warp * 16 + g) * 8 * NT) + nt * 8 + 2 * t;
+                float* r1 = red + ((warp * 16 + g + 8) * 8 * NT) + nt * 8 + 2 * t;
+                r0[0] = acc[nt][0]; r0[1] = acc[nt][1]; r1[0] = acc[nt][2]; r1[1] = acc[nt][3];
+                acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
             }
+            __syncthreads();
+            constexpr int OUT_ROWS = (EPI == SWIGLU) ? 8 : 16;
+            for (int e = threadIdx.x; e < OUT_ROWS * 8 * NT; e += THREADS) {
+                const int r = e / (8 * NT), c = e - r * (8 * NT);      // weight row in the tile, token
+                const int col = tile * OUT_ROWS + r;
+                if (c >= n || col >= N) continue;
+                float v = 0.f;
+#pragma unroll
+                for (int w = 0; w < WARPS; w++) v += red[(w * 16 + r) * 8 * NT + c];
+                if (EPI == SWIGLU) {
+                    float u = 0.f;
+#pragma unroll
+                    for (int w = 0; w < WARPS; w++) u += red[(w * 16 + r + 8) * 8 * NT + c];
+                    a.y_bf16[(int64_t)c * a.y_stride + col] = __float2bfloat16_rn((v / (1.f + expf(-v))) * u);
+                } else if (EPI == STORE_BF16) {
+                    a.y_bf16[(int64_t)c * a.y_stride + col] = __float2bfloat16_rn(v);
+                } else if (EPI == STORE_F32) {
+                    a.y_f32[(int64_t)c * a.y_stride + col] = v;
+                } else {
+                    a.y_f32[(int64_t)c * a.y_stride + col] += v;
+                }
+            }
+            __syncthreads();
         }
-        __syncthreads();
+        cur_tile = nxt_tile;
+        cur_b = nxt_b;
+    };
+    while (cur_tile < n_tiles) {
+        phase(buf0a, buf0b, buf1a, buf1b);
+        if (cur_tile >= n_tiles) break;
+        phase(buf1a, buf1b, buf0a, buf0b);
     }
 }
 
@@ -253,7 +291,7 @@ int launch(const Args& a, cudaStream_t s) {
     const int rows_per_tile = (EPI == SWIGLU) ? 8 : 16;
     const int n_tiles = (a.N + rows_per_tile - 1) / rows_per_tile;
     const int grid = min(n_tiles, max_grid);
-    kern<<<grid, THREADS, smem, s>>>(a);
+    kllm_launch((kern), dim3(grid), dim3(THREADS), smem, s, a);
     KLLM_LAUNCH_STATUS();
 }
 

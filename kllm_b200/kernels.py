@@ -231,6 +231,35 @@ def attention_decode(out, q, kcache, vcache, positions, token_req, block_table, 
         launches += 1       # the combine kernel
 
 
+def attention_decode_fused(out, q, k_new, v_new, cos_sin, kcache, vcache, positions, token_req, block_table,
+                           counters, n_heads, n_kv, head_dim, window, scale, num_splits: int) -> None:
+    """Decode attention of one token per request with the rotary encoding, the cache
+    write and the merge of the key ranges inside the kernel.  q, k_new, v_new are the
+    step's unrotated projections; ``counters`` is an all-zero int32 tensor of at least
+    n_tokens * n_kv elements that the kernel leaves all zero."""
+    _cuda(out, q, k_new, v_new, cos_sin, kcache, vcache, positions, token_req, block_table, counters)
+    _check_attention(out, q, kcache, vcache, block_table, n_kv, head_dim)
+    _i32(positions, "positions"); _i32(token_req, "token_req"); _i32(counters, "counters")
+    n = q.shape[0]
+    if k_new.stride(1) != 1 or v_new.stride(1) != 1 or k_new.dtype != q.dtype or v_new.dtype != q.dtype:
+        raise KernelError("attention (fused): k and v must be bfloat16 with dense rows")
+    if cos_sin.dtype != torch.float32 or not cos_sin.is_contiguous() or cos_sin.shape[1] != head_dim:
+        raise KernelError("attention (fused): the cos/sin table must be float32 [positions, head_dim]")
+    if counters.numel() < n * n_kv:
+        raise KernelError("attention (fused): too few counters")
+    part_o = part_ml = None
+    if num_splits > 1:
+        part_o = torch.empty((n, n_heads, num_splits, head_dim), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((n, n_heads, num_splits, 2), dtype=torch.float32, device=q.device)
+    lib = load_library("attention_tc", {"KLLM_HD": head_dim})
+    rc = lib.kllm_attention_decode_fused(
+        _p(out), _p(part_o), _p(part_ml), _p(counters), _p(q), ctypes.c_int64(q.stride(0)), _p(k_new),
+        ctypes.c_int64(k_new.stride(0)), _p(v_new), ctypes.c_int64(v_new.stride(0)), _p(cos_sin), _p(kcache),
+        _p(vcache), _p(positions), _p(token_req), _p(block_table), block_table.shape[1], n, n_heads, n_kv,
+        head_dim, kcache.shape[2], int(window or 0), ctypes.c_float(scale), int(num_splits), _stream())
+    _check(lib, "attention_tc", rc)
+
+
 def attention_prefill(out, q, kcache, vcache, q_start, start_pos, block_table, n_requests, n_heads, n_kv,
                       head_dim, window, scale) -> None:
     """Tensor-core attention of portions: request s brings rows q_start[s]..q_start[s+1]
@@ -290,7 +319,7 @@ def skinny_fits(n: int, k: int, dtype: torch.dtype) -> bool:
         return False
     nt = 1 if n <= 8 else 2
     row = k + (32 if (k * 2) % 128 == 0 else 0)
-    return 8 * nt * row * 2 + 8 * 16 * 8 * nt * 4 <= 227 * 1024
+    return 8 * nt * row * 2 + 16 * 16 * 8 * nt * 4 <= 227 * 1024     # X rows + the 16 warps' partial tiles
 
 
 def skinny_gemm(weight: torch.Tensor, *, x: Optional[torch.Tensor] = None, x_f32: Optional[torch.Tensor] = None,

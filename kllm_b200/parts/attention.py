@@ -52,6 +52,7 @@ class PagedAttention:
         self.position = part_factory("position", pos.kind)(pos, env) if pos is not None else None
         self.w_qkv = None
         self.w_o = None
+        self._counters = None      # zeroed scratch of the fused decode kernel, which keeps it zero
 
     def _names(self):
         return {k: f"{self.prefix}.{k}_proj.weight" for k in "qkvo"}
@@ -82,6 +83,19 @@ class PagedAttention:
 
     def _attend(self, q, k, v, ctx, cache):
         n = q.shape[0]
+        group = self.n_heads // self.n_kv
+        table = getattr(self.position, "full_rotary_table", lambda: None)() if self.position is not None else None
+        if (table is not None and cache.writes and ctx.all_single and self.dtype == torch.bfloat16 and group <= 16
+                and self.head_dim in kernels.TC_HEAD_DIMS and self.head_dim % 32 == 0):
+            # decode: rotary encoding, cache write and attention in one kernel
+            if self._counters is None or self._counters.numel() < n * self.n_kv:
+                self._counters = torch.zeros(max(64, n) * self.n_kv, dtype=torch.int32, device=q.device)
+            attn = torch.empty((n, self.q_dim), dtype=self.dtype, device=q.device)
+            kernels.attention_decode_fused(
+                attn, q, k, v, table, cache.k, cache.v, ctx.positions, ctx.token_req, cache.block_table,
+                self._counters, self.n_heads, self.n_kv, self.head_dim, self.window or 0, self.scale,
+                kernels.decode_splits(n, self.n_kv, ctx.split_bound or ctx.max_ctx))
+            return attn
         if self.position is not None:
             self.position.apply(q, k, v, ctx, cache, self.n_heads, self.n_kv)
         elif cache.writes:

@@ -8,7 +8,9 @@ how the reference forms its angles (backend/model.cu:176-178).
 
 Interface of a position part used by the attention mixer:
 ``apply(q, k, v, ctx, cache, n_heads, n_kv_heads)`` rotates q in place and, when the
-layer writes its cache, stores rotated k and v into the pages.
+layer writes its cache, stores rotated k and v into the pages.  Optional:
+``full_rotary_table()`` returns the cos/sin table when the whole head is rotated, for
+a mixer whose kernel can do the rotation itself.
 """
 from __future__ import annotations
 
@@ -37,6 +39,9 @@ class RotaryEmbedding:
 
     def bind(self, tensors):
         pass
+
+    def full_rotary_table(self):
+        return self.cos_sin if self.rotary_dim == self.head_dim else None
 
     def apply(self, q, k, v, ctx, cache, n_heads, n_kv_heads):
         writes = cache.writes and cache.k is not None

@@ -209,6 +209,55 @@ def test_tensor_core_attention_finds_one_far_key(kernel, splits):
     assert np.abs(want.reshape(1, H, hd)[0, 2]).max() > 0.5
 
 
+@pytest.mark.parametrize("H,G,hd,page", [(8, 2, 64, 16), (32, 4, 128, 64), (3, 1, 32, 5), (4, 4, 96, 16)])
+@pytest.mark.parametrize("splits", [1, 3, 8])
+def test_fused_decode_attention_rotates_appends_and_merges(H, G, hd, page, splits):
+    """Against the separate kernels' math: rotate q and the new k, store k and v at the
+    token's slot, attend over everything.  Run twice on one counter buffer."""
+    from kllm_b200 import kernels
+    rng = np.random.default_rng(H * hd + splits)
+    lengths = [70, 1, 33, 129, 300]
+    theta, max_pos = 1e4, 320
+    j = np.arange(hd // 2, dtype=np.float64)
+    ang = np.arange(max_pos, dtype=np.float64)[:, None] * theta ** (-2.0 * j / hd)
+    cos_sin = dev(np.concatenate([np.cos(ang), np.sin(ang)], 1).astype(np.float32))
+    counters = torch.zeros(64, dtype=torch.int32, device="cuda")
+    for rep in range(2):
+        ks, vs, want, qraw, knew, vnew = [], [], [], [], [], []
+        for L in lengths:
+            # history keys are stored rotated already; the last position is this step's token
+            k = rng.standard_normal((L, G, hd)).astype(np.float32)
+            v = rng.standard_normal((L, G, hd)).astype(np.float32)
+            q = rng.standard_normal((1, H, hd)).astype(np.float32)
+            kq, vq, qq = as_stored(k, "bfloat16"), as_stored(v, "bfloat16"), as_stored(q, "bfloat16")
+            k_last_rot = plain.round_act_bf16(plain.rope(kq[-1:].reshape(1, G * hd), [L - 1], G, hd, theta))
+            q_rot = plain.round_act_bf16(plain.rope(qq.reshape(1, H * hd), [L - 1], H, hd, theta))
+            k_all = np.concatenate([kq[:-1].reshape(L - 1, G * hd), k_last_rot])
+            # attention of the single query over all L keys (causal mask is the loop bound)
+            sc_q = np.concatenate([np.zeros((L - 1, H * hd)), q_rot])
+            full = plain.attention(sc_q, k_all, vq.reshape(L, G * hd), H, G, hd, rnd_p=plain.round_act_bf16)
+            want.append(full[-1:])
+            hist_k = k.copy(); hist_k[-1] = np.nan          # the slot of the new token holds nothing yet
+            hist_v = v.copy(); hist_v[-1] = np.nan
+            ks.append(hist_k); vs.append(hist_v)
+            qraw.append(q.reshape(1, H * hd)); knew.append(k[-1:].reshape(1, G * hd)); vnew.append(v[-1:].reshape(1, G * hd))
+        kc, vc, table = paged(ks, vs, page, sum(-(-L // page) for L in lengths) + 3, rng, "bfloat16", lengths)
+        q_t, k_t, v_t = (dev(np.concatenate(a), torch.bfloat16) for a in (qraw, knew, vnew))
+        out = torch.empty_like(q_t)
+        pos = dev(np.array([L - 1 for L in lengths], np.int32))
+        req = dev(np.arange(len(lengths), dtype=np.int32))
+        kernels.attention_decode_fused(out, q_t, k_t, v_t, cos_sin, kc, vc, pos, req, table, counters, H, G, hd, 0,
+                                       1.0 / math.sqrt(hd), splits)
+        assert not torch.isnan(out.float()).any()
+        close(out, np.concatenate(want), "bfloat16", f"attention, run {rep}")
+        assert int(counters.abs().sum()) == 0, "the counters must be zero again"
+        for s, L in enumerate(lengths):
+            pg, slot = int(table[s, (L - 1) // page]), (L - 1) % page
+            k_rot = plain.rope(as_stored(knew[s], "bfloat16"), [L - 1], G, hd, theta).reshape(G, hd)
+            close(kc[pg, :, slot], k_rot, "bfloat16", "stored key")
+            assert torch.equal(vc[pg, :, slot].float().cpu(), torch.from_numpy(as_stored(vnew[s], "bfloat16").reshape(G, hd)).float())
+
+
 def test_tensor_core_attention_refusals():
     from kllm_b200 import kernels
     q = torch.zeros(1, 34 * 64, device="cuda", dtype=torch.bfloat16)
