@@ -20,8 +20,9 @@
 //    (it is found with one atomic counter; the merge itself runs in split order,
 //    so the result does not depend on who is last).  One launch replaces three.
 //
-//  * prefill: a CTA takes up to 64 rows = (tokens of one request's portion) x
-//    (heads of one group), each warp 16 of them, and walks the keys from the first
+//  * prefill: a CTA takes up to 128 rows (64 for head sizes above 64) = (tokens of
+//    one request's portion) x (heads of one group), each warp 32 (16) of them as two
+//    (one) MMA tiles that share every key and value fragment, and walks the keys from the first
 //    visible one to the last token's own position in 64-key tiles that all warps
 //    share.  Portions of prompts and single tokens may be mixed in one launch; a
 //    CTA finds its request from the prefix sums of the portions' lengths.
@@ -404,6 +405,11 @@ __global__ void attn_combine_kernel(bf16* __restrict__ out, const float* __restr
 
 // ---- prefill ------------------------------------------------------------------
 
+// Rows per warp in the prefill kernel: two 16-row MMA tiles share every key and value
+// fragment (half the shared-memory reads per flop) where the registers allow it.
+constexpr int MT = HD <= 64 ? 2 : 1;
+constexpr int PRE_ROWS = 4 * 16 * MT;          // rows (token x head of the group) per CTA
+
 __global__ void __launch_bounds__(THREADS)
 attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t q_stride,
                     const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
@@ -419,7 +425,10 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t 
     const int gs = n_heads / n_kv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tq = lane & 3;
     if (threadIdx.x == 0) {
-        int tile = blockIdx.x, req = -1, tok0 = 0;
+        // CTAs start in the order of blockIdx.x: hand out the tiles back to front, so
+        // that those with the longest key ranges (the ends of the portions) start first
+        // and the short ones fill the tail of the launch
+        int tile = gridDim.x - 1 - blockIdx.x, req = -1, tok0 = 0;
         for (int s = 0; s < n_requests; s++) {
             const int n = q_start[s + 1] - q_start[s];
             const int nt = (n + tokens_per_tile - 1) / tokens_per_tile;
@@ -440,43 +449,58 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t 
     const int* table = block_table + (int64_t)req * max_blocks;
     const int ntiles = (hi - lo + TILE - 1) / TILE;
 
-    // this thread's two rows: (token, head of the group)
-    const int r0 = 16 * warp + gid, r1 = r0 + 8;
-    const int t0 = r0 / gs, h0 = r0 - t0 * gs, t1 = r1 / gs, h1 = r1 - t1 * gs;
-    const bool v0 = t0 < n_tok, v1 = t1 < n_tok;
-    const int p0 = v0 ? pos0 + t0 : -1, p1 = v1 ? pos0 + t1 : -1;   // -1: no key is visible
-    const int w0 = (window > 0) ? p0 + 1 - window : 0, w1 = (window > 0) ? p1 + 1 - window : 0;
+    // this thread's rows, two per MMA tile: (token, head of the group)
+    int pr[MT][2], wr[MT][2];            // position of the row's token (-1: row unused), first visible key
+    bool vr[MT][2];
+    uint32_t qa[MT][KSTEPS][4];
+    int64_t orow[MT][2];
+#pragma unroll
+    for (int m = 0; m < MT; m++) {
+        const bf16* qp[2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int r = (16 * MT) * warp + 16 * m + gid + 8 * h;
+            const int tt = r / gs, hh = r - tt * gs;
+            vr[m][h] = tt < n_tok;
+            pr[m][h] = vr[m][h] ? pos0 + tt : -1;
+            wr[m][h] = (window > 0) ? pr[m][h] + 1 - window : 0;
+            qp[h] = q + (int64_t)(tok0 + tt) * q_stride + (int64_t)(g * gs + hh) * HD;
+            orow[m][h] = (int64_t)(tok0 + tt) * n_heads * HD + (int64_t)(g * gs + hh) * HD;
+        }
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ks++) {
+            const int c = ks * 16 + 2 * tq;
+            qa[m][ks][0] = vr[m][0] ? *reinterpret_cast<const uint32_t*>(qp[0] + c) : 0u;
+            qa[m][ks][1] = vr[m][1] ? *reinterpret_cast<const uint32_t*>(qp[1] + c) : 0u;
+            qa[m][ks][2] = vr[m][0] ? *reinterpret_cast<const uint32_t*>(qp[0] + c + 8) : 0u;
+            qa[m][ks][3] = vr[m][1] ? *reinterpret_cast<const uint32_t*>(qp[1] + c + 8) : 0u;
+        }
+    }
     // key range that this warp's rows can see at all
-    const int wt_first = (16 * warp) / gs, wt_last = min(n_tok - 1, (16 * warp + 15) / gs);
+    const int wrow0 = 16 * MT * warp;
+    const int wt_first = wrow0 / gs, wt_last = min(n_tok - 1, (wrow0 + 16 * MT - 1) / gs);
     const bool warp_active = wt_first < n_tok;
     const int warp_hi = pos0 + wt_last + 1;
     const int warp_full_below = pos0 + wt_first;                    // keys <= this are causal for every row
 
-    uint32_t qa[KSTEPS][4];
-    {
-        const bf16* q0 = q + (int64_t)(tok0 + t0) * q_stride + (int64_t)(g * gs + h0) * HD;
-        const bf16* q1 = q + (int64_t)(tok0 + t1) * q_stride + (int64_t)(g * gs + h1) * HD;
+    float o[MT][DTILES][4];
+    float mx[MT][2], l[MT][2];
 #pragma unroll
-        for (int ks = 0; ks < KSTEPS; ks++) {
-            const int c = ks * 16 + 2 * tq;
-            qa[ks][0] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + c) : 0u;
-            qa[ks][1] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + c) : 0u;
-            qa[ks][2] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + c + 8) : 0u;
-            qa[ks][3] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + c + 8) : 0u;
-        }
+    for (int m = 0; m < MT; m++) {
+#pragma unroll
+        for (int i = 0; i < DTILES; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) o[m][i][j] = 0.f;
+        mx[m][0] = mx[m][1] = -INFINITY;
+        l[m][0] = l[m][1] = 0.f;
     }
-    float o[DTILES][4];
-#pragma unroll
-    for (int i = 0; i < DTILES; i++)
-#pragma unroll
-        for (int j = 0; j < 4; j++) o[i][j] = 0.f;
-    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
 #pragma unroll
     for (int s = 0; s < PRE_STAGES - 1; s++) {
         if (s < ntiles) load_tile(smem + s * STAGE_ELEMS, kcache, vcache, table, lo + s * TILE, hi, g, n_kv, page_size);
         cp_async_commit();
     }
+    const int mi = lane >> 3;
     for (int i = 0; i < ntiles; i++) {
         cp_async_wait<PRE_STAGES - 2>();
         __syncthreads();
@@ -489,75 +513,112 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t 
         const int key0 = lo + i * TILE;
         if (!warp_active || key0 >= warp_hi) continue;             // nothing of this tile is visible to the warp
         const bool need_mask = window > 0 || key0 + TILE - 1 > warp_full_below;
-        float s[8][4];
+        // scores of the warp's rows against the 64 keys: every key fragment serves all MT tiles
+        float s[MT][8][4];
 #pragma unroll
-        for (int sl = 0; sl < 4; sl++) {
-            float s2[2][4];
-            scores16(s2, qa, sk, sl, lane);
-#pragma unroll
-            for (int j = 0; j < 4; j++) { s[2 * sl][j] = s2[0][j]; s[2 * sl + 1][j] = s2[1][j]; }
-        }
-        if (need_mask) {
+        for (int m = 0; m < MT; m++)
 #pragma unroll
             for (int nt = 0; nt < 8; nt++)
 #pragma unroll
-                for (int j = 0; j < 2; j++) {
-                    const int key = key0 + nt * 8 + 2 * tq + j;
-                    if (key > p0 || key < w0) s[nt][j] = -INFINITY;
-                    if (key > p1 || key < w1) s[nt][2 + j] = -INFINITY;
-                }
-        }
-        float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-        for (int nt = 0; nt < 8; nt++) {
-            mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
-            mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
-        }
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
-        // a row that has seen no key yet keeps max -inf: subtract 0 instead, all its p are exp2(-inf) = 0
-        const float b0 = (n0 == -INFINITY) ? 0.f : n0, b1 = (n1 == -INFINITY) ? 0.f : n1;
-        const float c0 = exp2f((m0 - b0) * scale_log2e), c1 = exp2f((m1 - b1) * scale_log2e);
-        m0 = n0; m1 = n1;
-        float sum0 = 0.f, sum1 = 0.f;
-#pragma unroll
-        for (int nt = 0; nt < 8; nt++) {
-            s[nt][0] = exp2f((s[nt][0] - b0) * scale_log2e);
-            s[nt][1] = exp2f((s[nt][1] - b0) * scale_log2e);
-            s[nt][2] = exp2f((s[nt][2] - b1) * scale_log2e);
-            s[nt][3] = exp2f((s[nt][3] - b1) * scale_log2e);
-            sum0 += s[nt][0] + s[nt][1];
-            sum1 += s[nt][2] + s[nt][3];
-        }
-        l0 = l0 * c0 + sum0;
-        l1 = l1 * c1 + sum1;
-#pragma unroll
-        for (int i2 = 0; i2 < DTILES; i2++) { o[i2][0] *= c0; o[i2][1] *= c0; o[i2][2] *= c1; o[i2][3] *= c1; }
+                for (int j = 0; j < 4; j++) s[m][nt][j] = 0.f;
 #pragma unroll
         for (int sl = 0; sl < 4; sl++) {
-            uint32_t pa[4] = {pack_bf16(s[2 * sl][0], s[2 * sl][1]), pack_bf16(s[2 * sl][2], s[2 * sl][3]),
-                              pack_bf16(s[2 * sl + 1][0], s[2 * sl + 1][1]), pack_bf16(s[2 * sl + 1][2], s[2 * sl + 1][3])};
-            accumulate16(o, pa, sv, sl, lane);
+            const bf16* base = sk + (16 * sl + (mi >> 1) * 8 + (lane & 7)) * ROW + (mi & 1) * 8;
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ks++) {
+                uint32_t b[4];
+                ldmatrix_x4(b, base + ks * 16);
+#pragma unroll
+                for (int m = 0; m < MT; m++) {
+                    mma_bf16(s[m][2 * sl], qa[m][ks], b[0], b[1]);
+                    mma_bf16(s[m][2 * sl + 1], qa[m][ks], b[2], b[3]);
+                }
+            }
+        }
+        uint32_t pa[MT][4][4];           // probabilities as bfloat16 A fragments, per 16-key slice
+#pragma unroll
+        for (int m = 0; m < MT; m++) {
+            if (need_mask) {
+#pragma unroll
+                for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+                    for (int j = 0; j < 2; j++) {
+                        const int key = key0 + nt * 8 + 2 * tq + j;
+                        if (key > pr[m][0] || key < wr[m][0]) s[m][nt][j] = -INFINITY;
+                        if (key > pr[m][1] || key < wr[m][1]) s[m][nt][2 + j] = -INFINITY;
+                    }
+            }
+            float t0 = -INFINITY, t1 = -INFINITY;
+#pragma unroll
+            for (int nt = 0; nt < 8; nt++) {
+                t0 = fmaxf(t0, fmaxf(s[m][nt][0], s[m][nt][1]));
+                t1 = fmaxf(t1, fmaxf(s[m][nt][2], s[m][nt][3]));
+            }
+            t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 1));
+            t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 2));
+            t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 1));
+            t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 2));
+            const float n0 = fmaxf(mx[m][0], t0), n1 = fmaxf(mx[m][1], t1);
+            // a row that has seen no key yet keeps max -inf: subtract 0 instead, all its p are exp2(-inf) = 0
+            const float b0 = (n0 == -INFINITY) ? 0.f : n0, b1 = (n1 == -INFINITY) ? 0.f : n1;
+            const float c0 = exp2f((mx[m][0] - b0) * scale_log2e), c1 = exp2f((mx[m][1] - b1) * scale_log2e);
+            mx[m][0] = n0; mx[m][1] = n1;
+            float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+            for (int nt = 0; nt < 8; nt++) {
+                s[m][nt][0] = exp2f((s[m][nt][0] - b0) * scale_log2e);
+                s[m][nt][1] = exp2f((s[m][nt][1] - b0) * scale_log2e);
+                s[m][nt][2] = exp2f((s[m][nt][2] - b1) * scale_log2e);
+                s[m][nt][3] = exp2f((s[m][nt][3] - b1) * scale_log2e);
+                sum0 += s[m][nt][0] + s[m][nt][1];
+                sum1 += s[m][nt][2] + s[m][nt][3];
+            }
+            l[m][0] = l[m][0] * c0 + sum0;
+            l[m][1] = l[m][1] * c1 + sum1;
+#pragma unroll
+            for (int i2 = 0; i2 < DTILES; i2++) {
+                o[m][i2][0] *= c0; o[m][i2][1] *= c0; o[m][i2][2] *= c1; o[m][i2][3] *= c1;
+            }
+#pragma unroll
+            for (int sl = 0; sl < 4; sl++) {
+                pa[m][sl][0] = pack_bf16(s[m][2 * sl][0], s[m][2 * sl][1]);
+                pa[m][sl][1] = pack_bf16(s[m][2 * sl][2], s[m][2 * sl][3]);
+                pa[m][sl][2] = pack_bf16(s[m][2 * sl + 1][0], s[m][2 * sl + 1][1]);
+                pa[m][sl][3] = pack_bf16(s[m][2 * sl + 1][2], s[m][2 * sl + 1][3]);
+            }
+        }
+        // output += P . V: every value fragment serves all MT tiles
+#pragma unroll
+        for (int sl = 0; sl < 4; sl++) {
+            const bf16* base = sv + (16 * sl + (mi & 1) * 8 + (lane & 7)) * ROW + (mi >> 1) * 8;
+#pragma unroll
+            for (int dp = 0; dp < HD / 16; dp++) {
+                uint32_t v[4];
+                ldmatrix_x4_trans(v, base + dp * 16);
+#pragma unroll
+                for (int m = 0; m < MT; m++) {
+                    mma_bf16(o[m][2 * dp], pa[m][sl], v[0], v[1]);
+                    mma_bf16(o[m][2 * dp + 1], pa[m][sl], v[2], v[3]);
+                }
+            }
         }
     }
     cp_async_wait<0>();
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    const float i0 = 1.f / l0, i1 = 1.f / l1;
-    if (v0) {
-        bf16* orow = out + (int64_t)(tok0 + t0) * n_heads * HD + (int64_t)(g * gs + h0) * HD;
 #pragma unroll
-        for (int dt = 0; dt < DTILES; dt++)
-            *reinterpret_cast<uint32_t*>(orow + dt * 8 + 2 * tq) = pack_bf16(o[dt][0] * i0, o[dt][1] * i0);
-    }
-    if (v1) {
-        bf16* orow = out + (int64_t)(tok0 + t1) * n_heads * HD + (int64_t)(g * gs + h1) * HD;
+    for (int m = 0; m < MT; m++) {
 #pragma unroll
-        for (int dt = 0; dt < DTILES; dt++)
-            *reinterpret_cast<uint32_t*>(orow + dt * 8 + 2 * tq) = pack_bf16(o[dt][2] * i1, o[dt][3] * i1);
+        for (int h = 0; h < 2; h++) {
+            float lv = l[m][h];
+            lv += __shfl_xor_sync(0xffffffffu, lv, 1);
+            lv += __shfl_xor_sync(0xffffffffu, lv, 2);
+            if (!vr[m][h]) continue;
+            const float inv = 1.f / lv;
+            bf16* op = out + orow[m][h];
+#pragma unroll
+            for (int dt = 0; dt < DTILES; dt++)
+                *reinterpret_cast<uint32_t*>(op + dt * 8 + 2 * tq) =
+                    pack_bf16(o[m][dt][2 * h] * inv, o[m][dt][2 * h + 1] * inv);
+        }
     }
 }
 
@@ -714,7 +775,7 @@ extern "C" int kllm_attention_prefill(void* out, const void* q, int64_t q_stride
     const int gs = n_heads / n_kv;
     if (gs > 64) KLLM_FAIL("attention prefill: %d heads per kv head, at most 64", gs);
     if ((rc = set_attributes())) return rc;
-    const int tpt = 64 / gs;
+    const int tpt = PRE_ROWS / gs;
     const int max_tiles = n_tokens / tpt + n_requests;          // >= sum of ceil(n_s / tpt)
     if (n_kv > 65535) KLLM_FAIL("attention prefill: grid too large");
     const float sl2e = scale * 1.4426950408889634f;
