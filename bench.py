@@ -118,6 +118,10 @@ def main():
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0: all)")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and the prefill")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                    help="decode: the batch's decode run alone; prefill: the 2048-token prompt alone (partial "
+                         "records for profiling small cases, not the bench line)")
+    ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -129,6 +133,8 @@ def main():
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(3, args.warmup)
+    if args.only == "decode":
+        args.no_points = True
 
     import torch
     from kllm_b200 import kernels
@@ -150,7 +156,8 @@ def main():
         max_b = max(B, 64 if not args.no_points else B)
         pages = max_b * (-(-ctx // page)) + 8
         eng = Engine(tmp, Options(dtype="bfloat16", max_seq=ctx, block_size=page, num_blocks=pages,
-                                  max_batch=max_b, max_step_tokens=max(2048, max_b)))
+                                  max_batch=max_b, max_step_tokens=max(2048, max_b),
+                                  cuda_graphs=not args.no_graphs))
     finally:
         shutil.rmtree(tmp, ignore_errors=True)
 
@@ -211,6 +218,33 @@ def main():
         sched.stop()
         return dev_ms, e2e_ms, launches, h2d, batch * 4, csum, cached
 
+    def prefill_run(T=2048):
+        from kllm_b200.engine import StepEntry
+        ids = prompts(1, T)[0]
+        times = []
+        for _ in range(4):
+            req = eng.cache.open()
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            ev0.record()
+            eng.runner.run([StepEntry(req, ids, [T - 1])])
+            ev1.record()
+            torch.cuda.synchronize()
+            times.append(ev0.elapsed_time(ev1))
+            eng.cache.close(req)
+        ms = min(times[1:])
+        per_layer, _ = model_bytes_and_flops(cfg, layers)
+        qd = cfg["num_attention_heads"] * cfg["head_dim"]
+        flops = 2 * T * (per_layer * layers) + 2 * cfg["vocab_size"] * cfg["hidden_size"] \
+            + 2 * T * T * qd * layers          # causal attention: QK^T and PV over half the square
+        return {"value": round(T / (ms * 1e-3), 1), "tokens": T, "ms": round(ms, 3),
+                "frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    if args.only == "prefill":
+        with torch.no_grad():
+            print(json.dumps({"partial": "prefill only", "layers": layers, "prefill": prefill_run()}))
+        return 0
+
     with torch.no_grad():
         dev_ms, e2e_ms, launches, h2d, d2h, clocks, cached = decode_run(B, K, W, sample_clocks=True)
         per_layer, weight_elems = model_bytes_and_flops(cfg, layers)
@@ -237,27 +271,7 @@ def main():
                          "mean_context": cached // B},
         }
         if not args.no_points:
-            T = 2048
-            sched = Scheduler(eng)
-            from kllm_b200.engine import StepEntry
-            ids = prompts(1, T)[0]
-            times = []
-            for _ in range(4):
-                req = eng.cache.open()
-                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                torch.cuda.synchronize()
-                ev0.record()
-                eng.runner.run([StepEntry(req, ids, [T - 1])])
-                ev1.record()
-                torch.cuda.synchronize()
-                times.append(ev0.elapsed_time(ev1))
-                eng.cache.close(req)
-            ms = min(times[1:])
-            qd = cfg["num_attention_heads"] * cfg["head_dim"]
-            flops = 2 * T * (per_layer * layers) + 2 * cfg["vocab_size"] * cfg["hidden_size"] \
-                + 2 * T * T * qd * layers          # causal attention: QK^T and PV over half the square
-            out["prefill"] = {"value": round(T / (ms * 1e-3), 1), "tokens": T, "ms": round(ms, 3),
-                              "frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+            out["prefill"] = prefill_run()
             pts = {}
             for b in (1, 64):
                 dms = decode_run(b, max(8, K // 2), 3)[0]

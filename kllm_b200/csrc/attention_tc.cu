@@ -59,10 +59,11 @@ constexpr int STAGE_ELEMS = 2 * TILE * ROW;                       // K tile then
 // the more of the range is in flight at once (with 5 stages a range of 256 keys is
 // requested whole before the first tile is used).  Prefill keeps 3 stages and more
 // CTAs per SM.
-constexpr int DEC_STAGES = HD <= 64 ? 5 : (HD <= 96 ? 4 : 3);
+constexpr int DEC_STAGES_DEEP = HD <= 64 ? 5 : (HD <= 96 ? 4 : 3);   // few CTAs: everything in flight at once
+constexpr int DEC_STAGES_WIDE = 3;                                    // many CTAs: more of them per SM
 constexpr int PRE_STAGES = 3;
-constexpr int DEC_SMEM_BYTES = DEC_STAGES * STAGE_ELEMS * 2;
 constexpr int PRE_SMEM_BYTES = PRE_STAGES * STAGE_ELEMS * 2;
+constexpr int dec_smem_bytes(int stages) { return stages * STAGE_ELEMS * 2; }
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -162,7 +163,7 @@ struct DecodeFusion {
     unsigned int* counters;
 };
 
-template <bool FUSED>
+template <bool FUSED, int DEC_STAGES>
 __global__ void __launch_bounds__(THREADS)
 attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                    const bf16* __restrict__ q, int64_t q_stride, bf16* __restrict__ kcache,
@@ -626,13 +627,17 @@ bool g_attr_set = false;
 
 int set_attributes() {
     if (g_attr_set) return 0;
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM_BYTES);
-    if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM_BYTES);
-    if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PRE_SMEM_BYTES);
+    cudaError_t e = cudaSuccess;
+    auto raise = [&](auto kernel, int bytes) {
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    };
+    raise(attn_decode_kernel<false, DEC_STAGES_DEEP>, dec_smem_bytes(DEC_STAGES_DEEP));
+    raise(attn_decode_kernel<true, DEC_STAGES_DEEP>, dec_smem_bytes(DEC_STAGES_DEEP));
+    raise(attn_decode_kernel<false, DEC_STAGES_WIDE>, dec_smem_bytes(DEC_STAGES_WIDE));
+    raise(attn_decode_kernel<true, DEC_STAGES_WIDE>, dec_smem_bytes(DEC_STAGES_WIDE));
+    raise(attn_prefill_kernel, PRE_SMEM_BYTES);
     if (e != cudaSuccess) {
-        snprintf(g_kllm_err, sizeof(g_kllm_err), "attention: cannot get %d bytes of shared memory: %s", DEC_SMEM_BYTES,
+        snprintf(g_kllm_err, sizeof(g_kllm_err), "attention: cannot get %d bytes of shared memory: %s", dec_smem_bytes(DEC_STAGES_DEEP),
                  cudaGetErrorString(e));
         return (int)e;
     }
@@ -670,7 +675,17 @@ extern "C" int kllm_attention_decode(void* out, void* part_o, void* part_ml, con
     cudaStream_t s = (cudaStream_t)stream;
     const float sl2e = scale * 1.4426950408889634f;
     dim3 grid(num_splits, n_kv, n_tokens);
-    kllm_launch((attn_decode_kernel<false>), dim3(grid), dim3(THREADS), DEC_SMEM_BYTES, s, 
+    // few CTAs (they fit the GPU two per SM): the deep pipeline; many: the wide one
+    const bool deep = (int64_t)num_splits * n_kv * n_tokens <= 2 * 148;
+    if (deep)
+        kllm_launch((attn_decode_kernel<false, DEC_STAGES_DEEP>), dim3(grid), dim3(THREADS),
+                    dec_smem_bytes(DEC_STAGES_DEEP), s, 
+        (bf16*)out, (float*)part_o, (float*)part_ml, (const bf16*)q, q_stride, (bf16*)kcache,
+        (bf16*)vcache, positions, token_req, block_table, max_blocks, n_heads, n_kv, page_size, window, sl2e,
+        num_splits, DecodeFusion{});
+    else
+        kllm_launch((attn_decode_kernel<false, DEC_STAGES_WIDE>), dim3(grid), dim3(THREADS),
+                    dec_smem_bytes(DEC_STAGES_WIDE), s, 
         (bf16*)out, (float*)part_o, (float*)part_ml, (const bf16*)q, q_stride, (bf16*)kcache,
         (bf16*)vcache, positions, token_req, block_table, max_blocks, n_heads, n_kv, page_size, window, sl2e,
         num_splits, DecodeFusion{});
@@ -704,7 +719,15 @@ extern "C" int kllm_attention_decode_fused(void* out, void* part_o, void* part_m
     const float sl2e = scale * 1.4426950408889634f;
     DecodeFusion fu{(const bf16*)k_new, k_stride, (const bf16*)v_new, v_stride, cos_sin, (unsigned int*)counters};
     dim3 grid(num_splits, n_kv, n_tokens);
-    kllm_launch((attn_decode_kernel<true>), dim3(grid), dim3(THREADS), DEC_SMEM_BYTES, (cudaStream_t)stream, 
+    const bool deep = (int64_t)num_splits * n_kv * n_tokens <= 2 * 148;
+    if (deep)
+        kllm_launch((attn_decode_kernel<true, DEC_STAGES_DEEP>), dim3(grid), dim3(THREADS),
+                    dec_smem_bytes(DEC_STAGES_DEEP), (cudaStream_t)stream, 
+        (bf16*)out, (float*)part_o, (float*)part_ml, (const bf16*)q, q_stride, (bf16*)kcache, (bf16*)vcache,
+        positions, token_req, block_table, max_blocks, n_heads, n_kv, page_size, window, sl2e, num_splits, fu);
+    else
+        kllm_launch((attn_decode_kernel<true, DEC_STAGES_WIDE>), dim3(grid), dim3(THREADS),
+                    dec_smem_bytes(DEC_STAGES_WIDE), (cudaStream_t)stream, 
         (bf16*)out, (float*)part_o, (float*)part_ml, (const bf16*)q, q_stride, (bf16*)kcache, (bf16*)vcache,
         positions, token_req, block_table, max_blocks, n_heads, n_kv, page_size, window, sl2e, num_splits, fu);
     KLLM_LAUNCH_STATUS();

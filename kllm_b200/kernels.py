@@ -172,10 +172,21 @@ SM_COUNT = 148
 
 
 def decode_splits(n_tokens: int, n_kv: int, ctx_bound: int) -> int:
-    """Into how many key ranges the decode kernel cuts a token's context: enough
-    CTAs for two per SM, none shorter than 128 keys."""
+    """Into how many key ranges the decode kernel cuts a token's context.
+
+    A CTA takes one (token, kv head, range); two CTAs fit an SM.  The ranges are
+    whole 64-key tiles, as many as fill the SMs in ONE wave (a second wave of short
+    CTAs would double the kernel's time), at most 16, all the same length.  When one
+    range per token would be long, two are used even if that spills into a second
+    wave: long CTAs hide it."""
+    slots = 2 * SM_COUNT
+    tiles = max(1, -(-ctx_bound // 64))
     base = max(1, n_tokens * n_kv)
-    return max(1, min(-(-2 * SM_COUNT // base), -(-ctx_bound // 128), 32))
+    splits = max(1, min(slots // base, tiles, 16))
+    if splits == 1 and tiles >= 16:
+        splits = 2
+    per = -(-tiles // splits)
+    return -(-tiles // per)
 
 
 def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, ctx,
