@@ -1,0 +1,378 @@
+// Causal grouped-query attention of prompt portions over the paged cache on the
+// fifth-generation tensor cores: both products (scores = Q.K^T and output = P.V) are
+// tcgen05.mma instructions issued by one thread, with the operands in shared memory
+// and the accumulators in tensor memory (TMEM).  One library per head size
+// (-DKLLM_HD=64 or 128), bfloat16 operands, float32 accumulation.
+//
+// A CTA of 128 threads takes 128 rows = (tokens of one request's portion) x (heads of
+// one kv group) and walks that portion's keys in tiles of 64:
+//
+//   1. the K and V tiles arrive in shared memory by cp.async, written directly in the
+//      128-byte-swizzled layout that the MMA's shared-memory descriptors name (rows of
+//      64 elements, 8-row groups of 1024 bytes, the 16-byte piece index XORed with the
+//      row index modulo 8); head sizes above 64 are kept as panels of 64 dims;
+//   2. one thread issues Q.K^T (M=128, N=64, K=16 per instruction, HD/16 of them) into
+//      64 TMEM columns and commits to an mbarrier;
+//   3. every thread owns one row: it reads its 64 scores from TMEM (tcgen05.ld
+//      32x32b), applies the mask and the online-softmax recurrence without any
+//      cross-thread traffic, and writes its probabilities as bfloat16 into a swizzled
+//      shared-memory tile;
+//   4. the thread issues P.V (M=128, N=HD, K=16 x 4, V as the MN-major operand) into
+//      another TMEM region, commits, and every thread adds its row of the result to
+//      its float32 accumulator in registers, rescaled by the softmax correction.
+//
+// Two tiles of K/V are in flight (the next one loads while this one is multiplied).
+// Waits on the mbarrier are bounded: a wait that runs out sets a status word, and the
+// CTA leaves after freeing its TMEM.  Math as in the reference
+// (backend/model.cu:343-408): keys [max(0, p + 1 - window), p], scale after the dot
+// product, one division by the sum at the end; probabilities are rounded to bfloat16
+// for the second product only.
+#include "common.cuh"
+
+#ifndef KLLM_HD
+#error "compile with -DKLLM_HD=64 or 128"
+#endif
+
+KLLM_EXPORT_LAST_ERROR(attention_tcgen05)
+
+namespace {
+
+constexpr int HD = KLLM_HD;
+static_assert(HD == 64 || HD == 128, "head size 64 or 128");
+constexpr int PANELS = HD / 64;            // 64-dim panels of a row
+constexpr int ROWS = 128;                  // query rows per CTA = TMEM lanes
+constexpr int TILE = 64;                   // keys per tile
+constexpr int THREADS = 128;
+constexpr int Q_BYTES = PANELS * ROWS * 128;          // [panel][128 rows][64 dims]
+constexpr int KV_BYTES = PANELS * TILE * 128;         // [panel][64 keys][64 dims]
+constexpr int P_BYTES = ROWS * 128;                   // [128 rows][64 keys]
+constexpr int STAGES = 2;
+constexpr int SMEM_BYTES = 1024 + Q_BYTES + P_BYTES + STAGES * 2 * KV_BYTES;
+constexpr int TMEM_COLS = HD == 64 ? 128 : 256;       // scores (64) + output tile (HD), a power of two
+constexpr unsigned kSpinLimit = 1u << 22;
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(unsigned dst, const void* gmem, bool valid) {
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+// shared-memory writes of this thread become visible to the tensor core's (async proxy) reads
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor
+// version 1.  K-major operands: 8-row groups 1024 bytes apart (stride offset), leading
+// offset 1.  MN-major operands: 8-k groups 1024 bytes apart (stride offset), 64-element
+// panels `lbo_bytes` apart (leading offset).
+__device__ __forceinline__ uint64_t make_desc(unsigned addr, unsigned lbo_bytes, unsigned sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;       // descriptor version for this architecture
+    d |= (uint64_t)2 << 61;       // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor: float32 accumulator, bfloat16 A and B, M x N, B optionally MN-major.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma(unsigned d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((unsigned)accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+// 32 consecutive float32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, float (&v)[32]) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+
+// byte offset of 16-byte piece `ch` (0..7) of row `r` inside a swizzled panel of 128-byte rows
+__device__ __forceinline__ unsigned swz(int r, int ch) {
+    return (unsigned)((r >> 3) * 1024 + (r & 7) * 128 + ((ch ^ (r & 7)) << 4));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// keys key0 .. key0+63 of kv head g into a stage: K panels then V panels
+__device__ __forceinline__ void load_kv(unsigned stage, const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
+                                        const int* __restrict__ table, int key0, int hi, int g, int n_kv, int page_size) {
+    for (int c = threadIdx.x; c < TILE * (HD / 8); c += THREADS) {
+        const int row = c / (HD / 8), piece = c - row * (HD / 8);     // piece: 16 bytes of the head's HD dims
+        const int key = key0 + row;
+        const bool valid = key < hi;
+        int64_t off = 0;
+        if (valid) {
+            const int lp = key / page_size;
+            off = (((int64_t)table[lp] * n_kv + g) * page_size + (key - lp * page_size)) * HD + piece * 8;
+        }
+        const unsigned dst = (unsigned)((piece >> 3) * (TILE * 128)) + swz(row, piece & 7);
+        cp_async16(stage + dst, kcache + off, valid);
+        cp_async16(stage + KV_BYTES + dst, vcache + off, valid);
+    }
+}
+
+__global__ void __launch_bounds__(THREADS)
+attn_prefill_tc5_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t q_stride,
+                        const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
+                        const int* __restrict__ q_start, const int* __restrict__ start_pos,
+                        const int* __restrict__ block_table, int max_blocks, int n_requests, int n_heads,
+                        int n_kv, int page_size, int window, float scale_log2e, int tokens_per_tile, int* status) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t bar_mma;
+    __shared__ unsigned s_tmem;
+    __shared__ int s_req, s_tok0, s_abort;
+    griddep_wait();
+    griddep_launch();
+    const int g = blockIdx.y;
+    const int gs = n_heads / n_kv;
+    const int warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) {
+        int tile = gridDim.x - 1 - blockIdx.x, req = -1, tok0 = 0;       // longest key ranges first
+        for (int s = 0; s < n_requests; s++) {
+            const int n = q_start[s + 1] - q_start[s];
+            const int nt = (n + tokens_per_tile - 1) / tokens_per_tile;
+            if (tile < nt) { req = s; tok0 = q_start[s] + tile * tokens_per_tile; break; }
+            tile -= nt;
+        }
+        s_req = req; s_tok0 = tok0; s_abort = 0;
+    }
+    __syncthreads();
+    const int req = s_req;
+    if (req < 0) return;                       // the grid is an upper bound on the tiles
+    const int tok0 = s_tok0;
+    const int n_tok = min(tokens_per_tile, q_start[req + 1] - tok0);
+    const int pos0 = start_pos[req] + (tok0 - q_start[req]);
+    const int lo = (window > 0 && pos0 + 1 > window) ? pos0 + 1 - window : 0;
+    const int hi = pos0 + n_tok;
+    const int* table = block_table + (int64_t)req * max_blocks;
+    const int ntiles = (hi - lo + TILE - 1) / TILE;
+
+    const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;       // swizzled tiles want 1024-byte alignment
+    const unsigned sQ = base, sP = base + Q_BYTES, sKV = sP + P_BYTES;
+
+    // TMEM: one warp allocates, everybody learns the address
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&s_tmem)), "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    }
+    if (threadIdx.x == 0) {
+        mbar_init(&bar_mma, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+
+    // this thread's row: (token, head of the group)
+    const int row = threadIdx.x;
+    const int tt = row / gs, hh = row - tt * gs;
+    const bool valid_row = tt < n_tok && tt < tokens_per_tile;
+    const int p_row = valid_row ? pos0 + tt : -1;                       // -1: sees no key
+    const int w_row = (window > 0) ? p_row + 1 - window : 0;
+
+    // Q tile: each row's HD dims, zero for unused rows
+    for (int c = threadIdx.x; c < ROWS * (HD / 8); c += THREADS) {
+        const int r = c / (HD / 8), piece = c - r * (HD / 8);
+        const int t2 = r / gs, h2 = r - t2 * gs;
+        const bool ok = t2 < n_tok && t2 < tokens_per_tile;
+        const bf16* src = ok ? q + (int64_t)(tok0 + t2) * q_stride + (int64_t)(g * gs + h2) * HD + piece * 8 : q;
+        cp_async16(sQ + (unsigned)((piece >> 3) * (ROWS * 128)) + swz(r, piece & 7), src, ok);
+    }
+    cp_async_commit();
+    if (ntiles > 0) load_kv(sKV, kcache, vcache, table, lo, hi, g, n_kv, page_size);
+    cp_async_commit();
+
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem = s_tmem;
+    const unsigned t_s = tmem + ((unsigned)(warp * 32) << 16);            // scores: columns 0..63
+    const unsigned t_o = t_s + 64;                                        // output tile: columns 64..64+HD-1
+
+    constexpr uint32_t IDESC_S = make_idesc(ROWS, TILE, false);
+    constexpr uint32_t IDESC_O = make_idesc(ROWS, HD, true);
+
+    float o_acc[HD];
+#pragma unroll
+    for (int i = 0; i < HD; i++) o_acc[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    unsigned phase = 0;
+
+    auto wait_mma = [&]() {
+        unsigned spins = 0;
+        while (!mbar_try_wait(&bar_mma, phase)) {
+            if (++spins > kSpinLimit) { s_abort = 1; if (status) *status = 1; break; }
+        }
+        phase ^= 1u;
+        tc_fence_after();
+    };
+
+    for (int i = 0; i < ntiles; i++) {
+        const unsigned st = sKV + (unsigned)(i & 1) * 2u * KV_BYTES;
+        cp_async_wait<0>();                   // Q and tile i are in shared memory (this thread's pieces)
+        fence_async_smem();
+        tc_fence_before();
+        __syncthreads();                      // everybody's pieces; TMEM reads of tile i-1 are done
+        if (s_abort) break;
+        if (i + 1 < ntiles)
+            load_kv(sKV + (unsigned)((i + 1) & 1) * 2u * KV_BYTES, kcache, vcache, table, lo + (i + 1) * TILE, hi, g, n_kv, page_size);
+        cp_async_commit();
+        if (threadIdx.x == 0) {               // scores = Q . K^T
+            tc_fence_after();
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; kk++) {
+                const unsigned a = sQ + (unsigned)((kk >> 2) * (ROWS * 128) + (kk & 3) * 32);
+                const unsigned b = st + (unsigned)((kk >> 2) * (TILE * 128) + (kk & 3) * 32);
+                umma(tmem, make_desc(a, 16, 1024), make_desc(b, 16, 1024), IDESC_S, kk > 0);
+            }
+            umma_commit(&bar_mma);
+        }
+        wait_mma();
+        // this row's 64 scores -> probabilities
+        const int key0 = lo + i * TILE;
+        float s[TILE];
+        {
+            float (*s2)[32] = reinterpret_cast<float (*)[32]>(s);
+            tmem_ld32(t_s, s2[0]);
+            tmem_ld32(t_s + 32, s2[1]);
+            tmem_ld_wait();
+        }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < TILE; j++) {
+            const int key = key0 + j;
+            if (key > p_row || key < w_row) s[j] = -INFINITY;
+            mx = fmaxf(mx, s[j]);
+        }
+        const float m_new = fmaxf(m_run, mx);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;       // a row that has seen no key yet
+        const float corr = exp2f((m_run - m_use) * scale_log2e);
+        m_run = m_new;
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < TILE; j++) {
+            s[j] = exp2f((s[j] - m_use) * scale_log2e);
+            sum += s[j];
+        }
+        l_run = l_run * corr + sum;
+#pragma unroll
+        for (int c = 0; c < 8; c++) {          // 8 keys = 16 bytes per piece, swizzled like an operand row
+            uint4 pk;
+            pk.x = pack_bf16(s[8 * c], s[8 * c + 1]);
+            pk.y = pack_bf16(s[8 * c + 2], s[8 * c + 3]);
+            pk.z = pack_bf16(s[8 * c + 4], s[8 * c + 5]);
+            pk.w = pack_bf16(s[8 * c + 6], s[8 * c + 7]);
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(sP + swz(row, c)), "r"(pk.x), "r"(pk.y), "r"(pk.z), "r"(pk.w) : "memory");
+        }
+        fence_async_smem();
+        tc_fence_before();
+        __syncthreads();                      // P complete; everybody has read the scores out of TMEM
+        if (threadIdx.x == 0) {               // output tile = P . V
+            tc_fence_after();
+#pragma unroll
+            for (int kk = 0; kk < TILE / 16; kk++) {
+                const unsigned a = sP + (unsigned)(kk * 32);
+                const unsigned b = st + KV_BYTES + (unsigned)(kk * 2048);
+                umma(tmem + 64, make_desc(a, 16, 1024), make_desc(b, TILE * 128, 1024), IDESC_O, kk > 0);
+            }
+            umma_commit(&bar_mma);
+        }
+        wait_mma();
+#pragma unroll
+        for (int cb = 0; cb < HD / 32; cb++) {
+            float t[32];
+            tmem_ld32(t_o + cb * 32, t);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; j++) o_acc[cb * 32 + j] = o_acc[cb * 32 + j] * corr + t[j];
+        }
+    }
+    cp_async_wait<0>();
+    if (valid_row && !s_abort) {
+        const float inv = 1.f / l_run;
+        bf16* orow = out + (int64_t)(tok0 + tt) * n_heads * HD + (int64_t)(g * gs + hh) * HD;
+#pragma unroll
+        for (int c = 0; c < HD / 8; c++) {
+            uint4 pk;
+            pk.x = pack_bf16(o_acc[8 * c] * inv, o_acc[8 * c + 1] * inv);
+            pk.y = pack_bf16(o_acc[8 * c + 2] * inv, o_acc[8 * c + 3] * inv);
+            pk.z = pack_bf16(o_acc[8 * c + 4] * inv, o_acc[8 * c + 5] * inv);
+            pk.w = pack_bf16(o_acc[8 * c + 6] * inv, o_acc[8 * c + 7] * inv);
+            *reinterpret_cast<uint4*>(orow + 8 * c) = pk;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS));
+}
+
+bool g_attr_set = false;
+
+}  // namespace
+
+extern "C" int kllm_attention_tcgen05_head_dim() { return HD; }
+
+// Same contract as the mma.sync prefill kernel: requests' portions
+// q_start[s]..q_start[s+1] start at cache position start_pos[s]; out [n, n_heads*HD].
+// status: device int, set to 1 if a bounded wait ran out.
+extern "C" int kllm_attention_prefill_tcgen05(void* out, const void* q, int64_t q_stride, const void* kcache,
+                                              const void* vcache, const int* q_start, const int* start_pos,
+                                              const int* block_table, int max_blocks, int n_tokens,
+                                              int n_requests, int n_heads, int n_kv, int hd, int page_size,
+                                              int window, float scale, int* status, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (hd != HD) KLLM_FAIL("attention (tcgen05): this library was built for head size %d, not %d", HD, hd);
+    if (n_kv <= 0 || n_heads % n_kv) KLLM_FAIL("attention: %d heads over %d kv heads", n_heads, n_kv);
+    const int gs = n_heads / n_kv;
+    if (gs > ROWS) KLLM_FAIL("attention (tcgen05): %d heads per kv head, at most %d", gs, ROWS);
+    if (page_size <= 0) KLLM_FAIL("attention: page size %d", page_size);
+    if (((uintptr_t)q & 15) || (q_stride & 7) || ((uintptr_t)out & 15) || ((uintptr_t)kcache & 15) || ((uintptr_t)vcache & 15))
+        KLLM_FAIL("attention (tcgen05): q, out and the caches must be 16-byte aligned, q's row stride a multiple of 8");
+    if (!g_attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) {
+            snprintf(g_kllm_err, sizeof(g_kllm_err), "attention (tcgen05): %d bytes of shared memory refused: %s",
+                     SMEM_BYTES, cudaGetErrorString(e));
+            return (int)e;
+        }
+        g_attr_set = true;
+    }
+    const int tpt = ROWS / gs;
+    const int max_tiles = n_tokens / tpt + n_requests;
+    if (n_kv > 65535) KLLM_FAIL("attention: grid too large");
+    const float sl2e = scale * 1.4426950408889634f;
+    kllm_launch((attn_prefill_tc5_kernel), dim3(max_tiles, n_kv), dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream,
+                (bf16*)out, (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache, q_start, start_pos,
+                block_table, max_blocks, n_requests, n_heads, n_kv, page_size, window, sl2e, tpt, status);
+    KLLM_LAUNCH_STATUS();
+}

@@ -42,6 +42,7 @@ def main(argv=None) -> int:
 
     import numpy as np
     import torch
+    from .. import kernels
     from .engine import Engine, Options
     from .step import StepEntry
     from ..config.base import load_config
@@ -79,6 +80,7 @@ def main(argv=None) -> int:
                 if rid in live:
                     eng.cache.close(live.pop(rid))
             torch.cuda.synchronize()
+            kernels.check_status(eng.device)
             print(f"done {step}", flush=True)
     eng.close()
     return 0

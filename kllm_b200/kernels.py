@@ -10,6 +10,7 @@ its own count).
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -168,6 +169,8 @@ def attention_generic(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, 
 
 
 TC_HEAD_DIMS = tuple(range(16, 129, 16))     # head sizes of the tensor-core attention library
+TCGEN05_HEAD_DIMS = (64, 128)                # head sizes of the tcgen05 prefill attention
+USE_TCGEN05 = os.environ.get("KLLM_B200_TCGEN05", "1") != "0"
 SM_COUNT = 148
 
 
@@ -194,7 +197,8 @@ def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: 
               scale: float) -> None:
     """Causal GQA attention of the step's tokens over the paged cache, by the
     kernel that fits: bfloat16 with a head size in TC_HEAD_DIMS runs on tensor cores
-    (the decode form when every request brings one token, else the prefill form);
+    (the decode form when every request brings one token, else the prefill form: on
+    tcgen05 for head sizes 64 and 128, on mma.sync for the other multiples of 16);
     float32, other head sizes or very wide groups run the generic kernel."""
     group = n_heads // max(1, n_kv)
     tc = q.dtype == torch.bfloat16 and head_dim in TC_HEAD_DIMS
@@ -202,6 +206,9 @@ def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: 
         return attention_decode(out, q, kcache, vcache, ctx.positions, ctx.token_req, block_table, n_heads,
                                 n_kv, head_dim, window, scale,
                                 decode_splits(ctx.n_tokens, n_kv, ctx.split_bound or ctx.max_ctx))
+    if tc and USE_TCGEN05 and head_dim in TCGEN05_HEAD_DIMS and group <= 128:
+        return attention_prefill_tcgen05(out, q, kcache, vcache, ctx.q_start, ctx.start_pos, block_table,
+                                         ctx.n_requests, n_heads, n_kv, head_dim, window, scale)
     if tc and group <= 64:
         return attention_prefill(out, q, kcache, vcache, ctx.q_start, ctx.start_pos, block_table,
                                  ctx.n_requests, n_heads, n_kv, head_dim, window, scale)
@@ -284,6 +291,41 @@ def attention_prefill(out, q, kcache, vcache, q_start, start_pos, block_table, n
                                     q.shape[0], int(n_requests), n_heads, n_kv, head_dim, kcache.shape[2],
                                     int(window or 0), ctypes.c_float(scale), _stream())
     _check(lib, "attention_tc", rc)
+
+
+def attention_prefill_tcgen05(out, q, kcache, vcache, q_start, start_pos, block_table, n_requests, n_heads, n_kv,
+                              head_dim, window, scale) -> None:
+    """Attention of portions on tcgen05 tensor cores with TMEM accumulators (head size
+    64 or 128); same contract as ``attention_prefill``."""
+    _cuda(out, q, kcache, vcache, q_start, start_pos, block_table)
+    _check_attention(out, q, kcache, vcache, block_table, n_kv, head_dim)
+    _i32(q_start, "q_start"); _i32(start_pos, "start_pos")
+    lib = load_library("attention_tcgen05", {"KLLM_HD": head_dim})
+    rc = lib.kllm_attention_prefill_tcgen05(_p(out), _p(q), ctypes.c_int64(q.stride(0)), _p(kcache), _p(vcache),
+                                            _p(q_start), _p(start_pos), _p(block_table), block_table.shape[1],
+                                            q.shape[0], int(n_requests), n_heads, n_kv, head_dim, kcache.shape[2],
+                                            int(window or 0), ctypes.c_float(scale), _p(status_word(q.device)),
+                                            _stream())
+    _check(lib, "attention_tcgen05", rc)
+
+
+_status_words = {}      # device index -> int32 tensor that kernels set when a bounded wait runs out
+
+
+def status_word(device) -> torch.Tensor:
+    dev = torch.device(device)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    if idx not in _status_words:
+        _status_words[idx] = torch.zeros(1, dtype=torch.int32, device=dev)
+    return _status_words[idx]
+
+
+def check_status(device) -> None:
+    """Raise if a kernel reported that a bounded wait (on an mbarrier) ran out; its
+    results are then not valid.  Synchronises the device."""
+    if int(status_word(device).item()) != 0:
+        status_word(device).zero_()
+        raise KernelError("a kernel gave up waiting on an mbarrier; its results are not valid")
 
 
 def silu_mul(out: torch.Tensor, gate: torch.Tensor, up: torch.Tensor) -> None:
