@@ -120,24 +120,39 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ unsigned swz(int r, int ch) {
     return (unsigned)((r >> 3) * 1024 + (r & 7) * 128 + ((ch ^ (r & 7)) << 4));
 }
+// 2^x for x <= 0 (and -inf -> 0): the hardware approximation, one instruction
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// keys key0 .. key0+63 of kv head g into a stage: K panels then V panels
+// keys key0 .. key0+63 of kv head g into a stage: K panels then V panels.  A thread
+// keeps its 16-byte piece of the row and walks the rows, so that a row's page is
+// looked up once per thread and row.
 __device__ __forceinline__ void load_kv(unsigned stage, const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                                         const int* __restrict__ table, int key0, int hi, int g, int n_kv, int page_size) {
-    for (int c = threadIdx.x; c < TILE * (HD / 8); c += THREADS) {
-        const int row = c / (HD / 8), piece = c - row * (HD / 8);     // piece: 16 bytes of the head's HD dims
+    constexpr int PIECES = HD / 8;                        // 16-byte pieces of a row
+    constexpr int ROWS_PER_PASS = THREADS / PIECES;       // 16 (HD 64) or 8 (HD 128)
+    const int piece = threadIdx.x % PIECES, r0 = threadIdx.x / PIECES;
+    const unsigned col = (unsigned)((piece >> 3) * (TILE * 128));
+    const int64_t head_off = (int64_t)g * page_size * HD + piece * 8;
+    const int64_t page_elems = (int64_t)n_kv * page_size * HD;
+#pragma unroll
+    for (int j = 0; j < TILE / ROWS_PER_PASS; j++) {
+        const int row = r0 + j * ROWS_PER_PASS;
         const int key = key0 + row;
         const bool valid = key < hi;
         int64_t off = 0;
         if (valid) {
             const int lp = key / page_size;
-            off = (((int64_t)table[lp] * n_kv + g) * page_size + (key - lp * page_size)) * HD + piece * 8;
+            off = (int64_t)table[lp] * page_elems + head_off + (int64_t)(key - lp * page_size) * HD;
         }
-        const unsigned dst = (unsigned)((piece >> 3) * (TILE * 128)) + swz(row, piece & 7);
+        const unsigned dst = col + swz(row, piece & 7);
         cp_async16(stage + dst, kcache + off, valid);
         cp_async16(stage + KV_BYTES + dst, vcache + off, valid);
     }
@@ -266,21 +281,26 @@ attn_prefill_tc5_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int6
             tmem_ld32(t_s + 32, s2[1]);
             tmem_ld_wait();
         }
-        float mx = -INFINITY;
+        // the mask matters only where the tile crosses this row's diagonal or window edge
+        if (key0 + TILE - 1 > p_row || key0 < w_row) {
 #pragma unroll
-        for (int j = 0; j < TILE; j++) {
-            const int key = key0 + j;
-            if (key > p_row || key < w_row) s[j] = -INFINITY;
-            mx = fmaxf(mx, s[j]);
+            for (int j = 0; j < TILE; j++) {
+                const int key = key0 + j;
+                if (key > p_row || key < w_row) s[j] = -INFINITY;
+            }
         }
+        float mx = s[0];
+#pragma unroll
+        for (int j = 1; j < TILE; j++) mx = fmaxf(mx, s[j]);
         const float m_new = fmaxf(m_run, mx);
         const float m_use = (m_new == -INFINITY) ? 0.f : m_new;       // a row that has seen no key yet
         const float corr = exp2f((m_run - m_use) * scale_log2e);
         m_run = m_new;
+        const float neg = -m_use * scale_log2e;                       // p = 2^(s * scale - m * scale): one FMA each
         float sum = 0.f;
 #pragma unroll
         for (int j = 0; j < TILE; j++) {
-            s[j] = exp2f((s[j] - m_use) * scale_log2e);
+            s[j] = fast_exp2(fmaf(s[j], scale_log2e, neg));
             sum += s[j];
         }
         l_run = l_run * corr + sum;
