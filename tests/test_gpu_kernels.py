@@ -68,6 +68,11 @@ def test_add_rmsnorm(dtype, d):
     summed = x0.astype(np.float64) + res_s
     close(x, summed, "float32", "residual sum is float32 in both dtypes")
     close(out, plain.rmsnorm(summed, gain, eps), dtype, "norm")
+    if dtype == "bfloat16":            # a float32 residual beside a bfloat16 result
+        x = dev(x0)
+        kernels.add_rmsnorm(x, dev(res), out, dev(gain), eps)
+        close(x, x0.astype(np.float64) + res, "float32", "float32 residual, unrounded")
+        close(out, plain.rmsnorm(x0.astype(np.float64) + res, gain, eps), dtype, "norm after a float32 residual")
     # no residual: x untouched
     x = dev(x0)
     kernels.add_rmsnorm(x, None, out, dev(gain), eps)
@@ -93,6 +98,13 @@ def test_silu_mul_on_strided_halves(dtype):
     kernels.silu_mul(out, t[:, :f], t[:, f:])
     s = as_stored(gu, dtype)
     close(out, plain.silu(s[:, :f]) * s[:, f:], dtype)
+    if dtype == "bfloat16":            # float32 gate/up beside a bfloat16 result (vectorised and plain forms)
+        for width in (f, f - 1):
+            t32 = dev(gu)
+            out = torch.empty((n, width), dtype=torch.bfloat16, device="cuda")
+            kernels.silu_mul(out, t32[:, :width], t32[:, f:f + width])
+            g64 = gu.astype(np.float64)
+            close(out, plain.silu(g64[:, :width]) * g64[:, f:f + width], dtype, f"float32 inputs, width {width}")
 
 
 def paged(k, v, page_size, n_pages, rng, dtype, lengths):

@@ -150,6 +150,87 @@ def test_embedding_and_head_parts(dtype):
     close(logits, stored(table, dtype)[[52, 0, 7]] @ stored(table, dtype).T, dtype)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("rotary_dim", [None, 8])
+def test_rotary_part_rotates_and_stores(dtype, rotary_dim):
+    """The position part alone: q rotated in place, rotated k and v stored at the
+    pages' slots; a partial rotary width leaves the other dims alone."""
+    from kllm_b200.cache import CacheManager
+    from kllm_b200.parts.spec import PagedKVNeed, PartSpec, part_factory
+    rng = np.random.default_rng(7)
+    H, G, hd, n, start = 3, 1, 16, 9, 5
+    params = {"head_dim": hd, "theta": 50.0}
+    if rotary_dim:
+        params["rotary_dim"] = rotary_dim
+    part = part_factory("position", "rotary")(PartSpec("rotary", "", params), env_for(dtype, 48))
+    rot = rotary_dim or hd
+    assert (part.full_rotary_table() is None) == (rot != hd)
+    cache = CacheManager([PagedKVNeed(G, hd)], page_size=4, num_pages=6, max_requests=1, dtype=DT[dtype], device="cuda")
+    req = cache.open()
+    cache.reserve(req, start + n)
+    cache.commit(req, start)
+    qkv = rng.standard_normal((n, (H + 2 * G) * hd)).astype(np.float32)
+    t = torch.from_numpy(qkv).cuda().to(DT[dtype])
+    q, k, v = t[:, :H * hd], t[:, H * hd:(H + G) * hd], t[:, (H + G) * hd:]
+    ctx = one_request_context(n, start)
+    table = torch.tensor([req.tables[0]], dtype=torch.int32, device="cuda")
+    lc = cache.layer_caches({0: table})[0]
+    part.apply(q, k, v, ctx, lc, H, G)
+    sq = stored(qkv, dtype)
+    pos = np.arange(start, start + n)
+
+    def rotated(x, heads):
+        x = x.reshape(n, heads, hd).copy()
+        x[:, :, :rot] = plain.rope(x[:, :, :rot].reshape(n, heads * rot), pos, heads, rot, 50.0).reshape(n, heads, rot)
+        return x.reshape(n, heads * hd)
+
+    close(q, rotated(sq[:, :H * hd], H), dtype, "q")
+    kw = rotated(sq[:, H * hd:(H + G) * hd], G).reshape(n, G, hd)
+    for i, p_ in enumerate(pos):
+        pg, slot = req.tables[0][p_ // 4], p_ % 4
+        close(lc.k[pg, :, slot], kw[i], dtype, f"k at position {p_}")
+        close(lc.v[pg, :, slot], sq[i, (H + G) * hd:].reshape(G, hd), dtype, f"v at position {p_}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n", [3, 40])
+def test_block_part_both_routes(dtype, n):
+    """A whole pre-norm block against the plain layer: n = 3 takes the fused route in
+    bfloat16 (norm and residual sum inside the products), n = 40 the general one."""
+    from kllm_b200.cache import CacheManager
+    from kllm_b200.parts.spec import BlockSpec, PartSpec, part_factory
+    rng = np.random.default_rng(8)
+    d, H, G, hd, f = 64, 4, 2, 16, 96
+    norm = {"width": d, "eps": 1e-5}
+    spec = BlockSpec("pre_norm", "model.layers.0",
+                     PartSpec("paged_attention", "model.layers.0.self_attn", {
+                         "hidden": d, "n_heads": H, "n_kv_heads": G, "head_dim": hd, "window": None,
+                         "position": PartSpec("rotary", "", {"head_dim": hd, "theta": 1e4})}),
+                     PartSpec("gated_mlp", "model.layers.0.mlp", {"hidden": d, "intermediate": f, "activation": "silu"}),
+                     PartSpec("rmsnorm", "model.layers.0.input_layernorm", dict(norm)),
+                     PartSpec("rmsnorm", "model.layers.0.post_attention_layernorm", dict(norm)))
+    block = part_factory("block", "pre_norm")(spec, env_for(dtype, d))
+    cfg = {"num_hidden_layers": 1, "hidden_size": d, "num_attention_heads": H, "num_key_value_heads": G, "head_dim": hd,
+           "intermediate_size": f, "vocab_size": 8, "rope_theta": 1e4, "rms_norm_eps": 1e-5}
+    w = plain.random_weights(cfg, 3, gain_std=0.1, std=0.15)
+    bind(block, w, dtype)
+    cache = CacheManager([block.mixer.cache_need()], page_size=16, num_pages=4, max_requests=1, dtype=DT[dtype], device="cuda")
+    req = cache.open()
+    cache.reserve(req, n)
+    x0 = rng.standard_normal((n, d)).astype(np.float32)
+    x = torch.from_numpy(x0).cuda()
+    ctx = one_request_context(n, 0)
+    table = torch.tensor([req.tables[0]], dtype=torch.int32, device="cuda")
+    pending = block.forward(x, None, ctx, cache.layer_caches({0: table})[0])
+    got = x if pending is None else x + pending.float()
+    ws = {k: (stored(v, dtype) if v.ndim == 2 else v) for k, v in w.items()}
+    rnd = plain.round_act_bf16 if dtype == "bfloat16" else (lambda a: a)
+    want = plain.decoder_layer(x0.astype(np.float64), ws, 0, plain.normalise_config(cfg), np.arange(n), rnd)
+    close(got, want, dtype, f"block output, {n} tokens")
+    if dtype == "bfloat16" and n == 3:
+        assert pending is None, "a small bfloat16 step is expected to take the fused route"
+
+
 # ---- a toy architecture defined in the test -----------------------------------
 
 class RunningMeanMixer:
