@@ -426,6 +426,67 @@ def skinny_gemm(weight: torch.Tensor, *, x: Optional[torch.Tensor] = None, x_f32
     return out
 
 
+def _gemm_args(x, weight, weight_up, out, epilogue):
+    return (_p(x), ctypes.c_int64(x.stride(0)), _p(weight), ctypes.c_int64(weight.stride(0)), _p(weight_up),
+            x.shape[0], weight.shape[0], x.shape[1], _p(out), ctypes.c_int64(out.stride(0)), _EPI[epilogue])
+
+
+def gemm_fits(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str = "bf16",
+              weight_up: Optional[torch.Tensor] = None) -> bool:
+    """Whether ``gemm`` takes these operands (bfloat16, dense rows, k and the row strides
+    multiples of 8, 16-byte aligned addresses)."""
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or x.dim() != 2 or weight.dim() != 2:
+        return False
+    if x.stride(1) != 1 or weight.stride(1) != 1 or out.stride(1) != 1 or x.shape[1] != weight.shape[1]:
+        return False
+    if weight_up is not None and (weight_up.dtype != torch.bfloat16 or weight_up.shape != weight.shape
+                                  or weight_up.stride() != weight.stride()):
+        return False
+    lib = load_library("gemm_tcgen05")
+    return bool(lib.kllm_gemm_tcgen05_fits(*_gemm_args(x, weight, weight_up, out, epilogue)))
+
+
+def gemm_pays(n: int, N: int, epilogue: str = "bf16", least: int = 75) -> bool:
+    """Whether ``gemm``'s tiles of 128 rows x 256 accumulator columns would keep the
+    tensor cores of all SMs busy for at least ``least`` percent of the product's time
+    (full tiles over waves x SMs); below that the library product adapts its tiling better."""
+    if not USE_TCGEN05:
+        return False
+    lib = load_library("gemm_tcgen05")
+    return int(lib.kllm_gemm_tcgen05_efficiency(int(n), int(N), _EPI[epilogue])) >= least
+
+
+def gemm(x: torch.Tensor, weight: torch.Tensor, *, epilogue: str = "bf16", out: Optional[torch.Tensor] = None,
+         weight_up: Optional[torch.Tensor] = None, bn: int = 0) -> torch.Tensor:
+    """y = x @ weight^T on the tcgen05 tensor cores (csrc/gemm_tcgen05.cu), x bfloat16
+    [n, K], weight bfloat16 [N, K].
+
+    ``epilogue``: "bf16" / "f32" store y [n, N]; "add" adds y into the float32 ``out``;
+    "swiglu" takes ``weight`` as gate and ``weight_up`` as up matrix and stores
+    silu(gate) * up as bfloat16 [n, N].  ``bn``: accumulator width of a tile (0 = chosen
+    by the tile count).
+    """
+    _cuda(x, weight, weight_up, out)
+    n, N = x.shape[0], weight.shape[0]
+    want = torch.float32 if epilogue in ("f32", "add") else torch.bfloat16
+    if out is None:
+        if epilogue == "add":
+            raise KernelError("gemm: 'add' needs the matrix to add into")
+        out = torch.empty((n, N), dtype=want, device=x.device)
+    if out.dtype != want or out.shape[0] != n or out.shape[1] != N:
+        raise KernelError("gemm: out has the wrong dtype or shape")
+    if epilogue == "swiglu" and weight_up is None:
+        raise KernelError("gemm: swiglu needs an up matrix like the gate matrix")
+    if not gemm_fits(x, weight, out, epilogue, weight_up):
+        raise KernelError(f"gemm: operands {tuple(x.shape)} x {tuple(weight.shape)} (strides {x.stride()}, "
+                          f"{weight.stride()}, out {out.stride()}) are not supported")
+    lib = load_library("gemm_tcgen05")
+    rc = lib.kllm_gemm_tcgen05(*_gemm_args(x, weight, weight_up, out, epilogue), int(bn), _p(status_word(x.device)),
+                               _stream())
+    _check(lib, "gemm_tcgen05", rc)
+    return out
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """y = x @ weight^T through the vendor GEMM library (cuBLAS, via torch.mm), as

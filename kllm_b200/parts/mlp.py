@@ -9,7 +9,9 @@ Optional ``forward_residual(x, norm, ctx) -> bool``: as for mixers, the part rea
 the float32 residual stream, applies ``norm`` inside its first kernel and adds its
 result into x, or returns False.  Here, for steps of a few tokens, the gate/up
 product carries the norm as prologue and the activation as epilogue, the down
-product adds into x (csrc/skinny_gemm.cu).
+product adds into x (csrc/skinny_gemm.cu).  Large portions in bfloat16 run gate, up
+and the activation as one tensor-core kernel (csrc/gemm_tcgen05.cu) where its tiles
+fill the GPU; everything else uses the library product and the activation kernel.
 
 Interface of a feed-forward part: ``forward(xn, ctx) -> [n, hidden]`` in float32 or
 the model dtype.
@@ -48,9 +50,16 @@ class GatedMLP:
     def forward(self, xn, ctx):
         # gate and up stay float32 until the activation has been applied; the down
         # projection's float32 result goes into the residual stream unrounded
-        gu = kernels.linear(xn, self.w_gate_up, out_dtype=torch.float32)
-        act = torch.empty((xn.shape[0], self.inter), dtype=self.dtype, device=xn.device)
-        kernels.silu_mul(act, gu[:, :self.inter], gu[:, self.inter:])
+        n = xn.shape[0]
+        act = torch.empty((n, self.inter), dtype=self.dtype, device=xn.device)
+        w_gate, w_up = self.w_gate_up[:self.inter], self.w_gate_up[self.inter:]
+        if (self.dtype == torch.bfloat16 and kernels.gemm_pays(n, self.inter, "swiglu")
+                and kernels.gemm_fits(xn, w_gate, act, "swiglu", w_up)):
+            # large portions: both products and the activation in one tcgen05 kernel
+            kernels.gemm(xn, w_gate, weight_up=w_up, epilogue="swiglu", out=act)
+        else:
+            gu = kernels.linear(xn, self.w_gate_up, out_dtype=torch.float32)
+            kernels.silu_mul(act, gu[:, :self.inter], gu[:, self.inter:])
         return kernels.linear(act, self.w_down, out_dtype=torch.float32)
 
 

@@ -459,6 +459,59 @@ def test_skinny_gemm_prologues_and_epilogues(n, N, K):
     close(got, plain.round_act_bf16(plain.rmsnorm(big[:n], gain, 1e-5)) @ ws.T, "bfloat16", "norm prologue, no gather")
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (200, 264, 136), (77, 520, 72), (300, 96, 1000), (1000, 1544, 520)])
+@pytest.mark.parametrize("bn", [0, 256, 192, 64])
+def test_tcgen05_gemm_epilogues(M, N, K, bn):
+    """The tensor-core product with each epilogue, at sizes with ragged edges in every
+    direction (rows, columns, k) and tiles narrower than the matrix and wider."""
+    from kllm_b200 import kernels
+    rng = np.random.default_rng(M + N + K)
+    w = (rng.standard_normal((N, K)) * 0.05).astype(np.float32)
+    w2 = (rng.standard_normal((N, K)) * 0.05).astype(np.float32)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    ws, w2s, xs = as_stored(w, "bfloat16"), as_stored(w2, "bfloat16"), as_stored(x, "bfloat16")
+    wt, w2t, xt = dev(w, torch.bfloat16), dev(w2, torch.bfloat16), dev(x, torch.bfloat16)
+    want = xs @ ws.T
+    close(kernels.gemm(xt, wt, epilogue="f32", bn=bn), want, "float32", "f32 store")
+    close(kernels.gemm(xt, wt, epilogue="bf16", bn=bn), want, "bfloat16", "bf16 store")
+    base = rng.standard_normal((M, N)).astype(np.float32)
+    acc = dev(base)
+    kernels.gemm(xt, wt, epilogue="add", out=acc, bn=bn)
+    close(acc, base.astype(np.float64) + want, "float32", "residual add")
+    got = kernels.gemm(xt, wt, weight_up=w2t, epilogue="swiglu", bn=bn)
+    close(got, plain.silu(want) * (xs @ w2s.T), "bfloat16", "swiglu")
+    kernels.check_status("cuda")
+
+
+def test_tcgen05_gemm_rows_do_not_depend_on_the_batch():
+    """A row's result is the same bits alone in a small batch and among many rows."""
+    from kllm_b200 import kernels
+    rng = np.random.default_rng(5)
+    w = dev((rng.standard_normal((300, 200)) * 0.05).astype(np.float32), torch.bfloat16)
+    x = dev(rng.standard_normal((333, 200)).astype(np.float32), torch.bfloat16)
+    whole = kernels.gemm(x, w, epilogue="f32")
+    part = kernels.gemm(x[130:141], w, epilogue="f32")
+    assert torch.equal(whole[130:141], part)
+
+
+def test_tcgen05_gemm_refusals():
+    from kllm_b200 import kernels
+    w = torch.zeros(64, 36, device="cuda", dtype=torch.bfloat16)
+    x = torch.zeros(40, 36, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(kernels.KernelError, match="not supported"):
+        kernels.gemm(x, w)                                    # k is no multiple of 8
+    w = torch.zeros(64, 64, device="cuda", dtype=torch.bfloat16)
+    x = torch.zeros(40, 64, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(kernels.KernelError, match="accumulator width"):
+        kernels.gemm(x, w, bn=100)
+    with pytest.raises(kernels.KernelError, match="swiglu needs"):
+        kernels.gemm(x, w, epilogue="swiglu")
+    with pytest.raises(kernels.KernelError, match="add"):
+        kernels.gemm(x, w, epilogue="add")
+    assert not kernels.gemm_fits(x.float(), w, torch.empty(40, 64, device="cuda"), "f32")
+    assert kernels.gemm_pays(2048, 5632, "swiglu") and not kernels.gemm_pays(40, 96, "swiglu")
+
+
 def test_skinny_gemm_refusals():
     from kllm_b200 import kernels
     w = torch.zeros(16, 40, device="cuda", dtype=torch.bfloat16)

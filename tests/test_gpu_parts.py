@@ -150,6 +150,36 @@ def test_embedding_and_head_parts(dtype):
     close(logits, stored(table, dtype)[[52, 0, 7]] @ stored(table, dtype).T, dtype)
 
 
+@pytest.mark.parametrize("n", [40, 300])
+def test_feed_forward_part_on_the_tensor_core_route(n, monkeypatch):
+    """The gated feed-forward with gate, up and activation in one tcgen05 kernel, the
+    route of large portions, forced here for a small one."""
+    from kllm_b200 import kernels
+    from kllm_b200.parts.spec import PartSpec, part_factory
+    rng = np.random.default_rng(9)
+    d, f = 72, 200
+    part = part_factory("feed_forward", "gated_mlp")(
+        PartSpec("gated_mlp", "mlp", {"hidden": d, "intermediate": f, "activation": "silu"}), env_for("bfloat16", d))
+    w = {f"mlp.{k}_proj.weight": (rng.standard_normal(shape) * 0.1).astype(np.float32)
+         for k, shape in (("gate", (f, d)), ("up", (f, d)), ("down", (d, f)))}
+    bind(part, w, "bfloat16")
+    xn = rng.standard_normal((n, d)).astype(np.float32)
+    xt = torch.from_numpy(xn).cuda().to(torch.bfloat16)
+    monkeypatch.setattr(kernels, "gemm_pays", lambda *a, **k: False)
+    library = part.forward(xt, None)
+    monkeypatch.setattr(kernels, "gemm_pays", lambda *a, **k: True)
+    calls, real_gemm = [], kernels.gemm
+    monkeypatch.setattr(kernels, "gemm", lambda *a, **k: calls.append(k.get("epilogue")) or real_gemm(*a, **k))
+    fused = part.forward(xt, None)
+    assert calls == ["swiglu"]
+    xs = stored(xn, "bfloat16")
+    g, u = xs @ stored(w["mlp.gate_proj.weight"], "bfloat16").T, xs @ stored(w["mlp.up_proj.weight"], "bfloat16").T
+    want = plain.round_act_bf16(plain.silu(g) * u) @ stored(w["mlp.down_proj.weight"], "bfloat16").T
+    close(fused, want, "bfloat16", "fused route")
+    close(library, want, "bfloat16", "library route")
+    kernels.check_status("cuda")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("rotary_dim", [None, 8])
 def test_rotary_part_rotates_and_stores(dtype, rotary_dim):
