@@ -77,6 +77,26 @@ static inline cudaError_t kllm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// ---- warming L2 for the kernel after this one ---------------------------------
+// A decode step streams each weight matrix once, in kernels too short to keep the
+// memory system full: each starts with empty queues and ends with a tail.  A kernel
+// may therefore be handed the weights that a LATER kernel of the chain will stream;
+// its CTAs ask for them to be brought into L2 (cp.async.bulk.prefetch.L2: no
+// destination, no completion to wait for) before doing their own work, so that DRAM
+// stays busy through this kernel's latency-bound phases and the later kernel reads
+// from L2.  ptr must be 16-byte aligned; the last bytes % 16 are left out.
+__device__ __forceinline__ void l2_prefetch_slice(const void* ptr, long long bytes, int threads) {
+    if (!ptr || bytes < 16) return;
+    constexpr long long CHUNK = 4096;
+    const long long per_cta = ((bytes / gridDim.x + CHUNK) / CHUNK) * CHUNK;
+    const long long lo = (long long)blockIdx.x * per_cta;
+    const long long hi = min(bytes & ~15LL, lo + per_cta);
+    for (long long o = lo + (long long)threadIdx.x * CHUNK; o < hi; o += (long long)threads * CHUNK) {
+        const unsigned sz = (unsigned)min(CHUNK, hi - o);
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"((const char*)ptr + o), "r"(sz) : "memory");
+    }
+}
+
 typedef __nv_bfloat16 bf16;
 
 __device__ __forceinline__ float to_f32(float v) { return v; }

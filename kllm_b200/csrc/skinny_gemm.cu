@@ -57,6 +57,8 @@ struct Args {
     bf16* y_bf16;         // STORE_BF16, SWIGLU
     float* y_f32;         // STORE_F32, ADD_F32
     int64_t y_stride;
+    const void* prefetch;   // optional: weights of a later kernel, to be brought into L2
+    int64_t prefetch_bytes;
 };
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -123,6 +125,7 @@ skinny_gemm_kernel(const Args a) {
 
     int cur_tile = blockIdx.x, cur_b = 0;     // the batch that sits in the buffer used next
     if (cur_tile < n_tiles) load_batch(buf0a, buf0b, cur_tile, 0);   // weights do not depend on X: start them first
+    l2_prefetch_slice(a.prefetch, a.prefetch_bytes, THREADS);
     griddep_wait();        // X (and, for ADD_F32, the matrix added into) come from the kernels before
     griddep_launch();
 
@@ -321,10 +324,12 @@ extern "C" int kllm_skinny_gemm_fits(int n, int K) {
 // rows[r] when rows is given), normalised with gain [K] and eps.
 // epilogue 0/3: y_bf16 [n, N] at y_stride (3: w = gate [N, K], w_up = up [N, K]);
 // epilogue 1: y_f32 written; epilogue 2: y_f32 += result.
+// prefetch: optional, `prefetch_bytes` bytes that a later kernel will stream; they are
+// requested into L2 before this kernel's own work.
 extern "C" int kllm_skinny_gemm(const void* w, const void* w_up, int N, int K, int n, const void* x_bf16,
                                 int64_t x_stride, const float* x_f32, const float* gain, const int* rows,
                                 float eps, void* y_bf16, float* y_f32, int64_t y_stride, int prologue,
-                                int epilogue, void* stream) {
+                                int epilogue, const void* prefetch, int64_t prefetch_bytes, void* stream) {
     if (n <= 0 || N <= 0) return 0;
     if (!kllm_skinny_gemm_fits(n, K))
         KLLM_FAIL("skinny_gemm: %d rows of width %d not supported (1..16 rows, width a multiple of 32 that fits "
@@ -340,6 +345,8 @@ extern "C" int kllm_skinny_gemm(const void* w, const void* w_up, int N, int K, i
     a.w = (const bf16*)w; a.w_up = (const bf16*)w_up; a.N = N; a.K = K; a.n = n;
     a.x_bf16 = (const bf16*)x_bf16; a.x_stride = x_stride; a.x_f32 = x_f32; a.gain = gain; a.rows = rows; a.eps = eps;
     a.y_bf16 = (bf16*)y_bf16; a.y_f32 = y_f32; a.y_stride = y_stride;
+    if (prefetch && ((uintptr_t)prefetch & 15)) KLLM_FAIL("skinny_gemm: the matrix to prefetch must be 16-byte aligned");
+    a.prefetch = prefetch; a.prefetch_bytes = prefetch ? prefetch_bytes : 0;
     cudaStream_t s = (cudaStream_t)stream;
     if (n <= 8) {
         if (prologue == X_BF16) return launch_epi<1, X_BF16>(a, epilogue, s);

@@ -170,6 +170,7 @@ def attention_generic(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, 
 
 TC_HEAD_DIMS = tuple(range(16, 129, 16))     # head sizes of the tensor-core attention library
 TCGEN05_HEAD_DIMS = (64, 128)                # head sizes of the tcgen05 prefill attention
+PREFETCH_L2 = os.environ.get("KLLM_B200_PREFETCH", "1") != "0"   # kernels warm L2 for the kernel after them
 USE_TCGEN05 = os.environ.get("KLLM_B200_TCGEN05", "1") != "0"
 SM_COUNT = 148
 
@@ -375,18 +376,28 @@ def skinny_fits(n: int, k: int, dtype: torch.dtype) -> bool:
     return 8 * nt * row * 2 + 16 * 16 * 8 * nt * 4 <= 227 * 1024     # X rows + the 16 warps' partial tiles
 
 
+def _prefetch_args(t: Optional[torch.Tensor]):
+    if t is None or not PREFETCH_L2:
+        return None, ctypes.c_int64(0)
+    if not t.is_contiguous():
+        raise KernelError("prefetch: the tensor to bring into L2 must be contiguous")
+    return _p(t), ctypes.c_int64(t.numel() * t.element_size())
+
+
 def skinny_gemm(weight: torch.Tensor, *, x: Optional[torch.Tensor] = None, x_f32: Optional[torch.Tensor] = None,
                 gain: Optional[torch.Tensor] = None, eps: float = 0.0, rows: Optional[torch.Tensor] = None,
                 n_rows: Optional[int] = None, weight_up: Optional[torch.Tensor] = None, epilogue: str = "bf16",
-                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                out: Optional[torch.Tensor] = None, prefetch: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y = X @ weight^T for at most 16 rows, the weights streamed once (csrc/skinny_gemm.cu).
 
     X is either ``x`` (bfloat16 [n, K]) or rmsnorm(``x_f32``) * ``gain`` computed inside
     the kernel (rows ``rows`` of x_f32 when given).  ``epilogue``: "bf16" / "f32" store
     y [n, N]; "add" adds y into the float32 ``out``; "swiglu" takes ``weight`` as gate and
     ``weight_up`` as up matrix and stores silu(gate) * up as bfloat16 [n, N].
+    ``prefetch``: a contiguous tensor that a later kernel will stream (the next weight
+    matrix); the kernel asks for it to be brought into L2 before its own work.
     """
-    _cuda(weight, x, x_f32, gain, rows, weight_up, out)
+    _cuda(weight, x, x_f32, gain, rows, weight_up, out, prefetch)
     N, K = weight.shape
     if weight.dtype != torch.bfloat16 or not weight.is_contiguous():
         raise KernelError("skinny_gemm: the weight must be contiguous bfloat16")
@@ -421,7 +432,8 @@ def skinny_gemm(weight: torch.Tensor, *, x: Optional[torch.Tensor] = None, x_f32
     y32 = out if want == torch.float32 else None
     rc = lib.kllm_skinny_gemm(_p(weight), _p(weight_up), N, K, n, _p(x),
                               ctypes.c_int64(x.stride(0) if x is not None else 0), _p(x_f32), _p(gain), _p(rows),
-                              ctypes.c_float(eps), _p(y16), _p(y32), ctypes.c_int64(out.stride(0)), pro, epi, _stream())
+                              ctypes.c_float(eps), _p(y16), _p(y32), ctypes.c_int64(out.stride(0)), pro, epi,
+                              *_prefetch_args(prefetch), _stream())
     _check(lib, "skinny_gemm", rc)
     return out
 
