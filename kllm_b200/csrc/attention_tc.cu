@@ -60,6 +60,7 @@ constexpr int STAGE_ELEMS = 2 * TILE * ROW;                       // K tile then
 // requested whole before the first tile is used).  Prefill keeps 3 stages and more
 // CTAs per SM.
 constexpr int DEC_STAGES_DEEP = HD <= 64 ? 5 : (HD <= 96 ? 4 : 3);   // few CTAs: everything in flight at once
+constexpr int DEC_PAGES = 256;                                        // block-table entries of a range kept in shared memory
 constexpr int DEC_STAGES_WIDE = 3;                                    // many CTAs: more of them per SM
 constexpr int PRE_STAGES = 3;
 constexpr int PRE_SMEM_BYTES = PRE_STAGES * STAGE_ELEMS * 2;
@@ -96,9 +97,11 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 // Keys key0 .. key0+63 of kv head g into one stage (K tile, then V tile).  Rows at
 // or past `hi` are zero-filled.
+// `table` holds the request's pages from logical page `page_base` on (the block table
+// itself with base 0, or a copy of the needed slice in shared memory).
 __device__ __forceinline__ void load_tile(bf16* stage, const bf16* __restrict__ kcache,
-                                          const bf16* __restrict__ vcache, const int* __restrict__ table,
-                                          int key0, int hi, int g, int n_kv, int page_size) {
+                                          const bf16* __restrict__ vcache, const int* table,
+                                          int key0, int hi, int g, int n_kv, int page_size, int page_base = 0) {
     bf16* sk = stage;
     bf16* sv = stage + TILE * ROW;
     for (int c = threadIdx.x; c < TILE * CHUNKS; c += THREADS) {
@@ -108,7 +111,7 @@ __device__ __forceinline__ void load_tile(bf16* stage, const bf16* __restrict__ 
         int64_t off = 0;
         if (valid) {
             const int lp = key / page_size;
-            const int page = table[lp];
+            const int page = table[lp - page_base];
             off = (((int64_t)page * n_kv + g) * page_size + (key - lp * page_size)) * HD + ch * 8;
         }
         cp_async16(sk + row * ROW + ch * 8, kcache + off, valid);
@@ -174,6 +177,7 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
     __shared__ int s_is_last;
+    __shared__ int s_pages[DEC_PAGES];
     __shared__ bf16 s_newkv[2 * HD];       // the writer CTA's rotated new key, then the new value
     // Plain form: the kernel before this one wrote this step's keys into the pages.
     // Fused form: nobody but this kernel writes this layer's pages, so their tiles may
@@ -191,11 +195,39 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
     const int* table = block_table + (int64_t)token_req[t] * max_blocks;
     const int ntiles = lo < hi ? (hi - lo + TILE - 1) / TILE : 0;
 
+    // This range's slice of the block table, read once and together: otherwise every
+    // tile's copies would wait for their own look-up, one memory round trip after the other.
+    const int* pages = table;
+    int page_base = 0;
+    if (ntiles > 0) {
+        const int first = lo / page_size, count = (hi - 1) / page_size - first + 1;
+        if (count <= DEC_PAGES) {
+            for (int i = threadIdx.x; i < count; i += THREADS) s_pages[i] = table[first + i];
+            __syncthreads();
+            pages = s_pages;
+            page_base = first;
+        }
+    }
     // the tiles do not depend on the query: start them first
 #pragma unroll
     for (int s = 0; s < DEC_STAGES - 1; s++) {
-        if (s < ntiles) load_tile(smem + s * STAGE_ELEMS, kcache, vcache, table, lo + s * TILE, hi, g, n_kv, page_size);
+        if (s < ntiles) load_tile(smem + s * STAGE_ELEMS, kcache, vcache, pages, lo + s * TILE, hi, g, n_kv, page_size, page_base);
         cp_async_commit();
+    }
+    // neither do the rotation's angles
+    const int p_new = len - 1;
+    constexpr int ROT = (FUSED && KSTEPS >= 2) ? KSTEPS / 2 : 1;
+    float rc[ROT][4][2], rs[ROT][4][2];
+    if (FUSED) {
+        const float* cs = fu.cos_sin + (int64_t)p_new * HD;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS / 2; ks++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int j = ks * 16 + 2 * tq + (i >= 2 ? 8 : 0);
+                const float2 c2 = *reinterpret_cast<const float2*>(cs + j), s2 = *reinterpret_cast<const float2*>(cs + HD / 2 + j);
+                rc[ks][i][0] = c2.x; rc[ks][i][1] = c2.y; rs[ks][i][0] = s2.x; rs[ks][i][1] = s2.y;
+            }
     }
     if (FUSED) { griddep_wait(); griddep_launch(); }
 
@@ -215,7 +247,6 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
     // The CTA whose range holds the token's own position owns the new key and value:
     // it stores them into the page for later steps and, instead of reading them back,
     // writes them over their row of the shared-memory tile once that tile has landed.
-    const int p_new = len - 1;
     const bool writer = FUSED && lo <= p_new && p_new < hi;
     if (FUSED) {
         // rotate_half on the query fragments: dims d and d + HD/2 sit in the same
@@ -226,8 +257,7 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
         for (int ks = 0; ks < KSTEPS / 2; ks++)
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                const int j = ks * 16 + 2 * tq + (i >= 2 ? 8 : 0);
-                const float c0 = cs[j], c1 = cs[j + 1], s0 = cs[HD / 2 + j], s1 = cs[HD / 2 + j + 1];
+                const float c0 = rc[ks][i][0], c1 = rc[ks][i][1], s0 = rs[ks][i][0], s1 = rs[ks][i][1];
                 const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&qa[ks][i]);
                 const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&qa[ks + KSTEPS / 2][i]);
                 const float a0 = __low2float(a), a1 = __high2float(a), b0 = __low2float(b), b1 = __high2float(b);
@@ -236,7 +266,7 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
             }
         if (writer) {
             const int lp = p_new / page_size;
-            const int64_t dst = (((int64_t)table[lp] * n_kv + g) * page_size + (p_new - lp * page_size)) * HD;
+            const int64_t dst = (((int64_t)pages[lp - page_base] * n_kv + g) * page_size + (p_new - lp * page_size)) * HD;
             const bf16* kr = fu.k_new + (int64_t)t * fu.k_stride + (int64_t)g * HD;
             const bf16* vr = fu.v_new + (int64_t)t * fu.v_stride + (int64_t)g * HD;
             for (int j = threadIdx.x; j < HD / 2; j += THREADS) {
@@ -265,7 +295,7 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
         __syncthreads();
         const int nxt = i + DEC_STAGES - 1;
         if (nxt < ntiles)
-            load_tile(smem + (nxt % DEC_STAGES) * STAGE_ELEMS, kcache, vcache, table, lo + nxt * TILE, hi, g, n_kv, page_size);
+            load_tile(smem + (nxt % DEC_STAGES) * STAGE_ELEMS, kcache, vcache, pages, lo + nxt * TILE, hi, g, n_kv, page_size, page_base);
         cp_async_commit();
         bf16* sk = smem + (i % DEC_STAGES) * STAGE_ELEMS;
         bf16* sv = sk + TILE * ROW;
@@ -366,21 +396,55 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
         __syncthreads();
         if (!s_is_last) return;
         __threadfence();
-        for (int e = threadIdx.x; e < gs * HD; e += THREADS) {
-            const int r = e / HD, d = e - r * HD;
-            const int64_t th = (int64_t)t * n_heads + g * gs + r;
-            const float* ml = part_ml + th * num_splits * 2;
+        // Every load of this merge is issued together with the others of its kind, so the
+        // whole merge costs two round trips to L2: first m and l of every (row, split),
+        // then the partial outputs, four dims of all splits per thread.
+        float* w_sm = reinterpret_cast<float*>(smem_raw);       // [gs][num_splits]: m, then the split's weight
+        float* l_sm = w_sm + gs * num_splits;                   // [gs][num_splits]: l
+        float* inv_sm = l_sm + gs * num_splits;                 // [gs]: 1 / sum
+        const int64_t th0 = (int64_t)t * n_heads + (int64_t)g * gs;
+        for (int e = threadIdx.x; e < gs * num_splits; e += THREADS) {
+            const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml) + th0 * num_splits + e);
+            w_sm[e] = ml.x;
+            l_sm[e] = ml.y;
+        }
+        __syncthreads();
+        if (threadIdx.x < gs) {
+            float* wr = w_sm + threadIdx.x * num_splits;
+            const float* lr = l_sm + threadIdx.x * num_splits;
             float M = -INFINITY;
-#pragma unroll 4
-            for (int j = 0; j < num_splits; j++) M = fmaxf(M, __ldcg(ml + 2 * j));
-            float L = 0.f, O = 0.f;
-#pragma unroll 4
+            for (int j = 0; j < num_splits; j++) M = fmaxf(M, wr[j]);
+            float L = 0.f;
             for (int j = 0; j < num_splits; j++) {
-                const float f = exp2f(__ldcg(ml + 2 * j) - M);
-                L += __ldcg(ml + 2 * j + 1) * f;
-                O += __ldcg(part_o + (th * num_splits + j) * HD + d) * f;
+                const float f = exp2f(wr[j] - M);
+                L += lr[j] * f;
+                wr[j] = f;
             }
-            out[th * HD + d] = __float2bfloat16_rn(O / L);
+            inv_sm[threadIdx.x] = 1.f / L;
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < gs * (HD / 4); e += THREADS) {
+            const int r = e / (HD / 4), d = (e - r * (HD / 4)) * 4;
+            const float4* po = reinterpret_cast<const float4*>(part_o + (th0 + r) * num_splits * HD + d);
+            const float* wr = w_sm + r * num_splits;
+            float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int j0 = 0; j0 < num_splits; j0 += 8) {
+                float4 v[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++)
+                    if (j0 + u < num_splits) v[u] = __ldcg(po + (int64_t)(j0 + u) * (HD / 4));
+#pragma unroll
+                for (int u = 0; u < 8; u++)
+                    if (j0 + u < num_splits) {
+                        const float f = wr[j0 + u];
+                        O.x += v[u].x * f; O.y += v[u].y * f; O.z += v[u].z * f; O.w += v[u].w * f;
+                    }
+            }
+            const float inv = inv_sm[r];
+            uint2 pk;
+            pk.x = pack_bf16(O.x * inv, O.y * inv);
+            pk.y = pack_bf16(O.z * inv, O.w * inv);
+            *reinterpret_cast<uint2*>(out + (th0 + r) * HD + d) = pk;
         }
     }
 }
@@ -713,6 +777,9 @@ extern "C" int kllm_attention_decode_fused(void* out, void* part_o, void* part_m
     if (n_heads / n_kv > 16) KLLM_FAIL("attention decode: %d heads per kv head, at most 16", n_heads / n_kv);
     if (num_splits < 1 || (num_splits > 1 && (!part_o || !part_ml || !counters)))
         KLLM_FAIL("attention decode (fused): bad split arguments");
+    if (num_splits > 256) KLLM_FAIL("attention decode (fused): %d splits, at most 256", num_splits);
+    if (((uintptr_t)part_o & 15) || ((uintptr_t)part_ml & 7) || ((uintptr_t)cos_sin & 7) || ((uintptr_t)out & 7))
+        KLLM_FAIL("attention decode (fused): scratch, cos/sin table and out must be 16-byte aligned");
     if (!k_new || !v_new || !cos_sin) KLLM_FAIL("attention decode (fused): k, v and the cos/sin table are needed");
     if (n_tokens > 65535 || n_kv > 65535) KLLM_FAIL("attention decode: grid too large");
     if ((rc = set_attributes())) return rc;

@@ -75,6 +75,15 @@ __device__ __forceinline__ uint4 ldg_stream(const bf16* p) {
     return v;
 }
 
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem, bool valid) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    const int bytes = valid ? 16 : 0;                     // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+}
+
 __host__ __device__ inline int x_row_elems(int K) {      // row stride of X in shared memory, elements
     return K + (((K * 2) % 128 == 0) ? 32 : 0);           // bytes = 64 (mod 128): 16-byte reads of 8 rows x 4
 }                                                         // quarter-row offsets hit 8 different bank groups
@@ -87,6 +96,7 @@ skinny_gemm_kernel(const Args a) {
     const int XS = x_row_elems(K);
     bf16* xs = reinterpret_cast<bf16*>(smem_raw);                         // [8*NT][XS]
     float* red = reinterpret_cast<float*>(smem_raw + (size_t)8 * NT * XS * 2);   // [WARPS][16][8*NT]
+    float* gain_s = red + WARPS * 16 * 8 * NT;                                   // [K], norm prologue only
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     constexpr int ROWS_PER_TILE = (EPI == SWIGLU) ? 8 : 16;
     const int n_tiles = (N + ROWS_PER_TILE - 1) / ROWS_PER_TILE;
@@ -125,19 +135,21 @@ skinny_gemm_kernel(const Args a) {
 
     int cur_tile = blockIdx.x, cur_b = 0;     // the batch that sits in the buffer used next
     if (cur_tile < n_tiles) load_batch(buf0a, buf0b, cur_tile, 0);   // weights do not depend on X: start them first
+    if (PRO == X_F32_NORM)                                 // the gain is a weight too: on its way before X exists
+        for (int c = threadIdx.x; c < K / 4; c += THREADS) cp_async16(gain_s + 4 * c, a.gain + 4 * c, true);
     l2_prefetch_slice(a.prefetch, a.prefetch_bytes, THREADS);
     griddep_wait();        // X (and, for ADD_F32, the matrix added into) come from the kernels before
     griddep_launch();
 
     // ---- prologue: X into shared memory as bfloat16, rows past n are zero ----
     if (PRO == X_BF16) {
+        // all copies in flight at once, one wait
         const int chunks = K / 8;
         for (int c = threadIdx.x; c < 8 * NT * chunks; c += THREADS) {
             const int r = c / chunks, ch = c - r * chunks;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (r < n) v = *reinterpret_cast<const uint4*>(a.x_bf16 + (int64_t)r * a.x_stride + ch * 8);
-            *reinterpret_cast<uint4*>(xs + r * XS + ch * 8) = v;
+            cp_async16(xs + r * XS + ch * 8, a.x_bf16 + (int64_t)(r < n ? r : 0) * a.x_stride + ch * 8, r < n);
         }
+        cp_async_wait_all();
     } else {
         // WARPS / (8*NT) warps share a row: each takes a contiguous part of it, the
         // parts' sums of squares are added in part order
@@ -170,6 +182,7 @@ skinny_gemm_kernel(const Args a) {
             ss = warp_sum(ss);
             if (lane == 0) ss_part[r * PARTS + part] = ss;
         }
+        cp_async_wait_all();       // the gain
         __syncthreads();
         if (live) {
             float tot = 0.f;
@@ -177,7 +190,7 @@ skinny_gemm_kernel(const Args a) {
             for (int q = 0; q < PARTS; q++) tot += ss_part[r * PARTS + q];
             const float scale = rsqrtf(tot / (float)K + a.eps);
             auto put = [&](int k, const float4& w4) {
-                const float4 gn = *reinterpret_cast<const float4*>(a.gain + k);
+                const float4 gn = *reinterpret_cast<const float4*>(gain_s + k);
                 __nv_bfloat162 lo2 = __floats2bfloat162_rn(w4.x * scale * gn.x, w4.y * scale * gn.y);
                 __nv_bfloat162 hi2 = __floats2bfloat162_rn(w4.z * scale * gn.z, w4.w * scale * gn.w);
                 uint2 pk;
@@ -269,7 +282,9 @@ skinny_gemm_kernel(const Args a) {
     }
 }
 
-size_t smem_bytes(int nt, int K) { return (size_t)8 * nt * x_row_elems(K) * 2 + (size_t)WARPS * 16 * 8 * nt * 4; }
+size_t smem_bytes(int nt, int K) {        // X, the warps' partial tiles, the norm's gain
+    return (size_t)8 * nt * x_row_elems(K) * 2 + (size_t)WARPS * 16 * 8 * nt * 4 + (size_t)K * 4;
+}
 
 template <int NT, int PRO, int EPI>
 int launch(const Args& a, cudaStream_t s) {
