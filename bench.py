@@ -108,6 +108,37 @@ def model_bytes_and_flops(cfg, layers):
     return per_layer, per_layer * layers + v * d                   # head counted once, embedding rows negligible
 
 
+def print_timeline(rows, dev_ms):
+    """The instrumented kernels of the last step, in time order: for each the phases
+    between its marks (mean over the recorded CTAs, microseconds) and how long after the
+    previous instrumented kernel's end it ended."""
+    if not rows:
+        print("no instrumented kernel ran")
+        return
+    # the last step: walk back from the newest row until the gap between two kernels is
+    # larger than any inside a step (the host's work between steps)
+    last = [rows[-1]]
+    for r in reversed(rows[:-1]):
+        if last[0]["start"] - r["end"] > 60_000 or r["start"] > last[0]["start"]:
+            break
+        last.insert(0, r)
+    t0 = last[0]["start"]
+    print(f"decode step of {dev_ms * 1e3:.0f} us (device time); {len(last)} instrumented kernels in the last step; "
+          "times in us")
+    prev_end = None
+    for r in last:
+        marks = [m for m in r["marks"]]
+        n = max(int((m > 0).sum()) for m in marks)
+        phases = []
+        for i in range(1, n):
+            d = [(m[i] - m[i - 1]) / 1e3 for m in marks if m[i] > 0 and m[i - 1] > 0]
+            phases.append(f"{sum(d) / len(d):5.2f}" if d else "    -")
+        since = f"{(r['end'] - prev_end) / 1e3:6.2f}" if prev_end is not None else "     -"
+        print(f"  {r['kernel']:<36s} start {(r['start'] - t0) / 1e3:8.2f}  end {(r['end'] - t0) / 1e3:8.2f}  "
+              f"after previous end {since}  phases {' '.join(phases)}")
+        prev_end = r["end"]
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -122,7 +153,13 @@ def main():
                     help="decode: the batch's decode run alone; prefill: the 2048-token prompt alone (partial "
                          "records for profiling small cases, not the bench line)")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
+    ap.add_argument("--timeline", action="store_true",
+                    help="decode run with the instrumented kernel builds; prints where the last step's time went, "
+                         "kernel by kernel (not a bench line)")
     args = ap.parse_args()
+    if args.timeline:
+        os.environ["KLLM_B200_TIMELINE"] = "1"
+        args.only = "decode"
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -243,6 +280,12 @@ def main():
     if args.only == "prefill":
         with torch.no_grad():
             print(json.dumps({"partial": "prefill only", "layers": layers, "prefill": prefill_run()}))
+        return 0
+
+    if args.timeline:
+        with torch.no_grad():
+            dev_ms = decode_run(B, K, W)[0]
+        print_timeline(kernels.timeline(), dev_ms)
         return 0
 
     with torch.no_grad():

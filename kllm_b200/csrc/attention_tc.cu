@@ -104,6 +104,20 @@ __device__ __forceinline__ void load_tile(bf16* stage, const bf16* __restrict__ 
                                           int key0, int hi, int g, int n_kv, int page_size, int page_base = 0) {
     bf16* sk = stage;
     bf16* sv = stage + TILE * ROW;
+    const int lp0 = key0 / page_size, in_page = key0 - lp0 * page_size;
+    if (in_page + TILE <= page_size) {
+        // the whole tile lies in one page: one look-up, rows one after the other
+        const int64_t base = (((int64_t)table[lp0 - page_base] * n_kv + g) * page_size + in_page) * HD;
+#pragma unroll
+        for (int c = threadIdx.x; c < TILE * CHUNKS; c += THREADS) {
+            const int row = c / CHUNKS, ch = c - row * CHUNKS;
+            const bool valid = key0 + row < hi;
+            const int64_t off = valid ? base + row * HD + ch * 8 : 0;
+            cp_async16(sk + row * ROW + ch * 8, kcache + off, valid);
+            cp_async16(sv + row * ROW + ch * 8, vcache + off, valid);
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < TILE * CHUNKS; c += THREADS) {
         const int row = c / CHUNKS, ch = c - row * CHUNKS;
         const int key = key0 + row;
@@ -164,7 +178,73 @@ struct DecodeFusion {
     int64_t v_stride;
     const float* cos_sin;
     unsigned int* counters;
+    int tl_slot;            // timeline row of this launch (-1: none)
+    const void* prefetch;   // optional: weights that a later kernel streams, to be brought into L2
+    long long prefetch_bytes;
 };
+
+// Merge of the splits of one (token, kv head) by one CTA.  (m, l) of row r and split j
+// sit at ml + r * ml_r + j * ml_j, the partial output row at po + r * o_r + j * o_j, in
+// global memory (GLOBAL: written by other CTAs, read past L1) or in this CTA's shared
+// memory.  Every load of a kind is issued together with the others of its kind, so the
+// merge costs two round trips: first all (m, l), then the partial outputs, four dims of
+// all splits per thread.  Sums run over the splits in order.
+template <bool GLOBAL>
+__device__ __forceinline__ void merge_splits(bf16* __restrict__ out, const float* ml, int64_t ml_r, int64_t ml_j,
+                                             const float* po, int64_t o_r, int64_t o_j, unsigned char* scratch,
+                                             int64_t th0, int gs, int num_splits) {
+    float* w_sm = reinterpret_cast<float*>(scratch);        // [gs][num_splits]: m, then the split's weight
+    float* l_sm = w_sm + gs * num_splits;                   // [gs][num_splits]: l
+    float* inv_sm = l_sm + gs * num_splits;                 // [gs]: 1 / sum
+    for (int e = threadIdx.x; e < gs * num_splits; e += THREADS) {
+        const int r = e / num_splits, j = e - r * num_splits;
+        const float2* p = reinterpret_cast<const float2*>(ml + r * ml_r + j * ml_j);
+        const float2 v = GLOBAL ? __ldcg(p) : *p;
+        w_sm[e] = v.x;
+        l_sm[e] = v.y;
+    }
+    __syncthreads();
+    if (threadIdx.x < gs) {
+        float* wr = w_sm + threadIdx.x * num_splits;
+        const float* lr = l_sm + threadIdx.x * num_splits;
+        float M = -INFINITY;
+        for (int j = 0; j < num_splits; j++) M = fmaxf(M, wr[j]);
+        float L = 0.f;
+        for (int j = 0; j < num_splits; j++) {
+            const float f = exp2f(wr[j] - M);
+            L += lr[j] * f;
+            wr[j] = f;
+        }
+        inv_sm[threadIdx.x] = 1.f / L;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < gs * (HD / 4); e += THREADS) {
+        const int r = e / (HD / 4), d = (e - r * (HD / 4)) * 4;
+        const float* pr = po + r * o_r + d;
+        const float* wr = w_sm + r * num_splits;
+        float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j0 = 0; j0 < num_splits; j0 += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++)
+                if (j0 + u < num_splits) {
+                    const float4* p = reinterpret_cast<const float4*>(pr + (j0 + u) * o_j);
+                    v[u] = GLOBAL ? __ldcg(p) : *p;
+                }
+#pragma unroll
+            for (int u = 0; u < 8; u++)
+                if (j0 + u < num_splits) {
+                    const float f = wr[j0 + u];
+                    O.x += v[u].x * f; O.y += v[u].y * f; O.z += v[u].z * f; O.w += v[u].w * f;
+                }
+        }
+        const float inv = inv_sm[r];
+        uint2 pk;
+        pk.x = pack_bf16(O.x * inv, O.y * inv);
+        pk.y = pack_bf16(O.z * inv, O.w * inv);
+        *reinterpret_cast<uint2*>(out + (th0 + r) * HD + d) = pk;
+    }
+}
 
 template <bool FUSED, int DEC_STAGES>
 __global__ void __launch_bounds__(THREADS)
@@ -182,24 +262,34 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
     // Plain form: the kernel before this one wrote this step's keys into the pages.
     // Fused form: nobody but this kernel writes this layer's pages, so their tiles may
     // be requested while the projection kernel before it is still finishing.
+    TL_BEGIN();
     if (!FUSED) { griddep_wait(); griddep_launch(); }
     const int split = blockIdx.x, g = blockIdx.y, t = blockIdx.z;
     const int gs = n_heads / n_kv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tq = lane & 3;
+    const bool whole_row = !token_req && max_blocks <= DEC_PAGES;
+    const int* table = block_table + (int64_t)(token_req ? token_req[t] : t) * max_blocks;
+    if (whole_row) {
+        for (int i = threadIdx.x; i < max_blocks; i += THREADS) s_pages[i] = table[i];
+    }
     const int len = positions[t] + 1;
+    if (whole_row) __syncthreads();
     const int start = (window > 0 && len > window) ? len - window : 0;
     const int total = len - start;
     const int chunk = (((total + num_splits - 1) / num_splits) + TILE - 1) / TILE * TILE;
     const int lo = start + split * chunk;
     const int hi = min(len, lo + chunk);
-    const int* table = block_table + (int64_t)token_req[t] * max_blocks;
     const int ntiles = lo < hi ? (hi - lo + TILE - 1) / TILE : 0;
 
     // This range's slice of the block table, read once and together: otherwise every
-    // tile's copies would wait for their own look-up, one memory round trip after the other.
+    // tile's copies would wait for their own look-up, one memory round trip after the
+    // other.  Without token_req (token t is request t) and with a narrow table the whole
+    // row is read at the same time as the position, before the range is known.
     const int* pages = table;
     int page_base = 0;
-    if (ntiles > 0) {
+    if (whole_row) {
+        pages = s_pages;
+    } else if (ntiles > 0) {
         const int first = lo / page_size, count = (hi - 1) / page_size - first + 1;
         if (count <= DEC_PAGES) {
             for (int i = threadIdx.x; i < count; i += THREADS) s_pages[i] = table[first + i];
@@ -214,6 +304,7 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
         if (s < ntiles) load_tile(smem + s * STAGE_ELEMS, kcache, vcache, pages, lo + s * TILE, hi, g, n_kv, page_size, page_base);
         cp_async_commit();
     }
+    if (FUSED) l2_prefetch_slice(fu.prefetch, fu.prefetch_bytes, THREADS);   // after this kernel's own requests
     // neither do the rotation's angles
     const int p_new = len - 1;
     constexpr int ROT = (FUSED && KSTEPS >= 2) ? KSTEPS / 2 : 1;
@@ -229,7 +320,9 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
                 rc[ks][i][0] = c2.x; rc[ks][i][1] = c2.y; rs[ks][i][0] = s2.x; rs[ks][i][1] = s2.y;
             }
     }
+    TL_MARK(1);
     if (FUSED) { griddep_wait(); griddep_launch(); }
+    TL_MARK(2);
 
     uint32_t qa[KSTEPS][4];
     {
@@ -289,6 +382,7 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
 #pragma unroll
         for (int j = 0; j < 4; j++) o[i][j] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    TL_MARK(3);
 
     for (int i = 0; i < ntiles; i++) {
         cp_async_wait<DEC_STAGES - 2>();
@@ -344,6 +438,7 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
     }
     cp_async_wait<0>();
     __syncthreads();
+    TL_MARK(4);
     // merge the four warps, in warp order
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
@@ -384,6 +479,7 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
             if (d == 0) { part_ml[slot * 2] = M * scale_log2e; part_ml[slot * 2 + 1] = L; }
         }
     }
+    TL_MARK(5);
     if (FUSED && num_splits > 1) {
         // the last CTA of this (token, kv head) to get here merges all splits
         __threadfence();
@@ -394,58 +490,16 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
             if (s_is_last) fu.counters[(int64_t)t * n_kv + g] = 0u;      // ready for the next launch
         }
         __syncthreads();
-        if (!s_is_last) return;
+        TL_MARK(6);
+        // marks: start, copies issued, dependency wait over, query ready, tiles done,
+        // partial written, counted (, merged: only the CTA that merges)
+        if (!s_is_last) { TL_END(fu.tl_slot, 200); return; }
         __threadfence();
-        // Every load of this merge is issued together with the others of its kind, so the
-        // whole merge costs two round trips to L2: first m and l of every (row, split),
-        // then the partial outputs, four dims of all splits per thread.
-        float* w_sm = reinterpret_cast<float*>(smem_raw);       // [gs][num_splits]: m, then the split's weight
-        float* l_sm = w_sm + gs * num_splits;                   // [gs][num_splits]: l
-        float* inv_sm = l_sm + gs * num_splits;                 // [gs]: 1 / sum
         const int64_t th0 = (int64_t)t * n_heads + (int64_t)g * gs;
-        for (int e = threadIdx.x; e < gs * num_splits; e += THREADS) {
-            const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml) + th0 * num_splits + e);
-            w_sm[e] = ml.x;
-            l_sm[e] = ml.y;
-        }
-        __syncthreads();
-        if (threadIdx.x < gs) {
-            float* wr = w_sm + threadIdx.x * num_splits;
-            const float* lr = l_sm + threadIdx.x * num_splits;
-            float M = -INFINITY;
-            for (int j = 0; j < num_splits; j++) M = fmaxf(M, wr[j]);
-            float L = 0.f;
-            for (int j = 0; j < num_splits; j++) {
-                const float f = exp2f(wr[j] - M);
-                L += lr[j] * f;
-                wr[j] = f;
-            }
-            inv_sm[threadIdx.x] = 1.f / L;
-        }
-        __syncthreads();
-        for (int e = threadIdx.x; e < gs * (HD / 4); e += THREADS) {
-            const int r = e / (HD / 4), d = (e - r * (HD / 4)) * 4;
-            const float4* po = reinterpret_cast<const float4*>(part_o + (th0 + r) * num_splits * HD + d);
-            const float* wr = w_sm + r * num_splits;
-            float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int j0 = 0; j0 < num_splits; j0 += 8) {
-                float4 v[8];
-#pragma unroll
-                for (int u = 0; u < 8; u++)
-                    if (j0 + u < num_splits) v[u] = __ldcg(po + (int64_t)(j0 + u) * (HD / 4));
-#pragma unroll
-                for (int u = 0; u < 8; u++)
-                    if (j0 + u < num_splits) {
-                        const float f = wr[j0 + u];
-                        O.x += v[u].x * f; O.y += v[u].y * f; O.z += v[u].z * f; O.w += v[u].w * f;
-                    }
-            }
-            const float inv = inv_sm[r];
-            uint2 pk;
-            pk.x = pack_bf16(O.x * inv, O.y * inv);
-            pk.y = pack_bf16(O.z * inv, O.w * inv);
-            *reinterpret_cast<uint2*>(out + (th0 + r) * HD + d) = pk;
-        }
+        merge_splits<true>(out, part_ml + th0 * num_splits * 2, num_splits * 2, 2, part_o + th0 * num_splits * HD,
+                           (int64_t)num_splits * HD, HD, smem_raw, th0, gs, num_splits);
+        TL_MARK(7);
+        TL_END(fu.tl_slot, 201);
     }
 }
 
@@ -769,10 +823,12 @@ extern "C" int kllm_attention_decode_fused(void* out, void* part_o, void* part_m
                                            void* kcache, void* vcache, const int* positions,
                                            const int* token_req, const int* block_table, int max_blocks,
                                            int n_tokens, int n_heads, int n_kv, int hd, int page_size, int window,
-                                           float scale, int num_splits, void* stream) {
+                                           float scale, int num_splits, const void* prefetch,
+                                           int64_t prefetch_bytes, void* stream) {
     if (n_tokens <= 0) return 0;
     int rc = check_common(n_heads, n_kv, hd, page_size, q, q_stride);
     if (rc) return rc;
+    if (prefetch && ((uintptr_t)prefetch & 15)) KLLM_FAIL("attention decode (fused): the matrix to prefetch must be 16-byte aligned");
     if (KSTEPS % 2) KLLM_FAIL("attention decode (fused): head size %d is not a multiple of 32", HD);
     if (n_heads / n_kv > 16) KLLM_FAIL("attention decode: %d heads per kv head, at most 16", n_heads / n_kv);
     if (num_splits < 1 || (num_splits > 1 && (!part_o || !part_ml || !counters)))
@@ -784,19 +840,17 @@ extern "C" int kllm_attention_decode_fused(void* out, void* part_o, void* part_m
     if (n_tokens > 65535 || n_kv > 65535) KLLM_FAIL("attention decode: grid too large");
     if ((rc = set_attributes())) return rc;
     const float sl2e = scale * 1.4426950408889634f;
-    DecodeFusion fu{(const bf16*)k_new, k_stride, (const bf16*)v_new, v_stride, cos_sin, (unsigned int*)counters};
+    DecodeFusion fu{(const bf16*)k_new, k_stride, (const bf16*)v_new, v_stride, cos_sin, (unsigned int*)counters, TL_SLOT(),
+                    prefetch, prefetch ? (long long)prefetch_bytes : 0LL};
     dim3 grid(num_splits, n_kv, n_tokens);
     const bool deep = (int64_t)num_splits * n_kv * n_tokens <= 2 * 148;
-    if (deep)
-        kllm_launch((attn_decode_kernel<true, DEC_STAGES_DEEP>), dim3(grid), dim3(THREADS),
-                    dec_smem_bytes(DEC_STAGES_DEEP), (cudaStream_t)stream, 
-        (bf16*)out, (float*)part_o, (float*)part_ml, (const bf16*)q, q_stride, (bf16*)kcache, (bf16*)vcache,
-        positions, token_req, block_table, max_blocks, n_heads, n_kv, page_size, window, sl2e, num_splits, fu);
-    else
-        kllm_launch((attn_decode_kernel<true, DEC_STAGES_WIDE>), dim3(grid), dim3(THREADS),
-                    dec_smem_bytes(DEC_STAGES_WIDE), (cudaStream_t)stream, 
-        (bf16*)out, (float*)part_o, (float*)part_ml, (const bf16*)q, q_stride, (bf16*)kcache, (bf16*)vcache,
-        positions, token_req, block_table, max_blocks, n_heads, n_kv, page_size, window, sl2e, num_splits, fu);
+    auto go = [&](auto kernel, size_t smem) {
+        return kllm_launch(kernel, grid, dim3(THREADS), smem, (cudaStream_t)stream, (bf16*)out, (float*)part_o,
+                           (float*)part_ml, (const bf16*)q, q_stride, (bf16*)kcache, (bf16*)vcache, positions, token_req,
+                           block_table, max_blocks, n_heads, n_kv, page_size, window, sl2e, num_splits, fu);
+    };
+    if (deep) go(attn_decode_kernel<true, DEC_STAGES_DEEP>, dec_smem_bytes(DEC_STAGES_DEEP));
+    else go(attn_decode_kernel<true, DEC_STAGES_WIDE>, dec_smem_bytes(DEC_STAGES_WIDE));
     KLLM_LAUNCH_STATUS();
 }
 

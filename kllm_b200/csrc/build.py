@@ -69,6 +69,15 @@ def build_dir() -> str:
     raise KernelBuildError(f"no writable build folder among {cands}")
 
 
+def _with_global(defines):
+    """A library's definitions plus those that the environment asks of every library:
+    KLLM_B200_TIMELINE=1 builds the instrumented variants (see common.cuh)."""
+    d = dict(defines or {})
+    if os.environ.get("KLLM_B200_TIMELINE", "0") not in ("", "0"):
+        d["KLLM_TIMELINE"] = 1
+    return d
+
+
 def _define_flags(defines) -> List[str]:
     return [f"-D{k}={v}" for k, v in sorted((defines or {}).items())]
 
@@ -100,6 +109,7 @@ def _find_built(name: str, digest: str):
 def compile_library(name: str, verbose: bool = True, defines=None) -> str:
     """Compile ``<name>.cu`` (with ``-D`` definitions, if any) unless a current
     build exists; return the .so path."""
+    defines = _with_global(defines)
     src = os.path.join(CSRC, name + ".cu")
     if not os.path.isfile(src):
         raise KernelBuildError(f"kernel source {src} is missing")
@@ -150,10 +160,46 @@ def compile_library(name: str, verbose: bool = True, defines=None) -> str:
     return out
 
 
-def load_library(name: str, defines=None) -> ctypes.CDLL:
+def entry_arity(name: str) -> Dict[str, int]:
+    """Number of parameters of every ``extern "C"`` function that ``<name>.cu`` defines,
+    read from the source text."""
+    import re
+    with open(os.path.join(CSRC, name + ".cu")) as fh:
+        text = re.sub(r"//[^\n]*", "", fh.read())
+    out = {}
+    for m in re.finditer(r'extern\s+"C"\s+[\w\s\*]+?\b(kllm_\w+)\s*\(([^)]*)\)\s*\{', text):
+        params = m.group(2).strip()
+        out[m.group(1)] = 0 if params in ("", "void") else params.count(",") + 1
+    return out
+
+
+class CheckedLibrary:
+    """A loaded kernel library whose entry points refuse a call with another number
+    of arguments than the C source declares: ctypes itself would pass whatever it is
+    given, and the launcher would read the rest from wherever."""
+
+    def __init__(self, cdll: ctypes.CDLL, arity: Dict[str, int], path: str):
+        self._cdll, self._arity, self.path = cdll, arity, path
+
+    def __getattr__(self, fname):
+        fn = getattr(self._cdll, fname)
+        want = self._arity.get(fname)
+        if want is None:
+            return fn
+
+        def call(*args):
+            if len(args) != want:
+                raise KernelBuildError(f"{fname} takes {want} arguments, {len(args)} given")
+            return fn(*args)
+        call.__name__ = fname
+        setattr(self, fname, call)
+        return call
+
+
+def load_library(name: str, defines=None) -> "CheckedLibrary":
     """The loaded library of ``<name>.cu`` (one per set of definitions), compiled
     now if needed."""
-    key = _variant(name, defines)
+    key = _variant(name, _with_global(defines))
     lib = _loaded.get(key)
     if lib is not None:
         return lib
@@ -162,11 +208,16 @@ def load_library(name: str, defines=None) -> ctypes.CDLL:
         if lib is None:
             path = compile_library(name, defines=defines)
             try:
-                lib = ctypes.CDLL(path)
+                lib = CheckedLibrary(ctypes.CDLL(path), entry_arity(name), path)
             except OSError as e:
                 raise KernelBuildError(f"cannot load {path}: {e}") from None
             _loaded[key] = lib
     return lib
+
+
+def loaded_libraries() -> Dict[str, "CheckedLibrary"]:
+    """Variant name -> library, for everything this process has loaded."""
+    return dict(_loaded)
 
 
 # Libraries that are built once per value of a compile-time size: build_all()

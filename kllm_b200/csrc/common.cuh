@@ -36,8 +36,51 @@ static thread_local char g_kllm_err[512];
         return 0;                                                              \
     } while (0)
 
+// ---- timeline (only with -DKLLM_TIMELINE) ---------------------------------------
+// A build for looking at where a kernel's time goes inside a step: a kernel that is
+// instrumented reads the GPU's nanosecond timer at up to 8 marks and, for three of its
+// CTAs (first, middle, last), thread 0 stores them in a table in this library's device
+// memory, one row per launch (rows are reused after KLLM_TL_LAUNCHES launches).  The
+// host reads the table with kllm_timeline_<library>().  Without the definition all of
+// this compiles to nothing.
+#define KLLM_TL_LAUNCHES 512
+#define KLLM_TL_MARKS 8
+#ifdef KLLM_TIMELINE
+__device__ unsigned long long g_kllm_tl[KLLM_TL_LAUNCHES][3][KLLM_TL_MARKS + 1];
+static int g_kllm_tl_next = 0;
+__device__ __forceinline__ unsigned long long kllm_gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define TL_BEGIN() unsigned long long tl_[KLLM_TL_MARKS] = {}; tl_[0] = kllm_gtime()
+#define TL_MARK(i) tl_[i] = kllm_gtime()
+#define TL_END(slot, tag)                                                                        \
+    do {                                                                                         \
+        const unsigned nb_ = gridDim.x * gridDim.y * gridDim.z;                                  \
+        const unsigned b_ = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;      \
+        const int w_ = b_ == 0 ? 0 : (b_ == nb_ / 2 ? 1 : (b_ == nb_ - 1 ? 2 : -1));             \
+        if (w_ >= 0 && threadIdx.x == 0 && (slot) >= 0) {                                        \
+            for (int i_ = 0; i_ < KLLM_TL_MARKS; i_++) g_kllm_tl[slot][w_][i_] = tl_[i_];        \
+            g_kllm_tl[slot][w_][KLLM_TL_MARKS] = (tag);                                          \
+        }                                                                                        \
+    } while (0)
+#define TL_SLOT() (g_kllm_tl_next++ % KLLM_TL_LAUNCHES)
+#define KLLM_EXPORT_TIMELINE(libname)                                                            \
+    extern "C" int kllm_timeline_##libname(unsigned long long* out) {                            \
+        return (int)cudaMemcpyFromSymbol(out, g_kllm_tl, sizeof(g_kllm_tl));                     \
+    }
+#else
+#define TL_BEGIN() do {} while (0)
+#define TL_MARK(i) do {} while (0)
+#define TL_END(slot, tag) do {} while (0)
+#define TL_SLOT() (-1)
+#define KLLM_EXPORT_TIMELINE(libname)
+#endif
+
 #define KLLM_EXPORT_LAST_ERROR(libname)                                 \
-    extern "C" const char* kllm_last_error_##libname() { return g_kllm_err; }
+    extern "C" const char* kllm_last_error_##libname() { return g_kllm_err; } \
+    KLLM_EXPORT_TIMELINE(libname)
 
 // ---- programmatic dependent launch ------------------------------------------
 // Kernels of one step form a chain in which each reads what the one before wrote.
@@ -88,8 +131,10 @@ static inline cudaError_t kllm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 
 __device__ __forceinline__ void l2_prefetch_slice(const void* ptr, long long bytes, int threads) {
     if (!ptr || bytes < 16) return;
     constexpr long long CHUNK = 4096;
-    const long long per_cta = ((bytes / gridDim.x + CHUNK) / CHUNK) * CHUNK;
-    const long long lo = (long long)blockIdx.x * per_cta;
+    const long long ctas = (long long)gridDim.x * gridDim.y * gridDim.z;
+    const long long cta = ((long long)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    const long long per_cta = ((bytes / ctas + CHUNK) / CHUNK) * CHUNK;
+    const long long lo = cta * per_cta;
     const long long hi = min(bytes & ~15LL, lo + per_cta);
     for (long long o = lo + (long long)threadIdx.x * CHUNK; o < hi; o += (long long)threads * CHUNK) {
         const unsigned sz = (unsigned)min(CHUNK, hi - o);

@@ -57,6 +57,7 @@ struct Args {
     bf16* y_bf16;         // STORE_BF16, SWIGLU
     float* y_f32;         // STORE_F32, ADD_F32
     int64_t y_stride;
+    int tl_slot;            // timeline row of this launch (-1: none)
     const void* prefetch;   // optional: weights of a later kernel, to be brought into L2
     int64_t prefetch_bytes;
 };
@@ -92,6 +93,7 @@ template <int NT, int PRO, int EPI>
 __global__ void __launch_bounds__(THREADS)
 skinny_gemm_kernel(const Args a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    TL_BEGIN();
     const int K = a.K, N = a.N, n = a.n;
     const int XS = x_row_elems(K);
     bf16* xs = reinterpret_cast<bf16*>(smem_raw);                         // [8*NT][XS]
@@ -140,6 +142,7 @@ skinny_gemm_kernel(const Args a) {
     l2_prefetch_slice(a.prefetch, a.prefetch_bytes, THREADS);
     griddep_wait();        // X (and, for ADD_F32, the matrix added into) come from the kernels before
     griddep_launch();
+    TL_MARK(1);
 
     // ---- prologue: X into shared memory as bfloat16, rows past n are zero ----
     if (PRO == X_BF16) {
@@ -212,6 +215,7 @@ skinny_gemm_kernel(const Args a) {
         }
     }
     __syncthreads();
+    TL_MARK(2);
 
     // ---- tiles ----
     float acc[NT][4];
@@ -280,6 +284,8 @@ skinny_gemm_kernel(const Args a) {
         if (cur_tile >= n_tiles) break;
         phase(buf1a, buf1b, buf0a, buf0b);
     }
+    TL_MARK(3);
+    TL_END(a.tl_slot, 100 + PRO * 10 + EPI);        // marks: start, dependency wait over, X ready, tiles done
 }
 
 size_t smem_bytes(int nt, int K) {        // X, the warps' partial tiles, the norm's gain
@@ -362,6 +368,7 @@ extern "C" int kllm_skinny_gemm(const void* w, const void* w_up, int N, int K, i
     a.y_bf16 = (bf16*)y_bf16; a.y_f32 = y_f32; a.y_stride = y_stride;
     if (prefetch && ((uintptr_t)prefetch & 15)) KLLM_FAIL("skinny_gemm: the matrix to prefetch must be 16-byte aligned");
     a.prefetch = prefetch; a.prefetch_bytes = prefetch ? prefetch_bytes : 0;
+    a.tl_slot = TL_SLOT();
     cudaStream_t s = (cudaStream_t)stream;
     if (n <= 8) {
         if (prologue == X_BF16) return launch_epi<1, X_BF16>(a, epilogue, s);

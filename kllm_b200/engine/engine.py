@@ -138,6 +138,7 @@ class Engine:
     def close(self) -> None:
         for r in list(self.cache.live.values()):
             self.cache.close(r)
+        self.runner.release_graphs()
         kernels.check_status(self.device)
 
     @staticmethod

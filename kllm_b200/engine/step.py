@@ -14,6 +14,8 @@ all entries together or not at all, and committed after the launch.
 """
 from __future__ import annotations
 
+import gc
+
 from dataclasses import dataclass
 from typing import List, Optional, Sequence
 
@@ -105,8 +107,17 @@ class GraphedDecode:
             self.launches = kernels.launches - before
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                self.logits = model.forward(self.ctx, self.caches)
+            # No garbage collection while the stream is capturing: a collected object
+            # that owns device memory, pinned memory or another graph would free it in
+            # the middle of the capture and invalidate it.
+            gc_was_on = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph):
+                    self.logits = model.forward(self.ctx, self.caches)
+            finally:
+                if gc_was_on:
+                    gc.enable()
             kernels.launches = before + self.launches              # recording launched nothing
             self.graph = graph
             return logits
@@ -132,6 +143,11 @@ class StepRunner:
         self.graphs = {}            # batch size -> GraphedDecode
 
     # ---- validation --------------------------------------------------------
+    def release_graphs(self) -> None:
+        """Drop the captured decode graphs and their static buffers now, not whenever
+        the garbage collector finds them."""
+        self.graphs.clear()
+
     def validate(self, entries: Sequence[StepEntry]) -> None:
         if not entries:
             raise StepError("a step needs at least one entry")

@@ -251,11 +251,15 @@ def attention_decode(out, q, kcache, vcache, positions, token_req, block_table, 
 
 
 def attention_decode_fused(out, q, k_new, v_new, cos_sin, kcache, vcache, positions, token_req, block_table,
-                           counters, n_heads, n_kv, head_dim, window, scale, num_splits: int) -> None:
+                           counters, n_heads, n_kv, head_dim, window, scale, num_splits: int,
+                           prefetch: Optional[torch.Tensor] = None) -> None:
     """Decode attention of one token per request with the rotary encoding, the cache
     write and the merge of the key ranges inside the kernel.  q, k_new, v_new are the
     step's unrotated projections; ``counters`` is an all-zero int32 tensor of at least
-    n_tokens * n_kv elements that the kernel leaves all zero."""
+    n_tokens * n_kv elements that the kernel leaves all zero.  ``token_req`` may be None:
+    token t then belongs to request t, and the kernel reads its block-table row without
+    waiting for that look-up.  ``prefetch``: a contiguous tensor that a later kernel
+    streams; it is requested into L2 once this kernel's own copies are on their way."""
     _cuda(out, q, k_new, v_new, cos_sin, kcache, vcache, positions, token_req, block_table, counters)
     _check_attention(out, q, kcache, vcache, block_table, n_kv, head_dim)
     _i32(positions, "positions"); _i32(token_req, "token_req"); _i32(counters, "counters")
@@ -275,7 +279,8 @@ def attention_decode_fused(out, q, k_new, v_new, cos_sin, kcache, vcache, positi
         _p(out), _p(part_o), _p(part_ml), _p(counters), _p(q), ctypes.c_int64(q.stride(0)), _p(k_new),
         ctypes.c_int64(k_new.stride(0)), _p(v_new), ctypes.c_int64(v_new.stride(0)), _p(cos_sin), _p(kcache),
         _p(vcache), _p(positions), _p(token_req), _p(block_table), block_table.shape[1], n, n_heads, n_kv,
-        head_dim, kcache.shape[2], int(window or 0), ctypes.c_float(scale), int(num_splits), _stream())
+        head_dim, kcache.shape[2], int(window or 0), ctypes.c_float(scale), int(num_splits),
+        *_prefetch_args(prefetch), _stream())
     _check(lib, "attention_tc", rc)
 
 
@@ -327,6 +332,41 @@ def check_status(device) -> None:
     if int(status_word(device).item()) != 0:
         status_word(device).zero_()
         raise KernelError("a kernel gave up waiting on an mbarrier; its results are not valid")
+
+
+TIMELINE_TAGS = {200: "attn_decode_fused", 201: "attn_decode_fused (merging CTA)"}
+for _pro, _pn in ((0, "x"), (1, "norm")):
+    for _epi, _en in ((0, "bf16"), (1, "f32"), (2, "add"), (3, "swiglu")):
+        TIMELINE_TAGS[100 + _pro * 10 + _epi] = f"skinny_gemm {_pn}->{_en}"
+
+
+def timeline():
+    """Rows of the kernels' timeline tables, oldest first (only in a process started with
+    KLLM_B200_TIMELINE=1, which loads the instrumented builds): a list of dicts with the
+    library, the kernel, and per recorded CTA (first, middle, last of the grid) the
+    nanosecond timer at the kernel's marks; see the TL_END lines in csrc for what the
+    marks of a kernel mean.  Synchronises the device."""
+    import numpy as np
+    from .csrc.build import loaded_libraries
+    torch.cuda.synchronize()
+    rows = []
+    for variant, lib in loaded_libraries().items():
+        name = variant.split("-")[0]
+        fn = getattr(lib, "kllm_timeline_" + name, None) if "KLLM_TIMELINE" in variant else None
+        if fn is None:
+            continue
+        buf = np.zeros((512, 3, 9), dtype=np.uint64)
+        if fn(buf.ctypes.data_as(ctypes.c_void_p)) != 0:
+            raise KernelError(f"timeline of {variant} could not be read")
+        for slot in range(512):
+            ctas = [buf[slot, c, :8].astype(np.int64) for c in range(3) if buf[slot, c, 0] > 0]
+            if ctas:
+                tags = sorted({int(buf[slot, c, 8]) for c in range(3) if buf[slot, c, 0] > 0})
+                rows.append({"library": variant, "kernel": " / ".join(TIMELINE_TAGS.get(t, str(t)) for t in tags),
+                             "start": int(min(c[0] for c in ctas)), "end": int(max(c.max() for c in ctas)),
+                             "marks": ctas})
+    rows.sort(key=lambda r: r["start"])
+    return rows
 
 
 def silu_mul(out: torch.Tensor, gate: torch.Tensor, up: torch.Tensor) -> None:

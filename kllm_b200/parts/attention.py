@@ -53,6 +53,7 @@ class PagedAttention:
         self.w_qkv = None
         self.w_o = None
         self._counters = None      # zeroed scratch of the fused decode kernel, which keeps it zero
+        self._after = []           # weights streamed right after this part (see set_prefetch_targets)
 
     def _names(self):
         return {k: f"{self.prefix}.{k}_proj.weight" for k in "qkvo"}
@@ -81,7 +82,20 @@ class PagedAttention:
             return q, q, q
         return q, qkv[:, self.q_dim:self.q_dim + self.kv_dim], qkv[:, self.q_dim + self.kv_dim:]
 
-    def _attend(self, q, k, v, ctx, cache):
+    def streamed_weights(self):
+        """The matrices this part streams in a small step, in kernel order."""
+        return [self.w_qkv, self.w_o]
+
+    def set_prefetch_targets(self, weights):
+        """What the kernels after this part stream first (the next part's
+        ``streamed_weights``): in a small step the attention kernel and the output
+        projection ask for them to be brought into L2 while they run."""
+        self._after = list(weights)
+
+    def _target(self, i):
+        return self._after[i] if i < len(self._after) else None
+
+    def _attend(self, q, k, v, ctx, cache, prefetch=None):
         n = q.shape[0]
         group = self.n_heads // self.n_kv
         table = getattr(self.position, "full_rotary_table", lambda: None)() if self.position is not None else None
@@ -92,9 +106,9 @@ class PagedAttention:
                 self._counters = torch.zeros(max(64, n) * self.n_kv, dtype=torch.int32, device=q.device)
             attn = torch.empty((n, self.q_dim), dtype=self.dtype, device=q.device)
             kernels.attention_decode_fused(
-                attn, q, k, v, table, cache.k, cache.v, ctx.positions, ctx.token_req, cache.block_table,
+                attn, q, k, v, table, cache.k, cache.v, ctx.positions, None, cache.block_table,   # token t is request t
                 self._counters, self.n_heads, self.n_kv, self.head_dim, self.window or 0, self.scale,
-                kernels.decode_splits(n, self.n_kv, ctx.split_bound or ctx.max_ctx))
+                kernels.decode_splits(n, self.n_kv, ctx.split_bound or ctx.max_ctx), prefetch=prefetch)
             return attn
         if self.position is not None:
             self.position.apply(q, k, v, ctx, cache, self.n_heads, self.n_kv)
@@ -122,8 +136,8 @@ class PagedAttention:
         w = self.w_qkv if cache.writes else self.w_qkv[:self.q_dim]
         qkv = kernels.skinny_gemm(w, x_f32=x, gain=norm.gain, eps=norm.eps, epilogue="bf16")
         q, k, v = self._split(qkv, cache.writes)
-        attn = self._attend(q, k, v, ctx, cache)
-        kernels.skinny_gemm(self.w_o, x=attn, epilogue="add", out=x)
+        attn = self._attend(q, k, v, ctx, cache, prefetch=self._target(0))
+        kernels.skinny_gemm(self.w_o, x=attn, epilogue="add", out=x, prefetch=self._target(1))
         return True
 
 

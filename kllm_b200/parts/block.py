@@ -12,6 +12,12 @@ None) is what is still to be added to x.
 A mixer or feed-forward may offer ``forward_residual`` (norm and residual sum inside
 its own kernels); the block tries it whenever nothing is pending and falls back to
 norm -> part -> pending otherwise.  Both routes compute the same sums.
+
+Two more optional methods let a part's kernels warm L2 for the kernels after them:
+``streamed_weights()`` (the matrices a part streams in a small step, in kernel order)
+and ``set_prefetch_targets(weights)`` (what runs right after the part).  The block
+wires mixer -> feed-forward when it is bound, the model wires feed-forward -> the next
+block's mixer through ``set_successor``.  A part without them is left alone.
 """
 from __future__ import annotations
 
@@ -34,6 +40,19 @@ class PreNormBlock:
     def bind(self, tensors):
         for p in self.parts():
             p.bind(tensors)
+        self._wire(self.mixer, self.feed_forward)
+
+    @staticmethod
+    def _wire(part, following):
+        """Tell ``part`` which weights the part after it streams, if both take part in
+        that (optional methods ``set_prefetch_targets`` / ``streamed_weights``)."""
+        tell, ask = getattr(part, "set_prefetch_targets", None), getattr(following, "streamed_weights", None)
+        if tell is not None and ask is not None:
+            tell(ask())
+
+    def set_successor(self, block):
+        """The block that runs after this one in the model's schedule."""
+        self._wire(self.feed_forward, getattr(block, "mixer", None))
 
     def forward(self, x, pending, ctx, cache):
         fused = getattr(self.mixer, "forward_residual", None)

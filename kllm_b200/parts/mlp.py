@@ -36,6 +36,7 @@ class GatedMLP:
         self.dtype = env.dtype
         self.w_gate_up = None
         self.w_down = None
+        self._after = []           # weights streamed right after this part (see set_prefetch_targets)
 
     def tensor_specs(self):
         return [TensorSpec(f"{self.prefix}.gate_proj.weight", (self.inter, self.hidden)),
@@ -46,6 +47,19 @@ class GatedMLP:
         self.w_gate_up = torch.cat([tensors[f"{self.prefix}.gate_proj.weight"],
                                     tensors[f"{self.prefix}.up_proj.weight"]], dim=0).contiguous()
         self.w_down = tensors[f"{self.prefix}.down_proj.weight"]
+
+    def streamed_weights(self):
+        """The matrices this part streams in a small step, in kernel order."""
+        return [self.w_gate_up, self.w_down]
+
+    def set_prefetch_targets(self, weights):
+        """What the kernels after this part stream first (the next layer's mixer's
+        ``streamed_weights``): in a small step this part's two kernels ask for them
+        to be brought into L2 while they run."""
+        self._after = list(weights)
+
+    def _target(self, i):
+        return self._after[i] if i < len(self._after) else None
 
     def forward(self, xn, ctx):
         # gate and up stay float32 until the activation has been applied; the down
@@ -69,8 +83,8 @@ class GatedMLP:
                 and kernels.skinny_fits(n, self.inter, self.dtype)):
             return False
         act = kernels.skinny_gemm(self.w_gate_up[:self.inter], weight_up=self.w_gate_up[self.inter:], x_f32=x,
-                                  gain=norm.gain, eps=norm.eps, epilogue="swiglu")
-        kernels.skinny_gemm(self.w_down, x=act, epilogue="add", out=x)
+                                  gain=norm.gain, eps=norm.eps, epilogue="swiglu", prefetch=self._target(0))
+        kernels.skinny_gemm(self.w_down, x=act, epilogue="add", out=x, prefetch=self._target(1))
         return True
 
 

@@ -69,6 +69,14 @@ class DecoderModel:
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         for p in self.parts():
             p.bind(tensors)
+        # a block may warm the cache for the block that the schedule runs after it
+        # (first successor wins where a block runs more than once)
+        told = set()
+        for call, nxt in zip(self.schedule, self.schedule[1:]):
+            tell = getattr(self.blocks[call.block], "set_successor", None)
+            if tell is not None and call.block not in told:
+                told.add(call.block)
+                tell(self.blocks[nxt.block])
 
     # ---- cache -----------------------------------------------------------
     def cache_needs(self):

@@ -233,10 +233,11 @@ def test_tensor_core_attention_finds_one_far_key(kernel, splits):
 
 
 @pytest.mark.parametrize("H,G,hd,page", [(8, 2, 64, 16), (32, 4, 128, 64), (3, 1, 32, 5), (4, 4, 96, 16)])
-@pytest.mark.parametrize("splits", [1, 3, 8])
+@pytest.mark.parametrize("splits", [1, 3, 8, 12])
 def test_fused_decode_attention_rotates_appends_and_merges(H, G, hd, page, splits):
     """Against the separate kernels' math: rotate q and the new k, store k and v at the
-    token's slot, attend over everything.  Run twice on one counter buffer."""
+    token's slot, attend over everything.  Run twice on one counter buffer: with the
+    token-to-request table, then without it (token t is request t)."""
     from kllm_b200 import kernels
     rng = np.random.default_rng(H * hd + splits)
     lengths = [70, 1, 33, 129, 300]
@@ -269,8 +270,8 @@ def test_fused_decode_attention_rotates_appends_and_merges(H, G, hd, page, split
         out = torch.empty_like(q_t)
         pos = dev(np.array([L - 1 for L in lengths], np.int32))
         req = dev(np.arange(len(lengths), dtype=np.int32))
-        kernels.attention_decode_fused(out, q_t, k_t, v_t, cos_sin, kc, vc, pos, req, table, counters, H, G, hd, 0,
-                                       1.0 / math.sqrt(hd), splits)
+        kernels.attention_decode_fused(out, q_t, k_t, v_t, cos_sin, kc, vc, pos, req if rep == 0 else None, table,
+                                       counters, H, G, hd, 0, 1.0 / math.sqrt(hd), splits)
         assert not torch.isnan(out.float()).any()
         close(out, np.concatenate(want), "bfloat16", f"attention, run {rep}")
         assert int(counters.abs().sum()) == 0, "the counters must be zero again"
