@@ -1,32 +1,35 @@
 // Causal grouped-query attention of prompt portions over the paged cache on the
 // fifth-generation tensor cores: both products (scores = Q.K^T and output = P.V) are
-// tcgen05.mma instructions issued by one thread, with the operands in shared memory
-// and the accumulators in tensor memory (TMEM).  One library per head size
-// (-DKLLM_HD=64 or 128), bfloat16 operands, float32 accumulation.
+// tcgen05.mma instructions, with the operands in shared memory and the accumulators in
+// tensor memory (TMEM).  One library per head size (-DKLLM_HD=64 or 128), bfloat16
+// operands, float32 accumulation.
 //
-// A CTA of 128 threads takes 128 rows = (tokens of one request's portion) x (heads of
-// one kv group) and walks that portion's keys in tiles of 64:
+// A CTA takes 128 rows = (tokens of one request's portion) x (heads of one kv group) and
+// walks that portion's keys in tiles of 64.  Its six warps have three roles that meet
+// only at mbarriers, so loading, the tensor core and the softmax of neighbouring tiles
+// run at the same time:
 //
-//   1. the K and V tiles arrive in shared memory by cp.async, written directly in the
-//      128-byte-swizzled layout that the MMA's shared-memory descriptors name (rows of
-//      64 elements, 8-row groups of 1024 bytes, the 16-byte piece index XORed with the
-//      row index modulo 8); head sizes above 64 are kept as panels of 64 dims;
-//   2. one thread issues Q.K^T (M=128, N=64, K=16 per instruction, HD/16 of them) into
-//      64 TMEM columns and commits to an mbarrier;
-//   3. every thread owns one row: it reads its 64 scores from TMEM (tcgen05.ld
-//      32x32b), applies the mask and the online-softmax recurrence without any
-//      cross-thread traffic, and writes its probabilities as bfloat16 into a swizzled
-//      shared-memory tile;
-//   4. the thread issues P.V (M=128, N=HD, K=16 x 4, V as the MN-major operand) into
-//      another TMEM region, commits, and every thread adds its row of the result to
-//      its float32 accumulator in registers, rescaled by the softmax correction.
+//   warp 5   loader: K and V tiles by cp.async into a ring of stages, written directly in
+//            the 128-byte-swizzled layout that the MMA's shared-memory descriptors name
+//            (rows of 64 elements, 8-row groups of 1024 bytes, the 16-byte piece index
+//            XORed with the row index modulo 8; head sizes above 64 as panels of 64
+//            dims); the copies' completion arrives on the stage's mbarrier;
+//   warp 4   one lane issues the tcgen05.mma: Q.K^T of tile j+1 (M=128, N=64, K=16 per
+//            instruction) into one of two score buffers in TMEM as soon as that buffer
+//            has been read out and the tile has landed, that is while the softmax warps
+//            still work on tile j; then P.V of tile j (V as the MN-major operand) into
+//            the output tile in TMEM once the probabilities are in shared memory;
+//   warps 0-3  softmax: every thread owns one row, reads its 64 scores from TMEM
+//            (tcgen05.ld 32x32b), applies the mask and the online-softmax recurrence
+//            without any cross-thread traffic, adds the previous tile's P.V result
+//            (rescaled) to its float32 accumulator in registers, and writes its
+//            probabilities as bfloat16 into a swizzled shared-memory tile.
 //
-// Two tiles of K/V are in flight (the next one loads while this one is multiplied).
-// Waits on the mbarrier are bounded: a wait that runs out sets a status word, and the
-// CTA leaves after freeing its TMEM.  Math as in the reference
-// (backend/model.cu:343-408): keys [max(0, p + 1 - window), p], scale after the dot
-// product, one division by the sum at the end; probabilities are rounded to bfloat16
-// for the second product only.
+// Every wait on an mbarrier is bounded by a cycle count: a wait that runs out raises a
+// flag in shared memory and sets the status word, every role leaves its loop, and the
+// CTA frees its TMEM and returns.  Math as in the reference (backend/model.cu:343-408):
+// keys [max(0, p + 1 - window), p], scale after the dot product, one division by the sum
+// at the end; probabilities are rounded to bfloat16 for the second product only.
 #include "common.cuh"
 
 #ifndef KLLM_HD
@@ -42,14 +45,15 @@ static_assert(HD == 64 || HD == 128, "head size 64 or 128");
 constexpr int PANELS = HD / 64;            // 64-dim panels of a row
 constexpr int ROWS = 128;                  // query rows per CTA = TMEM lanes
 constexpr int TILE = 64;                   // keys per tile
-constexpr int THREADS = 128;
+constexpr int THREADS = 192;                          // 4 softmax warps, the MMA warp, the loader warp
+constexpr int SOFTMAX_THREADS = 128;
 constexpr int Q_BYTES = PANELS * ROWS * 128;          // [panel][128 rows][64 dims]
 constexpr int KV_BYTES = PANELS * TILE * 128;         // [panel][64 keys][64 dims]
 constexpr int P_BYTES = ROWS * 128;                   // [128 rows][64 keys]
-constexpr int STAGES = 2;
+constexpr int STAGES = HD == 64 ? 3 : 2;
 constexpr int SMEM_BYTES = 1024 + Q_BYTES + P_BYTES + STAGES * 2 * KV_BYTES;
-constexpr int TMEM_COLS = HD == 64 ? 128 : 256;       // scores (64) + output tile (HD), a power of two
-constexpr unsigned kSpinLimit = 1u << 22;
+constexpr int TMEM_COLS = 256;                        // two score buffers (2 x 64) + output tile (HD): a power of two
+constexpr long long kCycleLimit = 4000000000LL;       // about two seconds
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 
@@ -57,8 +61,9 @@ __device__ __forceinline__ void cp_async16(unsigned dst, const void* gmem, bool 
     const int bytes = valid ? 16 : 0;
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem), "r"(bytes));
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.commit_group;\ncp.async.wait_group %0;\n" ::"n"(N));
+}
 // shared-memory writes of this thread become visible to the tensor core's (async proxy) reads
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
@@ -131,18 +136,59 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// keys key0 .. key0+63 of kv head g into a stage: K panels then V panels.  A thread
-// keeps its 16-byte piece of the row and walks the rows, so that a row's page is
-// looked up once per thread and row.
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+// the barrier gets one arrival when all cp.async copies that this thread has issued so far have landed
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait.  Returns false (and raises the flags) when the limit ran out or another
+// role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag, int* status, int where) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    unsigned spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 63u) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > kCycleLimit) {
+                *abort_flag = 1;
+                if (status) atomicCAS(status, 0, where);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// keys key0 .. key0+63 of kv head g into a stage (K panels, then V panels), by the 32
+// lanes of the loader warp.  A lane keeps its 16-byte piece of the row and walks the rows.
 __device__ __forceinline__ void load_kv(unsigned stage, const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
-                                        const int* __restrict__ table, int key0, int hi, int g, int n_kv, int page_size) {
+                                        const int* __restrict__ table, int key0, int hi, int g, int n_kv, int page_size,
+                                        int lane) {
     constexpr int PIECES = HD / 8;                        // 16-byte pieces of a row
-    constexpr int ROWS_PER_PASS = THREADS / PIECES;       // 16 (HD 64) or 8 (HD 128)
-    const int piece = threadIdx.x % PIECES, r0 = threadIdx.x / PIECES;
+    constexpr int ROWS_PER_PASS = 32 / PIECES;            // 4 (HD 64) or 2 (HD 128)
+    const int piece = lane % PIECES, r0 = lane / PIECES;
     const unsigned col = (unsigned)((piece >> 3) * (TILE * 128));
     const int64_t head_off = (int64_t)g * page_size * HD + piece * 8;
     const int64_t page_elems = (int64_t)n_kv * page_size * HD;
-#pragma unroll
+    const int lp0 = key0 / page_size, in_page = key0 - lp0 * page_size;
+    if (in_page + TILE <= page_size) {
+        // the whole tile lies in one page: one look-up, the rows follow one another
+        const int64_t base = (int64_t)table[lp0] * page_elems + head_off + (int64_t)in_page * HD;
+#pragma unroll 8
+        for (int j = 0; j < TILE / ROWS_PER_PASS; j++) {
+            const int row = r0 + j * ROWS_PER_PASS;
+            const bool valid = key0 + row < hi;
+            const int64_t off = valid ? base + row * HD : 0;
+            const unsigned dst = col + swz(row, piece & 7);
+            cp_async16(stage + dst, kcache + off, valid);
+            cp_async16(stage + KV_BYTES + dst, vcache + off, valid);
+        }
+        return;
+    }
+#pragma unroll 4
     for (int j = 0; j < TILE / ROWS_PER_PASS; j++) {
         const int row = r0 + j * ROWS_PER_PASS;
         const int key = key0 + row;
@@ -158,21 +204,20 @@ __device__ __forceinline__ void load_kv(unsigned stage, const bf16* __restrict__
     }
 }
 
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, HD == 64 ? 2 : 1)
 attn_prefill_tc5_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t q_stride,
                         const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                         const int* __restrict__ q_start, const int* __restrict__ start_pos,
                         const int* __restrict__ block_table, int max_blocks, int n_requests, int n_heads,
                         int n_kv, int page_size, int window, float scale_log2e, int tokens_per_tile, int* status) {
     extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t bar_mma;
+    __shared__ __align__(8) uint64_t bar_kv_full[STAGES], bar_kv_empty[STAGES], bar_q_full, bar_s_full[2], bar_s_free[2],
+        bar_p_full, bar_o_full;
     __shared__ unsigned s_tmem;
     __shared__ int s_req, s_tok0, s_abort;
-    griddep_wait();
-    griddep_launch();
     const int g = blockIdx.y;
     const int gs = n_heads / n_kv;
-    const int warp = threadIdx.x >> 5;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         int tile = gridDim.x - 1 - blockIdx.x, req = -1, tok0 = 0;       // longest key ranges first
         for (int s = 0; s < n_requests; s++) {
@@ -182,177 +227,204 @@ attn_prefill_tc5_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int6
             tile -= nt;
         }
         s_req = req; s_tok0 = tok0; s_abort = 0;
+        for (int s = 0; s < STAGES; s++) { mbar_init(&bar_kv_full[s], 32); mbar_init(&bar_kv_empty[s], 1); }
+        mbar_init(&bar_q_full, 32);
+        for (int b = 0; b < 2; b++) { mbar_init(&bar_s_full[b], 1); mbar_init(&bar_s_free[b], SOFTMAX_THREADS); }
+        mbar_init(&bar_p_full, SOFTMAX_THREADS);
+        mbar_init(&bar_o_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncthreads();
     const int req = s_req;
     if (req < 0) return;                       // the grid is an upper bound on the tiles
+    if (warp == 4) {                           // TMEM: one warp allocates, everybody learns the address
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&s_tmem)), "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    griddep_wait();
+    griddep_launch();
+    const unsigned tmem = s_tmem;
     const int tok0 = s_tok0;
     const int n_tok = min(tokens_per_tile, q_start[req + 1] - tok0);
     const int pos0 = start_pos[req] + (tok0 - q_start[req]);
     const int lo = (window > 0 && pos0 + 1 > window) ? pos0 + 1 - window : 0;
     const int hi = pos0 + n_tok;
     const int* table = block_table + (int64_t)req * max_blocks;
-    const int ntiles = (hi - lo + TILE - 1) / TILE;
+    const int ntiles = (hi - lo + TILE - 1) / TILE;      // at least 1: a row sees its own key
+    volatile int* abort_flag = &s_abort;
 
     const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;       // swizzled tiles want 1024-byte alignment
     const unsigned sQ = base, sP = base + Q_BYTES, sKV = sP + P_BYTES;
 
-    // TMEM: one warp allocates, everybody learns the address
-    if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&s_tmem)), "r"(TMEM_COLS));
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    if (warp == 5) {
+        // ---- loader ----------------------------------------------------------------
+        for (int c = lane; c < ROWS * (HD / 8); c += 32) {     // Q tile: each row's HD dims, zero for unused rows
+            const int r = c / (HD / 8), piece = c - r * (HD / 8);
+            const int t2 = r / gs, h2 = r - t2 * gs;
+            const bool ok = t2 < n_tok;
+            const bf16* src = ok ? q + (int64_t)(tok0 + t2) * q_stride + (int64_t)(g * gs + h2) * HD + piece * 8 : q;
+            cp_async16(sQ + (unsigned)((piece >> 3) * (ROWS * 128)) + swz(r, piece & 7), src, ok);
+        }
+        cp_async_arrive(&bar_q_full);
+        for (int j = 0; j < ntiles; j++) {
+            const int s = j % STAGES;
+            if (!mbar_wait(&bar_kv_empty[s], (((unsigned)(j / STAGES)) & 1u) ^ 1u, abort_flag, status, 1)) break;
+            load_kv(sKV + (unsigned)s * 2u * KV_BYTES, kcache, vcache, table, lo + j * TILE, hi, g, n_kv, page_size, lane);
+            cp_async_arrive(&bar_kv_full[s]);
+        }
+        cp_async_wait<0>();                    // nothing of this warp is in flight when the CTA ends
+    } else if (warp == 4) {
+        // ---- tensor-core issuer ----------------------------------------------------
+        constexpr uint32_t IDESC_S = make_idesc(ROWS, TILE, false);
+        constexpr uint32_t IDESC_O = make_idesc(ROWS, HD, true);
+        bool ok = mbar_wait(&bar_q_full, 0, abort_flag, status, 2);
+        auto issue_scores = [&](int j) -> bool {            // scores of tile j into buffer j & 1
+            const int s = j % STAGES, b = j & 1;
+            if (!mbar_wait(&bar_kv_full[s], ((unsigned)(j / STAGES)) & 1u, abort_flag, status, 3)) return false;
+            if (!mbar_wait(&bar_s_free[b], (((unsigned)(j >> 1)) & 1u) ^ 1u, abort_flag, status, 4)) return false;
+            fence_async_smem();                // the copies landed through the generic proxy
+            tc_fence_after();
+            if (lane == 0) {
+                const unsigned st = sKV + (unsigned)s * 2u * KV_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; kk++) {
+                    const unsigned a = sQ + (unsigned)((kk >> 2) * (ROWS * 128) + (kk & 3) * 32);
+                    const unsigned bb = st + (unsigned)((kk >> 2) * (TILE * 128) + (kk & 3) * 32);
+                    umma(tmem + (unsigned)(b * 64), make_desc(a, 16, 1024), make_desc(bb, 16, 1024), IDESC_S, kk > 0);
+                }
+                umma_commit(&bar_s_full[b]);
+            }
+            __syncwarp();
+            return true;
+        };
+        if (ok) ok = issue_scores(0);
+        for (int j = 0; ok && j < ntiles; j++) {
+            if (j + 1 < ntiles) { ok = issue_scores(j + 1); if (!ok) break; }     // runs while tile j is in the softmax
+            ok = mbar_wait(&bar_p_full, (unsigned)j & 1u, abort_flag, status, 5);
+            if (!ok) break;
+            tc_fence_after();
+            if (lane == 0) {                   // output tile = P . V
+                const unsigned st = sKV + (unsigned)(j % STAGES) * 2u * KV_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < TILE / 16; kk++) {
+                    const unsigned a = sP + (unsigned)(kk * 32);
+                    const unsigned bb = st + KV_BYTES + (unsigned)(kk * 2048);
+                    umma(tmem + 128, make_desc(a, 16, 1024), make_desc(bb, TILE * 128, 1024), IDESC_O, kk > 0);
+                }
+                umma_commit(&bar_o_full);
+                umma_commit(&bar_kv_empty[j % STAGES]);
+            }
+            __syncwarp();
+        }
+    } else {
+        // ---- softmax: this thread's row is (token, head of the group) ---------------
+        const int row = threadIdx.x;
+        const int tt = row / gs, hh = row - tt * gs;
+        const bool valid_row = tt < n_tok;
+        const int p_row = valid_row ? pos0 + tt : -1;                       // -1: sees no key
+        const int w_row = (window > 0) ? p_row + 1 - window : 0;
+        const unsigned lane_base = (unsigned)(warp * 32) << 16;
+        const unsigned t_o = tmem + lane_base + 128;
+        float o_acc[HD];
+#pragma unroll
+        for (int i = 0; i < HD; i++) o_acc[i] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f, corr_pending = 1.f;
+        auto add_output_tile = [&]() {         // o_acc = o_acc * (its tile's correction) + P.V of that tile
+#pragma unroll
+            for (int cb = 0; cb < HD / 32; cb++) {
+                float t[32];
+                tmem_ld32(t_o + cb * 32, t);
+                tmem_ld_wait();
+#pragma unroll
+                for (int jj = 0; jj < 32; jj++) o_acc[cb * 32 + jj] = o_acc[cb * 32 + jj] * corr_pending + t[jj];
+            }
+        };
+        bool ok = true;
+        for (int j = 0; j < ntiles; j++) {
+            const int b = j & 1;
+            ok = mbar_wait(&bar_s_full[b], ((unsigned)(j >> 1)) & 1u, abort_flag, status, 6);
+            if (!ok) break;
+            tc_fence_after();
+            float s[TILE];
+            {
+                float (*s2)[32] = reinterpret_cast<float (*)[32]>(s);
+                const unsigned t_s = tmem + lane_base + (unsigned)(b * 64);
+                tmem_ld32(t_s, s2[0]);
+                tmem_ld32(t_s + 32, s2[1]);
+                tmem_ld_wait();
+            }
+            tc_fence_before();
+            mbar_arrive(&bar_s_free[b]);       // the buffer may take the scores of tile j + 2
+            const int key0 = lo + j * TILE;
+            // the mask matters only where the tile crosses this row's diagonal or window edge
+            if (key0 + TILE - 1 > p_row || key0 < w_row) {
+#pragma unroll
+                for (int jj = 0; jj < TILE; jj++) {
+                    const int key = key0 + jj;
+                    if (key > p_row || key < w_row) s[jj] = -INFINITY;
+                }
+            }
+            float mx4[4] = {s[0], s[1], s[2], s[3]};
+#pragma unroll
+            for (int jj = 4; jj < TILE; jj++) mx4[jj & 3] = fmaxf(mx4[jj & 3], s[jj]);
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            const float m_new = fmaxf(m_run, mx);
+            const float m_use = (m_new == -INFINITY) ? 0.f : m_new;       // a row that has seen no key yet
+            const float corr = exp2f((m_run - m_use) * scale_log2e);
+            m_run = m_new;
+            const float neg = -m_use * scale_log2e;                       // p = 2^(s * scale - m * scale): one FMA each
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int jj = 0; jj < TILE; jj++) {
+                s[jj] = fast_exp2(fmaf(s[jj], scale_log2e, neg));
+                sum4[jj & 3] += s[jj];
+            }
+            l_run = l_run * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            if (j > 0) {                       // the product of tile j - 1 has had the whole softmax to finish
+                ok = mbar_wait(&bar_o_full, (unsigned)(j - 1) & 1u, abort_flag, status, 7);
+                if (!ok) break;
+                tc_fence_after();
+                add_output_tile();
+            }
+            corr_pending = corr;
+#pragma unroll
+            for (int c = 0; c < 8; c++) {      // 8 keys = 16 bytes per piece, swizzled like an operand row
+                uint4 pk;
+                pk.x = pack_bf16(s[8 * c], s[8 * c + 1]);
+                pk.y = pack_bf16(s[8 * c + 2], s[8 * c + 3]);
+                pk.z = pack_bf16(s[8 * c + 4], s[8 * c + 5]);
+                pk.w = pack_bf16(s[8 * c + 6], s[8 * c + 7]);
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(sP + swz(row, c)), "r"(pk.x), "r"(pk.y), "r"(pk.z), "r"(pk.w) : "memory");
+            }
+            fence_async_smem();
+            tc_fence_before();
+            mbar_arrive(&bar_p_full);          // P of tile j is in shared memory, the output tile has been read
+        }
+        if (ok) ok = mbar_wait(&bar_o_full, (unsigned)(ntiles - 1) & 1u, abort_flag, status, 8);
+        if (ok) {
+            tc_fence_after();
+            add_output_tile();
+            if (valid_row) {
+                const float inv = 1.f / l_run;
+                bf16* orow = out + (int64_t)(tok0 + tt) * n_heads * HD + (int64_t)(g * gs + hh) * HD;
+#pragma unroll
+                for (int c = 0; c < HD / 8; c++) {
+                    uint4 pk;
+                    pk.x = pack_bf16(o_acc[8 * c] * inv, o_acc[8 * c + 1] * inv);
+                    pk.y = pack_bf16(o_acc[8 * c + 2] * inv, o_acc[8 * c + 3] * inv);
+                    pk.z = pack_bf16(o_acc[8 * c + 4] * inv, o_acc[8 * c + 5] * inv);
+                    pk.w = pack_bf16(o_acc[8 * c + 6] * inv, o_acc[8 * c + 7] * inv);
+                    *reinterpret_cast<uint4*>(orow + 8 * c) = pk;
+                }
+            }
+        }
     }
-    if (threadIdx.x == 0) {
-        mbar_init(&bar_mma, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-    }
-
-    // this thread's row: (token, head of the group)
-    const int row = threadIdx.x;
-    const int tt = row / gs, hh = row - tt * gs;
-    const bool valid_row = tt < n_tok && tt < tokens_per_tile;
-    const int p_row = valid_row ? pos0 + tt : -1;                       // -1: sees no key
-    const int w_row = (window > 0) ? p_row + 1 - window : 0;
-
-    // Q tile: each row's HD dims, zero for unused rows
-    for (int c = threadIdx.x; c < ROWS * (HD / 8); c += THREADS) {
-        const int r = c / (HD / 8), piece = c - r * (HD / 8);
-        const int t2 = r / gs, h2 = r - t2 * gs;
-        const bool ok = t2 < n_tok && t2 < tokens_per_tile;
-        const bf16* src = ok ? q + (int64_t)(tok0 + t2) * q_stride + (int64_t)(g * gs + h2) * HD + piece * 8 : q;
-        cp_async16(sQ + (unsigned)((piece >> 3) * (ROWS * 128)) + swz(r, piece & 7), src, ok);
-    }
-    cp_async_commit();
-    if (ntiles > 0) load_kv(sKV, kcache, vcache, table, lo, hi, g, n_kv, page_size);
-    cp_async_commit();
-
     tc_fence_before();
     __syncthreads();
-    tc_fence_after();
-    const unsigned tmem = s_tmem;
-    const unsigned t_s = tmem + ((unsigned)(warp * 32) << 16);            // scores: columns 0..63
-    const unsigned t_o = t_s + 64;                                        // output tile: columns 64..64+HD-1
-
-    constexpr uint32_t IDESC_S = make_idesc(ROWS, TILE, false);
-    constexpr uint32_t IDESC_O = make_idesc(ROWS, HD, true);
-
-    float o_acc[HD];
-#pragma unroll
-    for (int i = 0; i < HD; i++) o_acc[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
-    unsigned phase = 0;
-
-    auto wait_mma = [&]() {
-        unsigned spins = 0;
-        while (!mbar_try_wait(&bar_mma, phase)) {
-            if (++spins > kSpinLimit) { s_abort = 1; if (status) *status = 1; break; }
-        }
-        phase ^= 1u;
-        tc_fence_after();
-    };
-
-    for (int i = 0; i < ntiles; i++) {
-        const unsigned st = sKV + (unsigned)(i & 1) * 2u * KV_BYTES;
-        cp_async_wait<0>();                   // Q and tile i are in shared memory (this thread's pieces)
-        fence_async_smem();
-        tc_fence_before();
-        __syncthreads();                      // everybody's pieces; TMEM reads of tile i-1 are done
-        if (s_abort) break;
-        if (i + 1 < ntiles)
-            load_kv(sKV + (unsigned)((i + 1) & 1) * 2u * KV_BYTES, kcache, vcache, table, lo + (i + 1) * TILE, hi, g, n_kv, page_size);
-        cp_async_commit();
-        if (threadIdx.x == 0) {               // scores = Q . K^T
-            tc_fence_after();
-#pragma unroll
-            for (int kk = 0; kk < HD / 16; kk++) {
-                const unsigned a = sQ + (unsigned)((kk >> 2) * (ROWS * 128) + (kk & 3) * 32);
-                const unsigned b = st + (unsigned)((kk >> 2) * (TILE * 128) + (kk & 3) * 32);
-                umma(tmem, make_desc(a, 16, 1024), make_desc(b, 16, 1024), IDESC_S, kk > 0);
-            }
-            umma_commit(&bar_mma);
-        }
-        wait_mma();
-        // this row's 64 scores -> probabilities
-        const int key0 = lo + i * TILE;
-        float s[TILE];
-        {
-            float (*s2)[32] = reinterpret_cast<float (*)[32]>(s);
-            tmem_ld32(t_s, s2[0]);
-            tmem_ld32(t_s + 32, s2[1]);
-            tmem_ld_wait();
-        }
-        // the mask matters only where the tile crosses this row's diagonal or window edge
-        if (key0 + TILE - 1 > p_row || key0 < w_row) {
-#pragma unroll
-            for (int j = 0; j < TILE; j++) {
-                const int key = key0 + j;
-                if (key > p_row || key < w_row) s[j] = -INFINITY;
-            }
-        }
-        float mx = s[0];
-#pragma unroll
-        for (int j = 1; j < TILE; j++) mx = fmaxf(mx, s[j]);
-        const float m_new = fmaxf(m_run, mx);
-        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;       // a row that has seen no key yet
-        const float corr = exp2f((m_run - m_use) * scale_log2e);
-        m_run = m_new;
-        const float neg = -m_use * scale_log2e;                       // p = 2^(s * scale - m * scale): one FMA each
-        float sum = 0.f;
-#pragma unroll
-        for (int j = 0; j < TILE; j++) {
-            s[j] = fast_exp2(fmaf(s[j], scale_log2e, neg));
-            sum += s[j];
-        }
-        l_run = l_run * corr + sum;
-#pragma unroll
-        for (int c = 0; c < 8; c++) {          // 8 keys = 16 bytes per piece, swizzled like an operand row
-            uint4 pk;
-            pk.x = pack_bf16(s[8 * c], s[8 * c + 1]);
-            pk.y = pack_bf16(s[8 * c + 2], s[8 * c + 3]);
-            pk.z = pack_bf16(s[8 * c + 4], s[8 * c + 5]);
-            pk.w = pack_bf16(s[8 * c + 6], s[8 * c + 7]);
-            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(sP + swz(row, c)), "r"(pk.x), "r"(pk.y), "r"(pk.z), "r"(pk.w) : "memory");
-        }
-        fence_async_smem();
-        tc_fence_before();
-        __syncthreads();                      // P complete; everybody has read the scores out of TMEM
-        if (threadIdx.x == 0) {               // output tile = P . V
-            tc_fence_after();
-#pragma unroll
-            for (int kk = 0; kk < TILE / 16; kk++) {
-                const unsigned a = sP + (unsigned)(kk * 32);
-                const unsigned b = st + KV_BYTES + (unsigned)(kk * 2048);
-                umma(tmem + 64, make_desc(a, 16, 1024), make_desc(b, TILE * 128, 1024), IDESC_O, kk > 0);
-            }
-            umma_commit(&bar_mma);
-        }
-        wait_mma();
-#pragma unroll
-        for (int cb = 0; cb < HD / 32; cb++) {
-            float t[32];
-            tmem_ld32(t_o + cb * 32, t);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 32; j++) o_acc[cb * 32 + j] = o_acc[cb * 32 + j] * corr + t[j];
-        }
-    }
-    cp_async_wait<0>();
-    if (valid_row && !s_abort) {
-        const float inv = 1.f / l_run;
-        bf16* orow = out + (int64_t)(tok0 + tt) * n_heads * HD + (int64_t)(g * gs + hh) * HD;
-#pragma unroll
-        for (int c = 0; c < HD / 8; c++) {
-            uint4 pk;
-            pk.x = pack_bf16(o_acc[8 * c] * inv, o_acc[8 * c + 1] * inv);
-            pk.y = pack_bf16(o_acc[8 * c + 2] * inv, o_acc[8 * c + 3] * inv);
-            pk.z = pack_bf16(o_acc[8 * c + 4] * inv, o_acc[8 * c + 5] * inv);
-            pk.w = pack_bf16(o_acc[8 * c + 6] * inv, o_acc[8 * c + 7] * inv);
-            *reinterpret_cast<uint4*>(orow + 8 * c) = pk;
-        }
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 0)
+    if (warp == 4)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS));
 }
 
@@ -364,7 +436,8 @@ extern "C" int kllm_attention_tcgen05_head_dim() { return HD; }
 
 // Same contract as the mma.sync prefill kernel: requests' portions
 // q_start[s]..q_start[s+1] start at cache position start_pos[s]; out [n, n_heads*HD].
-// status: device int, set to 1 if a bounded wait ran out.
+// status: device int that a bounded wait which ran out sets (1: loader, 2-5: tensor-core
+// issuer, 6-8: softmax).
 extern "C" int kllm_attention_prefill_tcgen05(void* out, const void* q, int64_t q_stride, const void* kcache,
                                               const void* vcache, const int* q_start, const int* start_pos,
                                               const int* block_table, int max_blocks, int n_tokens,
