@@ -21,9 +21,16 @@
 //            the output tile in TMEM once the probabilities are in shared memory;
 //   warps 0-3  softmax: every thread owns one row, reads its 64 scores from TMEM
 //            (tcgen05.ld 32x32b), applies the mask and the online-softmax recurrence
-//            without any cross-thread traffic, adds the previous tile's P.V result
-//            (rescaled) to its float32 accumulator in registers, and writes its
-//            probabilities as bfloat16 into a swizzled shared-memory tile.
+//            without any cross-thread traffic, and writes its probabilities as bfloat16
+//            into one of two swizzled shared-memory tiles.
+//
+// The output accumulates in TMEM over all tiles (P.V with accumulation); a row's
+// probabilities are taken relative to a reference maximum that is only moved when the
+// running maximum has grown by more than a factor 2^8 since (then the row of the
+// accumulator is read, rescaled and written back, tcgen05.ld / tcgen05.st, between two
+// P.V products).  Sum and output share the reference, so the quotient at the end is the
+// softmax-weighted mean exactly as with a reference moved at every tile; what a row does
+// depends on its own scores only.
 //
 // Every wait on an mbarrier is bounded by a cycle count: a wait that runs out raises a
 // flag in shared memory and sets the status word, every role leaves its loop, and the
@@ -49,9 +56,10 @@ constexpr int THREADS = 192;                          // 4 softmax warps, the MM
 constexpr int SOFTMAX_THREADS = 128;
 constexpr int Q_BYTES = PANELS * ROWS * 128;          // [panel][128 rows][64 dims]
 constexpr int KV_BYTES = PANELS * TILE * 128;         // [panel][64 keys][64 dims]
-constexpr int P_BYTES = ROWS * 128;                   // [128 rows][64 keys]
+constexpr int P_BYTES = ROWS * 128;                   // [128 rows][64 keys], two of them
 constexpr int STAGES = HD == 64 ? 3 : 2;
-constexpr int SMEM_BYTES = 1024 + Q_BYTES + P_BYTES + STAGES * 2 * KV_BYTES;
+constexpr int SMEM_BYTES = 1024 + Q_BYTES + 2 * P_BYTES + STAGES * 2 * KV_BYTES;
+constexpr float kRescaleAt = 8.f;                     // move a row's reference when its maximum grew by 2^8
 constexpr int TMEM_COLS = 256;                        // two score buffers (2 x 64) + output tile (HD): a power of two
 constexpr long long kCycleLimit = 4000000000LL;       // about two seconds
 
@@ -119,6 +127,18 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, float (&v)[32]) {
                    "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                  : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void tmem_st32(unsigned taddr, const float (&v)[32]) {
+    const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+                 "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                   "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                   "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 
 // byte offset of 16-byte piece `ch` (0..7) of row `r` inside a swizzled panel of 128-byte rows
@@ -212,7 +232,7 @@ attn_prefill_tc5_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int6
                         int n_kv, int page_size, int window, float scale_log2e, int tokens_per_tile, int* status) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bar_kv_full[STAGES], bar_kv_empty[STAGES], bar_q_full, bar_s_full[2], bar_s_free[2],
-        bar_p_full, bar_o_full;
+        bar_p_full, bar_o_full[2];
     __shared__ unsigned s_tmem;
     __shared__ int s_req, s_tok0, s_abort;
     const int g = blockIdx.y;
@@ -231,7 +251,7 @@ attn_prefill_tc5_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int6
         mbar_init(&bar_q_full, 32);
         for (int b = 0; b < 2; b++) { mbar_init(&bar_s_full[b], 1); mbar_init(&bar_s_free[b], SOFTMAX_THREADS); }
         mbar_init(&bar_p_full, SOFTMAX_THREADS);
-        mbar_init(&bar_o_full, 1);
+        for (int b = 0; b < 2; b++) mbar_init(&bar_o_full[b], 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncthreads();
@@ -257,7 +277,7 @@ attn_prefill_tc5_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int6
     volatile int* abort_flag = &s_abort;
 
     const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;       // swizzled tiles want 1024-byte alignment
-    const unsigned sQ = base, sP = base + Q_BYTES, sKV = sP + P_BYTES;
+    const unsigned sQ = base, sP = base + Q_BYTES, sKV = sP + 2 * P_BYTES;
 
     if (warp == 5) {
         // ---- loader ----------------------------------------------------------------
@@ -306,15 +326,15 @@ attn_prefill_tc5_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int6
             ok = mbar_wait(&bar_p_full, (unsigned)j & 1u, abort_flag, status, 5);
             if (!ok) break;
             tc_fence_after();
-            if (lane == 0) {                   // output tile = P . V
+            if (lane == 0) {                   // output += P . V
                 const unsigned st = sKV + (unsigned)(j % STAGES) * 2u * KV_BYTES;
 #pragma unroll
                 for (int kk = 0; kk < TILE / 16; kk++) {
-                    const unsigned a = sP + (unsigned)(kk * 32);
+                    const unsigned a = sP + (unsigned)((j & 1) * P_BYTES + kk * 32);
                     const unsigned bb = st + KV_BYTES + (unsigned)(kk * 2048);
-                    umma(tmem + 128, make_desc(a, 16, 1024), make_desc(bb, TILE * 128, 1024), IDESC_O, kk > 0);
+                    umma(tmem + 128, make_desc(a, 16, 1024), make_desc(bb, TILE * 128, 1024), IDESC_O, j > 0 || kk > 0);
                 }
-                umma_commit(&bar_o_full);
+                umma_commit(&bar_o_full[j & 1]);
                 umma_commit(&bar_kv_empty[j % STAGES]);
             }
             __syncwarp();
@@ -328,20 +348,7 @@ attn_prefill_tc5_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int6
         const int w_row = (window > 0) ? p_row + 1 - window : 0;
         const unsigned lane_base = (unsigned)(warp * 32) << 16;
         const unsigned t_o = tmem + lane_base + 128;
-        float o_acc[HD];
-#pragma unroll
-        for (int i = 0; i < HD; i++) o_acc[i] = 0.f;
-        float m_run = -INFINITY, l_run = 0.f, corr_pending = 1.f;
-        auto add_output_tile = [&]() {         // o_acc = o_acc * (its tile's correction) + P.V of that tile
-#pragma unroll
-            for (int cb = 0; cb < HD / 32; cb++) {
-                float t[32];
-                tmem_ld32(t_o + cb * 32, t);
-                tmem_ld_wait();
-#pragma unroll
-                for (int jj = 0; jj < 32; jj++) o_acc[cb * 32 + jj] = o_acc[cb * 32 + jj] * corr_pending + t[jj];
-            }
-        };
+        float m_ref = -INFINITY, l_run = 0.f;          // the row's reference maximum; its sum relative to it
         bool ok = true;
         for (int j = 0; j < ntiles; j++) {
             const int b = j & 1;
@@ -371,11 +378,32 @@ attn_prefill_tc5_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int6
 #pragma unroll
             for (int jj = 4; jj < TILE; jj++) mx4[jj & 3] = fmaxf(mx4[jj & 3], s[jj]);
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            const float m_new = fmaxf(m_run, mx);
-            const float m_use = (m_new == -INFINITY) ? 0.f : m_new;       // a row that has seen no key yet
-            const float corr = exp2f((m_run - m_use) * scale_log2e);
-            m_run = m_new;
-            const float neg = -m_use * scale_log2e;                       // p = 2^(s * scale - m * scale): one FMA each
+            // move the reference only for a first key or a maximum that outgrew it by 2^8
+            const bool move = mx > m_ref && (mx - m_ref) * scale_log2e > kRescaleAt;
+            float corr = 1.f;
+            if (move) {
+                corr = (m_ref == -INFINITY) ? 0.f : exp2f((m_ref - mx) * scale_log2e);
+                m_ref = mx;
+            }
+            if (j > 0 && __any_sync(0xffffffffu, move)) {
+                // rows of this warp rescale what the products so far have added up (rows that
+                // did not move multiply by one); the product of tile j - 1 must be over, the
+                // one of tile j waits for this thread's probabilities
+                ok = mbar_wait(&bar_o_full[(j - 1) & 1], ((unsigned)((j - 1) >> 1)) & 1u, abort_flag, status, 7);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int cb = 0; cb < HD / 32; cb++) {
+                    float t[32];
+                    tmem_ld32(t_o + cb * 32, t);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int jj = 0; jj < 32; jj++) t[jj] *= corr;
+                    tmem_st32(t_o + cb * 32, t);
+                }
+                tmem_st_wait();
+            }
+            const float neg = (m_ref == -INFINITY) ? 0.f : -m_ref * scale_log2e;   // p = 2^(s * scale - m * scale): one FMA each
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int jj = 0; jj < TILE; jj++) {
@@ -383,13 +411,11 @@ attn_prefill_tc5_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int6
                 sum4[jj & 3] += s[jj];
             }
             l_run = l_run * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-            if (j > 0) {                       // the product of tile j - 1 has had the whole softmax to finish
-                ok = mbar_wait(&bar_o_full, (unsigned)(j - 1) & 1u, abort_flag, status, 7);
+            if (j >= 2) {                      // this P buffer was read by the product of tile j - 2
+                ok = mbar_wait(&bar_o_full[b], ((unsigned)((j - 2) >> 1)) & 1u, abort_flag, status, 8);
                 if (!ok) break;
-                tc_fence_after();
-                add_output_tile();
             }
-            corr_pending = corr;
+            const unsigned sPb = sP + (unsigned)(b * P_BYTES);
 #pragma unroll
             for (int c = 0; c < 8; c++) {      // 8 keys = 16 bytes per piece, swizzled like an operand row
                 uint4 pk;
@@ -397,27 +423,32 @@ attn_prefill_tc5_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int6
                 pk.y = pack_bf16(s[8 * c + 2], s[8 * c + 3]);
                 pk.z = pack_bf16(s[8 * c + 4], s[8 * c + 5]);
                 pk.w = pack_bf16(s[8 * c + 6], s[8 * c + 7]);
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(sP + swz(row, c)), "r"(pk.x), "r"(pk.y), "r"(pk.z), "r"(pk.w) : "memory");
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(sPb + swz(row, c)), "r"(pk.x), "r"(pk.y), "r"(pk.z), "r"(pk.w) : "memory");
             }
             fence_async_smem();
             tc_fence_before();
-            mbar_arrive(&bar_p_full);          // P of tile j is in shared memory, the output tile has been read
+            mbar_arrive(&bar_p_full);          // P of tile j is in shared memory, the accumulator is rescaled
         }
-        if (ok) ok = mbar_wait(&bar_o_full, (unsigned)(ntiles - 1) & 1u, abort_flag, status, 8);
+        if (ok) ok = mbar_wait(&bar_o_full[(ntiles - 1) & 1], ((unsigned)((ntiles - 1) >> 1)) & 1u, abort_flag, status, 9);
         if (ok) {
             tc_fence_after();
-            add_output_tile();
-            if (valid_row) {
-                const float inv = 1.f / l_run;
-                bf16* orow = out + (int64_t)(tok0 + tt) * n_heads * HD + (int64_t)(g * gs + hh) * HD;
+            const float inv = 1.f / l_run;
+            bf16* orow = out + (int64_t)(tok0 + tt) * n_heads * HD + (int64_t)(g * gs + hh) * HD;
 #pragma unroll
-                for (int c = 0; c < HD / 8; c++) {
-                    uint4 pk;
-                    pk.x = pack_bf16(o_acc[8 * c] * inv, o_acc[8 * c + 1] * inv);
-                    pk.y = pack_bf16(o_acc[8 * c + 2] * inv, o_acc[8 * c + 3] * inv);
-                    pk.z = pack_bf16(o_acc[8 * c + 4] * inv, o_acc[8 * c + 5] * inv);
-                    pk.w = pack_bf16(o_acc[8 * c + 6] * inv, o_acc[8 * c + 7] * inv);
-                    *reinterpret_cast<uint4*>(orow + 8 * c) = pk;
+            for (int cb = 0; cb < HD / 32; cb++) {
+                float t[32];
+                tmem_ld32(t_o + cb * 32, t);
+                tmem_ld_wait();
+                if (valid_row) {
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        uint4 pk;
+                        pk.x = pack_bf16(t[8 * c] * inv, t[8 * c + 1] * inv);
+                        pk.y = pack_bf16(t[8 * c + 2] * inv, t[8 * c + 3] * inv);
+                        pk.z = pack_bf16(t[8 * c + 4] * inv, t[8 * c + 5] * inv);
+                        pk.w = pack_bf16(t[8 * c + 6] * inv, t[8 * c + 7] * inv);
+                        *reinterpret_cast<uint4*>(orow + cb * 32 + 8 * c) = pk;
+                    }
                 }
             }
         }
@@ -437,7 +468,7 @@ extern "C" int kllm_attention_tcgen05_head_dim() { return HD; }
 // Same contract as the mma.sync prefill kernel: requests' portions
 // q_start[s]..q_start[s+1] start at cache position start_pos[s]; out [n, n_heads*HD].
 // status: device int that a bounded wait which ran out sets (1: loader, 2-5: tensor-core
-// issuer, 6-8: softmax).
+// issuer, 6-9: softmax).
 extern "C" int kllm_attention_prefill_tcgen05(void* out, const void* q, int64_t q_stride, const void* kcache,
                                               const void* vcache, const int* q_start, const int* start_pos,
                                               const int* block_table, int max_blocks, int n_tokens,
