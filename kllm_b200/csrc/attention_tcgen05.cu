@@ -232,7 +232,7 @@ attn_prefill_tc5_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int6
                         int n_kv, int page_size, int window, float scale_log2e, int tokens_per_tile, int* status) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bar_kv_full[STAGES], bar_kv_empty[STAGES], bar_q_full, bar_s_full[2], bar_s_free[2],
-        bar_p_full, bar_o_full[2];
+        bar_p_full[2], bar_o_full[2];
     __shared__ unsigned s_tmem;
     __shared__ int s_req, s_tok0, s_abort;
     const int g = blockIdx.y;
@@ -250,7 +250,7 @@ attn_prefill_tc5_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int6
         for (int s = 0; s < STAGES; s++) { mbar_init(&bar_kv_full[s], 32); mbar_init(&bar_kv_empty[s], 1); }
         mbar_init(&bar_q_full, 32);
         for (int b = 0; b < 2; b++) { mbar_init(&bar_s_full[b], 1); mbar_init(&bar_s_free[b], SOFTMAX_THREADS); }
-        mbar_init(&bar_p_full, SOFTMAX_THREADS);
+        for (int b = 0; b < 2; b++) mbar_init(&bar_p_full[b], SOFTMAX_THREADS);
         for (int b = 0; b < 2; b++) mbar_init(&bar_o_full[b], 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -298,6 +298,9 @@ attn_prefill_tc5_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int6
         cp_async_wait<0>();                    // nothing of this warp is in flight when the CTA ends
     } else if (warp == 4) {
         // ---- tensor-core issuer ----------------------------------------------------
+        // (every barrier is waited on by parity, so none may complete twice before its
+        // waiter has looked: the probabilities' barrier, like their buffer, exists twice,
+        // and a buffer's next round needs the product that this warp issues)
         constexpr uint32_t IDESC_S = make_idesc(ROWS, TILE, false);
         constexpr uint32_t IDESC_O = make_idesc(ROWS, HD, true);
         bool ok = mbar_wait(&bar_q_full, 0, abort_flag, status, 2);
@@ -323,7 +326,7 @@ attn_prefill_tc5_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int6
         if (ok) ok = issue_scores(0);
         for (int j = 0; ok && j < ntiles; j++) {
             if (j + 1 < ntiles) { ok = issue_scores(j + 1); if (!ok) break; }     // runs while tile j is in the softmax
-            ok = mbar_wait(&bar_p_full, (unsigned)j & 1u, abort_flag, status, 5);
+            ok = mbar_wait(&bar_p_full[j & 1], ((unsigned)(j >> 1)) & 1u, abort_flag, status, 5);
             if (!ok) break;
             tc_fence_after();
             if (lane == 0) {                   // output += P . V
@@ -427,7 +430,7 @@ attn_prefill_tc5_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int6
             }
             fence_async_smem();
             tc_fence_before();
-            mbar_arrive(&bar_p_full);          // P of tile j is in shared memory, the accumulator is rescaled
+            mbar_arrive(&bar_p_full[b]);       // P of tile j is in shared memory, the accumulator is rescaled
         }
         if (ok) ok = mbar_wait(&bar_o_full[(ntiles - 1) & 1], ((unsigned)((ntiles - 1) >> 1)) & 1u, abort_flag, status, 9);
         if (ok) {

@@ -329,9 +329,11 @@ def status_word(device) -> torch.Tensor:
 def check_status(device) -> None:
     """Raise if a kernel reported that a bounded wait (on an mbarrier) ran out; its
     results are then not valid.  Synchronises the device."""
-    if int(status_word(device).item()) != 0:
+    code = int(status_word(device).item())
+    if code != 0:
         status_word(device).zero_()
-        raise KernelError("a kernel gave up waiting on an mbarrier; its results are not valid")
+        raise KernelError(f"a kernel gave up waiting on an mbarrier (wait number {code} in its source); "
+                          "its results are not valid")
 
 
 TIMELINE_TAGS = {200: "attn_decode_fused", 201: "attn_decode_fused (merging CTA)"}
