@@ -108,6 +108,50 @@ def model_bytes_and_flops(cfg, layers):
     return per_layer, per_layer * layers + v * d                   # head counted once, embedding rows negligible
 
 
+def reference_arm(args):
+    """--impl reference: the reference's own CUDA backend, float32, through its C ABI
+    (baseline/reference_arm.py), same metric and sizes; one JSON line."""
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline"))
+    import reference_arm as ra
+    why = ra.available()
+    if why:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: the reference runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    cfg = dict(TINYLLAMA)
+    layers_full = cfg["num_hidden_layers"]
+    cfg["num_hidden_layers"] = args.layers or layers_full
+    B, ctx, K, W = args.batch, args.context, args.steps, max(3, args.warmup)
+    points = not args.no_points and args.only == "all"
+    ref = ra.Reference(cfg, max_seqs=max(B, 64 if points else B), max_seq=ctx)
+    clocks = ClockSampler(0)
+    t0 = time.time()
+    ms = ref.decode_run(B, ctx, K, W)
+    t1 = time.time()
+    time.sleep(0.15)
+    clocks.stop()
+    out = {"impl": "reference", "metric": "decode tok/s at batch 8 (TinyLlama 1.1B shape, context 2048)",
+           "value": round(B / (ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+           "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+           "dtype": "fp32", "data": "synthetic token ids, random weights",
+           "config": {"model": "TinyLlama-1.1B shape", "global_batch": B, "seq_len": ctx, "parallelism": "single GPU",
+                      "layers": cfg["num_hidden_layers"], "layers_of_config": layers_full, "page_size": 16,
+                      "how": "reference backend (backend/*.cu, unmodified) through its C ABI te_forward_batch; "
+                             "wall clock around the synchronous call, logits to the host every step as it does"},
+           "clocks": clocks.summary(t0, t1),
+           "e2e": {"value": round(B / (ms * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(ms, 4),
+                   "h2d_bytes_per_step": B * 4 * 3 + B * ref.blocks_per_seq * 4,
+                   "d2h_bytes_per_step": B * cfg["vocab_size"] * 4}}
+    if points:
+        pms = ref.prefill_run(2048)
+        out["prefill"] = {"value": round(2048 / (pms * 1e-3), 1), "tokens": 2048, "ms": round(pms, 3)}
+        out["points"] = {f"decode_b{b}": round(b / (ref.decode_run(b, ctx, max(8, K // 4), 3) * 1e-3), 1) for b in (1, 64)}
+    print(json.dumps(out))
+    return 0
+
+
 def print_timeline(rows, dev_ms):
     """The instrumented kernels of the last step, in time order: for each the phases
     between its marks (mean over the recorded CTAs, microseconds) and how long after the
@@ -162,10 +206,7 @@ def main():
         args.only = "decode"
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference is a Go program with a CUDA backend; pip reports 'not installable: neither "
-                          "setup.py nor pyproject.toml' and no Go toolchain exists here"}))
-        return 0
+        return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
