@@ -500,14 +500,24 @@ def gemm_fits(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue
     return bool(lib.kllm_gemm_tcgen05_fits(*_gemm_args(x, weight, weight_up, out, epilogue)))
 
 
+_sm_count = {}
+
+
 def gemm_pays(n: int, N: int, epilogue: str = "bf16", least: int = 75) -> bool:
     """Whether ``gemm``'s tiles of 128 rows x 256 accumulator columns would keep the
     tensor cores of all SMs busy for at least ``least`` percent of the product's time
-    (full tiles over waves x SMs); below that the library product adapts its tiling better."""
-    if not USE_TCGEN05:
+    (full tiles over waves x SMs); below that the library product adapts its tiling
+    better.  Same arithmetic as kllm_gemm_tcgen05_efficiency, without loading the library."""
+    if not USE_TCGEN05 or n <= 0 or N <= 0:
         return False
-    lib = load_library("gemm_tcgen05")
-    return int(lib.kllm_gemm_tcgen05_efficiency(int(n), int(N), _EPI[epilogue])) >= least
+    dev = torch.cuda.current_device()
+    if dev not in _sm_count:
+        _sm_count[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+    sms = _sm_count[dev]
+    nout = 128 if epilogue == "swiglu" else 256
+    tiles = -(-n // 128) * -(-N // nout)
+    waves = -(-tiles // sms)
+    return 100.0 * (n / 128.0) * (N / float(nout)) / (waves * sms) >= least
 
 
 def gemm(x: torch.Tensor, weight: torch.Tensor, *, epilogue: str = "bf16", out: Optional[torch.Tensor] = None,
