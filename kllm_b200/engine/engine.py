@@ -112,8 +112,11 @@ class Engine:
 
     @torch.no_grad()
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
-        """One batch through the model; see ``StepRunner.run``."""
-        return self.runner.run(entries)
+        """One batch through the model; see ``StepRunner.run``.  The result is the
+        caller's own tensor (a replayed decode step writes into a buffer that the next
+        step overwrites; the scheduler, which samples at once, reads that buffer)."""
+        logits = self.runner.run(entries)
+        return None if logits is None else logits.clone()
 
     @torch.no_grad()
     def generate(self, prompt: Union[Sequence[int], Sequence[Sequence[int]]], max_new_tokens: int = 16,

@@ -80,8 +80,13 @@ class GraphedDecode:
         self.graph = None
         self.logits = None
         self.launches = 0
+        self.copied = None          # event after the last copy of the pinned buffer to the device
 
     def fill(self, entries: Sequence["StepEntry"]) -> None:
+        # the pinned buffer is reused: the copy of the step before must have read it
+        # (a caller that does not read a step's logits back could be that far ahead)
+        if self.copied is not None:
+            self.copied.synchronize()
         o, h, B, W = self.offs, self.h, self.batch, self.width
         h[o[0]:o[1]] = [int(e.tokens[0]) for e in entries]
         start = [e.request.length for e in entries]
@@ -95,6 +100,9 @@ class GraphedDecode:
                 t = e.request.tables[gi]
                 tab[si, :len(t)] = t
         self.dev.copy_(self.host, non_blocking=True)
+        if self.copied is None:
+            self.copied = torch.cuda.Event()
+        self.copied.record()
         self.runner.last_h2d_bytes = self.host.numel() * 4
 
     def run(self, entries: Sequence["StepEntry"]) -> torch.Tensor:
@@ -139,7 +147,7 @@ class StepRunner:
         self.steps = 0
         self.tokens_run = 0
         self.last_h2d_bytes = 0     # bytes of the last step's host-to-device copy
-        self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
+        self.use_graphs = bool(use_graphs) and self.device.type == "cuda" and getattr(model, "graph_safe", True)
         self.graphs = {}            # batch size -> GraphedDecode
 
     # ---- validation --------------------------------------------------------

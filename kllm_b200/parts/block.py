@@ -37,6 +37,10 @@ class PreNormBlock:
     def tensor_specs(self):
         return [s for p in self.parts() for s in p.tensor_specs()]
 
+    @property
+    def graph_safe(self):
+        return all(getattr(p, "graph_safe", True) for p in self.parts())
+
     def bind(self, tensors):
         for p in self.parts():
             p.bind(tensors)

@@ -66,6 +66,13 @@ class DecoderModel:
                 seen.setdefault(s.name, s)
         return list(seen.values())
 
+    @property
+    def graph_safe(self) -> bool:
+        """False when a part says that its forward cannot be captured into a CUDA graph
+        (class or instance attribute ``graph_safe = False``: it reads device data on the
+        host, or its shapes depend on the data)."""
+        return all(getattr(p, "graph_safe", True) for p in self.parts())
+
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         for p in self.parts():
             p.bind(tensors)

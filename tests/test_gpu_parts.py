@@ -265,7 +265,10 @@ def test_block_part_both_routes(dtype, n):
 
 class RunningMeanMixer:
     """out_t = W . mean(x_0..x_t): needs the sum of a request's inputs so far and
-    their count, i.e. per-request state of fixed size, and no pages."""
+    their count, i.e. per-request state of fixed size, and no pages.  It reads slot
+    numbers on the host, so it asks not to be captured into a CUDA graph."""
+
+    graph_safe = False
 
     def __init__(self, spec, env):
         self.d = spec.params["hidden"]
@@ -404,9 +407,166 @@ def test_toy_architecture_with_a_stateful_mixer(tmp_path):
     l4 = eng.step([StepEntry(a, a_ids[17:], range(2)), StepEntry(b, b_ids[10:], [0])]); got_a.append(l4[:2]); got_b.append(l4[2:])
     close(torch.cat(got_a), plain_toy(w, a_ids, d), "float32", "request a")
     close(torch.cat(got_b), plain_toy(w, b_ids, d), "float32", "request b")
+    assert not eng.runner.use_graphs, "a part that is not graph-safe keeps decode steps out of CUDA graphs"
     # a new request in a's slot starts from zero state
     eng.cache.close(a)
     c = eng.cache.open()
     assert c.state_slot == a.state_slot
     close(eng.step([StepEntry(c, b_ids, range(11))]), plain_toy(w, b_ids, d), "float32", "reused state slot")
+    eng.close()
+
+
+# ---- toy parts of the other families: a routed feed-forward, another position encoding ----
+
+class TopOneExperts:
+    """out = p_e . (W_e x) for the expert e with the largest router probability
+    (softmax over the router's float32 logits): a feed-forward with routing."""
+
+    def __init__(self, spec, env):
+        self.d, self.n = spec.params["hidden"], spec.params["experts"]
+        self.p = spec.prefix
+        self.dtype = env.dtype
+
+    def tensor_specs(self):
+        from kllm_b200.parts.spec import TensorSpec
+        return [TensorSpec(self.p + ".router.weight", (self.n, self.d), store="float32")] + \
+               [TensorSpec(f"{self.p}.experts.{e}.weight", (self.d, self.d)) for e in range(self.n)]
+
+    def bind(self, tensors):
+        self.router = tensors[self.p + ".router.weight"]
+        self.experts = [tensors[f"{self.p}.experts.{e}.weight"] for e in range(self.n)]
+
+    def forward(self, xn, ctx):
+        prob = torch.softmax(xn.float() @ self.router.t(), dim=-1)
+        top_p, top_e = prob.max(dim=-1)
+        out = torch.zeros((xn.shape[0], self.d), dtype=torch.float32, device=xn.device)
+        for e in range(self.n):          # every expert on every row, the others masked: shapes that a graph can replay
+            gate = torch.where(top_e == e, top_p, torch.zeros_like(top_p))
+            out += gate[:, None] * (xn.float() @ self.experts[e].float().t())
+        return out
+
+
+class HalfSpeedRotary:
+    """Rotary encoding whose angle grows with position / 2 (positions interpolated): a
+    position part with a table of its own, through the same kernels as the built-in one."""
+
+    def __init__(self, spec, env):
+        hd = self.head_dim = spec.params["head_dim"]
+        j = torch.arange(hd // 2, dtype=torch.float64)
+        ang = (torch.arange(env.max_position, dtype=torch.float64) / 2.0)[:, None] * torch.pow(
+            torch.tensor(float(spec.params["theta"]), dtype=torch.float64), -2.0 * j / hd)[None, :]
+        self.cos_sin = torch.cat([torch.cos(ang), torch.sin(ang)], dim=1).to(torch.float32).contiguous().to(env.device)
+
+    def tensor_specs(self):
+        return []
+
+    def bind(self, tensors):
+        pass
+
+    def full_rotary_table(self):
+        return self.cos_sin
+
+    def apply(self, q, k, v, ctx, cache, n_heads, n_kv_heads):
+        from kllm_b200 import kernels
+        kernels.rope_append(q, k, v, self.cos_sin, ctx.positions, ctx.token_req, cache.block_table, cache.k, cache.v,
+                            n_heads, n_kv_heads, self.head_dim)
+
+
+def routed_spec(cfg):
+    from kllm_b200.parts.spec import BlockSpec, LayerCall, ModelSpec, PartSpec
+    d = cfg.hidden
+    norm = {"width": d, "eps": 1e-6}
+    pos = PartSpec("toy_half_speed_rotary", "", {"head_dim": 32, "theta": 50.0})
+    blocks = [BlockSpec("pre_norm", f"l.{i}",
+                        PartSpec("paged_attention", f"l.{i}.attn", {"hidden": d, "n_heads": 2, "n_kv_heads": 2, "head_dim": 32,
+                                                                   "window": 6 if i == 1 else None, "position": pos}),
+                        PartSpec("toy_top_one_experts", f"l.{i}.moe", {"hidden": d, "experts": 3}),
+                        PartSpec("rmsnorm", f"l.{i}.n1", dict(norm)), PartSpec("rmsnorm", f"l.{i}.n2", dict(norm)))
+              for i in range(2)]
+    return ModelSpec(hidden_size=d, vocab_size=cfg.vocab, max_position=64,
+                     embedding=PartSpec("token_embedding", "emb", {"vocab": cfg.vocab, "width": d}),
+                     blocks=blocks, schedule=[LayerCall(0, 0), LayerCall(1, 1)],
+                     final_norm=PartSpec("rmsnorm", "final", dict(norm)),
+                     head=PartSpec("linear_head", "head", {"vocab": cfg.vocab, "width": d, "tied_to": None}))
+
+
+def plain_routed(w, ids, d, rnd=lambda a: a):
+    n = len(ids)
+    x = plain.embed(w["emb.weight"], ids)
+    pos = np.arange(n) / 2.0
+    for i in range(2):
+        p = f"l.{i}.attn."
+        xn = rnd(plain.rmsnorm(x, w[f"l.{i}.n1.weight"], 1e-6))
+        q = rnd(plain.rope(rnd(xn @ plain.f64(w[p + "q_proj.weight"]).T), pos, 2, 32, 50.0))
+        k = rnd(plain.rope(rnd(xn @ plain.f64(w[p + "k_proj.weight"]).T), pos, 2, 32, 50.0))
+        v = rnd(xn @ plain.f64(w[p + "v_proj.weight"]).T)
+        att = rnd(plain.attention(q, k, v, 2, 2, 32, window=6 if i == 1 else None,
+                                  rnd_p=None if rnd(np.float64(1 / 3)) == 1 / 3 else plain.round_act_bf16))
+        x = x + att @ plain.f64(w[p + "o_proj.weight"]).T
+        xn = rnd(plain.rmsnorm(x, w[f"l.{i}.n2.weight"], 1e-6))
+        logits = xn @ plain.f64(w[f"l.{i}.moe.router.weight"]).T
+        prob = np.exp(logits - logits.max(-1, keepdims=True))
+        prob /= prob.sum(-1, keepdims=True)
+        e = prob.argmax(-1)
+        out = np.stack([prob[t, e[t]] * (xn[t] @ plain.f64(w[f"l.{i}.moe.experts.{e[t]}.weight"]).T) for t in range(n)])
+        x = x + out
+    return plain.rmsnorm(x, w["final.weight"], 1e-6) @ plain.f64(w["head.weight"]).T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_with_routed_experts_and_its_own_position_encoding(tmp_path, dtype):
+    """A feed-forward with routing and a position encoding that the framework does not
+    have, registered from here; whole prompts, portions, and tokens one by one (which
+    takes the decode attention kernel with the toy part's table) agree with the plain
+    sum.  One layer has a window, so the cache manager keeps two groups of pages."""
+    import json
+    from kllm_b200.config import ModelConfig, register_architecture
+    from kllm_b200.engine import Engine, Options, StepEntry
+    from kllm_b200.parts.spec import register_part
+    from kllm_b200.weights import save_tensors
+
+    @dataclass(frozen=True)
+    class RoutedConfig(ModelConfig):
+        hidden: int = 64
+        vocab: int = 48
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(architecture=d["architectures"][0], hidden=d["hidden"], vocab=d["vocab"])
+
+    register_part("feed_forward", "toy_top_one_experts", TopOneExperts)
+    register_part("position", "toy_half_speed_rotary", HalfSpeedRotary)
+    register_architecture("ToyRoutedLM", RoutedConfig, routed_spec)
+
+    d = 64
+    rng = np.random.default_rng(11)
+    mat = lambda r, c, s=0.2: (rng.standard_normal((r, c)) * s).astype(np.float32)
+    w = {"emb.weight": mat(48, d, 1.0), "head.weight": mat(48, d), "final.weight": np.ones(d, np.float32)}
+    for i in range(2):
+        w.update({f"l.{i}.n1.weight": (1 + 0.1 * rng.standard_normal(d)).astype(np.float32),
+                  f"l.{i}.n2.weight": np.ones(d, np.float32),
+                  f"l.{i}.attn.q_proj.weight": mat(64, d, 0.4), f"l.{i}.attn.k_proj.weight": mat(64, d, 0.4),
+                  f"l.{i}.attn.v_proj.weight": mat(64, d), f"l.{i}.attn.o_proj.weight": mat(d, 64),
+                  f"l.{i}.moe.router.weight": mat(3, d, 1.5)})      # far apart: no routing decision near a tie
+        w.update({f"l.{i}.moe.experts.{e}.weight": mat(d, d) for e in range(3)})
+    model_dir = tmp_path / "routed"
+    model_dir.mkdir()
+    (model_dir / "config.json").write_text(json.dumps({"architectures": ["ToyRoutedLM"], "hidden": d, "vocab": 48}))
+    store = lambda k, v: torch.from_numpy(v) if (v.ndim == 1 or "router" in k or dtype == "float32") \
+        else torch.from_numpy(v).to(torch.bfloat16)
+    save_tensors(str(model_dir / "model.safetensors"), {k: store(k, v) for k, v in w.items()})
+    ws = {k: (v if (v.ndim == 1 or "router" in k) else stored(v, dtype)) for k, v in w.items()}
+    rnd = plain.round_act_bf16 if dtype == "bfloat16" else (lambda a: a)
+
+    eng = Engine(str(model_dir), Options(dtype=dtype, max_seq=64, block_size=4, num_blocks=40, max_batch=2))
+    assert len(eng.cache.groups) == 2, "a full and a windowed group of pages"
+    ids = rng.integers(0, 48, 37).tolist()
+    want = plain_routed(ws, ids, d, rnd)
+    a = eng.cache.open()
+    close(eng.step([StepEntry(a, ids, range(37))]), want, dtype, "whole prompt")
+    b = eng.cache.open()
+    got = [eng.step([StepEntry(b, ids[:9], range(9))]), eng.step([StepEntry(b, ids[9:11], range(2))]),
+           eng.step([StepEntry(b, ids[11:30], range(19))])]
+    got += [eng.step([StepEntry(b, ids[t:t + 1], [0])]) for t in range(30, 37)]       # one by one
+    close(torch.cat(got), want, dtype, "portions, then token by token")
     eng.close()
