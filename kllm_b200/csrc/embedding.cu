@@ -3,7 +3,10 @@
 //   x[t,:] = float32(E[ids[t],:])      (reference backend/model.cu:89-95)
 //
 // The residual stream that this fills is float32 whatever the table's element
-// type is.  An id outside [0, vocab) never indexes the table: its row is filled
+// type is.  A negative id -(s + 1) stands for "the token that the sampling kernel chose
+// for request slot s in the step before", which is still on the device in
+// last_token[s]: the host may launch a step before it has read the previous one's
+// tokens.  Any other id outside [0, vocab) never indexes the table: its row is filled
 // with NaN so the fault shows in the logits (ids are validated on the host before).
 #include "common.cuh"
 
@@ -13,11 +16,12 @@ namespace {
 
 template <typename T>
 __global__ void embed_kernel(float* __restrict__ x, const T* __restrict__ table,
-                             const int* __restrict__ ids, int d, int vocab) {
+                             const int* __restrict__ ids, const int* __restrict__ last_token, int d, int vocab) {
     griddep_wait();
     griddep_launch();
     const int t = blockIdx.x;
-    const int id = ids[t];
+    int id = ids[t];
+    if (id < 0 && last_token != nullptr) id = last_token[-id - 1];
     float* xr = x + (int64_t)t * d;
     if (id < 0 || id >= vocab) {
         for (int i = threadIdx.x; i < d; i += blockDim.x) xr[i] = __int_as_float(0x7fc00000);
@@ -47,15 +51,16 @@ __global__ void gather_rows_kernel(char* __restrict__ out, const char* __restric
 
 }  // namespace
 
-extern "C" int kllm_embed(void* x, const void* table, const int* ids, int n, int d, int vocab,
-                          int dtype, void* stream) {
+// last_token: optional int32 table indexed by request slot (see above).
+extern "C" int kllm_embed(void* x, const void* table, const int* ids, const int* last_token, int n, int d,
+                          int vocab, int dtype, void* stream) {
     if (n <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = d >= 1024 ? 256 : 128;
     if (dtype == KLLM_F32)
-        kllm_launch((embed_kernel<float>), dim3(n), dim3(threads), 0, s, (float*)x, (const float*)table, ids, d, vocab);
+        kllm_launch((embed_kernel<float>), dim3(n), dim3(threads), 0, s, (float*)x, (const float*)table, ids, last_token, d, vocab);
     else if (dtype == KLLM_BF16)
-        kllm_launch((embed_kernel<bf16>), dim3(n), dim3(threads), 0, s, (float*)x, (const bf16*)table, ids, d, vocab);
+        kllm_launch((embed_kernel<bf16>), dim3(n), dim3(threads), 0, s, (float*)x, (const bf16*)table, ids, last_token, d, vocab);
     else
         KLLM_FAIL("embed: unknown element type %d", dtype);
     KLLM_LAUNCH_STATUS();

@@ -52,6 +52,58 @@ add_rmsnorm_kernel(float* __restrict__ x, const R* __restrict__ res, T* __restri
     }
 }
 
+// The common case of a step's rows (every row, float32 residual or none, bfloat16 out,
+// width a multiple of 4 up to kThreads * 4 * kVec) in one pass: a thread keeps its
+// elements in registers between the sum of squares and the scaling, 16-byte accesses.
+// Same sums in the same order as the kernel above: thread k adds its elements i = k,
+// k + kThreads, ... in that order (here four neighbours at a time, whose squares are
+// added first; a rounding may differ from the scalar kernel's).
+constexpr int kVec = 8;
+
+__global__ void __launch_bounds__(kThreads)
+add_rmsnorm_vec4_kernel(float* __restrict__ x, const float* __restrict__ res, bf16* __restrict__ out,
+                        const float* __restrict__ gain, int d, float eps) {
+    __shared__ float red[32];
+    griddep_wait();
+    griddep_launch();
+    const int r = blockIdx.x;
+    float4* xr = reinterpret_cast<float4*>(x + (int64_t)r * d);
+    const float4* rr = res ? reinterpret_cast<const float4*>(res + (int64_t)r * d) : nullptr;
+    const float4* g4 = reinterpret_cast<const float4*>(gain);
+    const int n4 = d >> 2;
+    float4 v[kVec];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < kVec; k++) {
+        const int i = threadIdx.x + k * kThreads;
+        if (i < n4) {
+            v[k] = xr[i];
+            if (rr) {
+                const float4 a = rr[i];
+                v[k].x += a.x; v[k].y += a.y; v[k].z += a.z; v[k].w += a.w;
+                xr[i] = v[k];
+            }
+            ss += (v[k].x * v[k].x + v[k].y * v[k].y) + (v[k].z * v[k].z + v[k].w * v[k].w);
+        }
+    }
+    ss = block_sum(ss, red);
+    const float scale = rsqrtf(ss / (float)d + eps);
+    uint2* orow = reinterpret_cast<uint2*>(out + (int64_t)r * d);
+#pragma unroll
+    for (int k = 0; k < kVec; k++) {
+        const int i = threadIdx.x + k * kThreads;
+        if (i < n4) {
+            const float4 g = g4[i];
+            __nv_bfloat162 lo = __floats2bfloat162_rn(v[k].x * scale * g.x, v[k].y * scale * g.y);
+            __nv_bfloat162 hi = __floats2bfloat162_rn(v[k].z * scale * g.z, v[k].w * scale * g.w);
+            uint2 pk;
+            pk.x = *reinterpret_cast<uint32_t*>(&lo);
+            pk.y = *reinterpret_cast<uint32_t*>(&hi);
+            orow[i] = pk;
+        }
+    }
+}
+
 }  // namespace
 
 // dtype: element type of out; res_dtype: element type of res (ignored when res is NULL).
@@ -61,6 +113,13 @@ extern "C" int kllm_add_rmsnorm(void* x, const void* res, void* out, const void*
     if (n_rows <= 0) return 0;
     if (d <= 0) KLLM_FAIL("rmsnorm: width %d must be positive", d);
     cudaStream_t s = (cudaStream_t)stream;
+    auto aligned = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+    if (dtype == KLLM_BF16 && (res == nullptr || res_dtype == KLLM_F32) && rows == nullptr && (d & 3) == 0 &&
+        d <= kThreads * 4 * kVec && aligned(x) && aligned(res) && aligned(gain) && ((uintptr_t)out & 7) == 0) {
+        kllm_launch((add_rmsnorm_vec4_kernel), dim3(n_rows), dim3(kThreads), 0, s, (float*)x, (const float*)res, (bf16*)out,
+                    (const float*)gain, d, eps);
+        KLLM_LAUNCH_STATUS();
+    }
     if (res == nullptr) res_dtype = dtype;
     if (dtype == KLLM_F32 && res_dtype == KLLM_F32) {
         kllm_launch((add_rmsnorm_kernel<float, float>), dim3(n_rows), dim3(kThreads), 0, s, 

@@ -27,7 +27,8 @@ __device__ __forceinline__ void take_better(float& v, int& i, float v2, int i2) 
 
 __global__ void __launch_bounds__(kThreads)
 sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int64_t row_stride,
-              int vocab, const float* __restrict__ temperature, const float* __restrict__ uniform) {
+              int vocab, const float* __restrict__ temperature, const float* __restrict__ uniform,
+              int* __restrict__ last_token, const int* __restrict__ slots) {
     __shared__ float s_val[kWarps];
     __shared__ int s_idx[kWarps];
     __shared__ float s_sum[kWarps];
@@ -75,7 +76,10 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int64_t r
     __syncthreads();
     const float tau = temperature ? temperature[r] : 0.f;
     if (!(tau > 0.f)) {
-        if (tid == 0) out[r] = s_choice;
+        if (tid == 0) {
+            out[r] = s_choice;
+            if (last_token) last_token[slots[r]] = s_choice;
+        }
         return;
     }
     // weights e^((z - max) / tau): a thread's part, then the parts' running sum over the
@@ -142,6 +146,7 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int64_t r
         }
         if (choice < 0) choice = (hi > lo) ? hi - 1 : s_choice;
         out[r] = choice;
+        if (last_token) last_token[slots[r]] = choice;
     }
 }
 
@@ -149,12 +154,16 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int64_t r
 
 // out [rows] int32; logits [rows, vocab] float32 at row_stride elements;
 // temperature, uniform [rows] float32 (temperature may be NULL: all greedy).
+// last_token, slots: optional; row r's choice is also stored at last_token[slots[r]], where
+// the embedding kernel of the next step finds it (see embedding.cu).
 extern "C" int kllm_sample(int* out, const float* logits, int64_t row_stride, int rows, int vocab,
-                           const float* temperature, const float* uniform, void* stream) {
+                           const float* temperature, const float* uniform, int* last_token, const int* slots,
+                           void* stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) KLLM_FAIL("sample: vocabulary %d", vocab);
     if (temperature && !uniform) KLLM_FAIL("sample: temperature given without uniform numbers");
+    if (last_token && !slots) KLLM_FAIL("sample: a token table without the rows' slots");
     kllm_launch((sample_kernel), dim3(rows), dim3(kThreads), 0, (cudaStream_t)stream, out, logits, row_stride, vocab,
-                                                             temperature, uniform);
+                                                             temperature, uniform, last_token, slots);
     KLLM_LAUNCH_STATUS();
 }

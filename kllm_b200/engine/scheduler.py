@@ -21,15 +21,34 @@ differences that the reference names as future work or cannot do:
 
 The decisions are made by ``plan()`` on host data alone (requests, the cache
 manager's counters), so they are tested without a GPU against a fake executor.
+
+With an engine the loop is pipelined: a step is launched before the tokens of the step
+before it have been read.  What a decoding request feeds into that step is then not a
+token id from the host but "whatever was sampled for this request slot", which the
+sampling kernel left on the device (``StepEntry.deferred``); positions, block tables
+and the sampler's counters do not depend on the token.  The host reads a step's tokens
+one step late, while the GPU already runs the next step, so its bookkeeping costs no
+GPU time.  Consequences: a request that ends on an EOS id has one more step in
+flight, whose token is thrown away (a request that ends on its count does not: that is
+known in advance); and before anything is preempted, or when nothing can be planned,
+everything in flight is collected first, so those decisions see complete requests.
+``pipelined=False`` gives the plain loop (launch, read, book-keep), which is also what
+the tests' fake executors get.
 """
 from __future__ import annotations
 
 from collections import deque
 from dataclasses import dataclass, field
-from typing import Callable, Deque, List, Optional, Sequence, Tuple
+from typing import Any, Callable, Deque, List, Optional, Sequence, Tuple
 
 from ..cache.manager import CacheManager, RequestCache
 from .step import StepEntry
+
+PENDING = -1     # stands in a request's tokens for one that was sampled but not read yet
+
+
+class _NeedDrain(Exception):
+    """Planning wants to preempt while steps are in flight: collect them first."""
 
 
 @dataclass
@@ -46,6 +65,8 @@ class Request:
     status: str = "waiting"       # waiting | running | finished | failed
     error: Optional[str] = None
     preemptions: int = 0
+    sampled: int = 0              # tokens drawn for it so far, those not read yet included
+    no_more: bool = False         # its last token (by count) is in flight: nothing more to plan
 
     @property
     def remaining(self) -> int:
@@ -76,17 +97,30 @@ class PlannedEntry:
     wants_logits: bool
 
 
+@dataclass
+class _InFlight:
+    """A launched step whose tokens the host has not read."""
+    rows: List[Tuple[Request, int]]     # per sampled row: the request and where in its tokens the result goes
+    tokens: Any                         # pinned host int32 [rows], filled by an asynchronous copy
+    event: Any                          # recorded after that copy
+
+
 class Scheduler:
     def __init__(self, engine=None, *, cache: Optional[CacheManager] = None,
                  execute: Optional[Callable] = None, max_batch: Optional[int] = None,
                  max_step_tokens: Optional[int] = None, max_seq: Optional[int] = None,
-                 eos_token_ids: Sequence[int] = (), on_pages_out: str = "preempt"):
+                 eos_token_ids: Sequence[int] = (), on_pages_out: str = "preempt",
+                 pipelined: Optional[bool] = None):
         """With an ``Engine`` everything is taken from it.  Tests pass ``cache`` (a
         CacheManager, possibly without device memory) and ``execute(entries, requests)
         -> list of next tokens`` for the entries that want logits."""
         if on_pages_out not in ("preempt", "fail"):
             raise ValueError("on_pages_out is 'preempt' or 'fail'")
         self.engine = engine
+        self.pipelined = (engine is not None and execute is None) if pipelined is None else bool(pipelined)
+        if self.pipelined and (engine is None or execute is not None):
+            raise ValueError("the pipelined loop needs an engine and its own executor")
+        self._inflight: Deque[_InFlight] = deque()
         if engine is not None:
             cache = engine.cache
             execute = execute or self._execute_on_engine
@@ -154,6 +188,8 @@ class Scheduler:
                 return entries
             # live requests but nothing can move: every one waits for pages that the
             # others hold.  The youngest gives way.
+            if self._inflight:
+                raise _NeedDrain()
             self._preempt(self.running[-1])
 
     def _plan_once(self) -> List[PlannedEntry]:
@@ -177,11 +213,13 @@ class Scheduler:
 
         # 1. one token for every request that is decoding, oldest first
         for r in list(self.running):
-            if r.remaining != 1 or r.status != "running":
+            if r.remaining != 1 or r.status != "running" or r.no_more:
                 continue
             if budget <= 0:
                 break
             while not fits(r, 1):
+                if self._inflight:
+                    raise _NeedDrain()
                 if self.on_pages_out == "fail":
                     self._fail(r, "kv reservation failed mid-stream: out of pages")
                     break
@@ -225,8 +263,107 @@ class Scheduler:
         keys = [(r.seed, r.rid, len(r.generated)) for r in wanting]
         return eng.sampler.sample(logits, temps, keys).tolist()
 
+    # ---- the pipelined loop ----------------------------------------------------
+    def _launch(self, plan: List[PlannedEntry]) -> None:
+        eng = self.engine
+        entries, requests = [], []
+        for p in plan:
+            r = p.request
+            toks = r.tokens[r.fed:r.fed + p.n_tokens]
+            entries.append(StepEntry(r.cache, toks, [p.n_tokens - 1] if p.wants_logits else [],
+                                     deferred=(p.n_tokens == 1 and toks[0] == PENDING)))
+            requests.append(r)
+        try:
+            logits = eng.runner.run(entries)
+            wanting = [r for r, e in zip(requests, entries) if e.want]
+            pinned = event = None
+            if logits is not None:
+                import torch
+                ctx = eng.runner.last_ctx
+                if len(wanting) == len(requests):
+                    slots = ctx.state_slots
+                else:
+                    slots = torch.tensor([r.cache.state_slot for r in wanting], dtype=torch.int32).to(
+                        logits.device, non_blocking=True)
+                out = eng.sampler.sample(logits, [r.temperature for r in wanting],
+                                         [(r.seed, r.rid, r.sampled) for r in wanting],
+                                         last_token=eng.runner.last_token, slots=slots)
+                pinned = torch.empty(out.shape[0], dtype=torch.int32, pin_memory=True)
+                pinned.copy_(out, non_blocking=True)
+                event = torch.cuda.Event()
+                event.record()
+        except Exception as e:  # a failed step fails its requests (scheduler.go:197-203)
+            for r in requests:
+                if r.cache is not None and not r.cache.closed:
+                    self.cache.trim_reservation(r.cache)
+                self._fail(r, f"step failed: {e}")
+            raise
+        self.metrics.steps += 1
+        self.metrics.max_batch_seen = max(self.metrics.max_batch_seen, len(plan))
+        self.metrics.pages_high_water = max([self.metrics.pages_high_water] +
+                                            [g.pool.high_water for g in self.cache.groups])
+        rows: List[Tuple[Request, int]] = []
+        for p in plan:
+            r = p.request
+            if p.n_tokens == 1 and r.fed >= len(r.prompt):
+                self.metrics.decode_tokens += 1
+            else:
+                self.metrics.prefill_tokens += p.n_tokens
+            r.fed += p.n_tokens
+            if p.wants_logits:
+                r.tokens.append(PENDING)
+                rows.append((r, len(r.tokens) - 1))
+                r.sampled += 1
+                r.no_more = r.sampled >= r.max_new
+        if rows:
+            self._inflight.append(_InFlight(rows, pinned, event))
+
+    def _collect(self, rec: _InFlight) -> List[Tuple[Request, int]]:
+        rec.event.synchronize()
+        events: List[Tuple[Request, int]] = []
+        for (r, idx), tok in zip(rec.rows, rec.tokens.tolist()):
+            if r.status != "running":        # ended on an EOS id a step earlier: this token is not its
+                continue
+            r.tokens[idx] = tok
+            r.generated.append(tok)
+            self.metrics.generated_tokens += 1
+            events.append((r, tok))
+            if tok in self.eos or len(r.generated) >= r.max_new:
+                del r.tokens[idx + 1:]       # the placeholder of a step launched since
+                self.cache.close(r.cache)    # a step in flight that still reads these pages runs before
+                r.cache = None               # any later step that could be given them (one stream)
+                r.status = "finished"
+                self.running.remove(r)
+                self.metrics.finished += 1
+        return events
+
+    def _collect_all(self) -> List[Tuple[Request, int]]:
+        events: List[Tuple[Request, int]] = []
+        while self._inflight:
+            events += self._collect(self._inflight.popleft())
+        return events
+
+    def _step_pipelined(self) -> List[Tuple[Request, int]]:
+        events: List[Tuple[Request, int]] = []
+        try:
+            plan = self.plan()
+        except _NeedDrain:
+            events += self._collect_all()
+            plan = self.plan()
+        if plan:
+            self._launch(plan)
+        # the step just launched stays in flight; everything before it is read now,
+        # while the GPU works on it
+        keep = 1 if plan else 0
+        while len(self._inflight) > keep:
+            events += self._collect(self._inflight.popleft())
+        return events
+
     def step(self) -> List[Tuple[Request, int]]:
-        """Run one batch; returns (request, new token) for every token generated."""
+        """Run one batch; returns (request, new token) for every token that became known
+        (pipelined: the tokens of the step before the one that this call launches)."""
+        if self.pipelined:
+            return self._step_pipelined()
         plan = self.plan()
         if not plan:
             return []
@@ -275,7 +412,7 @@ class Scheduler:
     def run(self, max_steps: int = 1 << 30) -> None:
         """Step until every submitted request has ended."""
         steps = 0
-        while (self.waiting or self.running) and steps < max_steps:
+        while (self.waiting or self.running or self._inflight) and steps < max_steps:
             before = (len(self.waiting), len(self.running), self.metrics.steps)
             self.step()
             steps += 1
@@ -286,6 +423,7 @@ class Scheduler:
 
     def stop(self) -> None:
         """Fail everything in flight (scheduler.go:130-134)."""
+        self._inflight.clear()
         for r in list(self.running) + list(self.waiting):
             self._fail(r, "scheduler stopped")
         self.waiting.clear()

@@ -36,6 +36,8 @@ class StepEntry:
     request: RequestCache
     tokens: Sequence[int]
     want: Sequence[int] = ()      # places among ``tokens`` whose logits are wanted
+    deferred: bool = False        # the one token is what the sampler chose for this request in the step
+                                  # before; it is still on the device (``tokens`` holds a placeholder)
 
 
 class GraphedDecode:
@@ -61,34 +63,39 @@ class GraphedDecode:
         sizes = [B, B, B, B + 1, B, B, B, B] + [B * self.width for _ in cache.groups]
         self.offs = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
         total = int(self.offs[-1])
-        self.host = torch.empty(total, dtype=torch.int32, pin_memory=True)
-        self.h = self.host.numpy()
+        # two pinned staging buffers that take turns: the host may fill the next step's
+        # while the copy of this step's has not run yet
+        self.hosts = [torch.empty(total, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self.copied = [None, None]                  # event after the last copy out of each staging buffer
+        self.turn = 0
         self.dev = torch.zeros(total, dtype=torch.int32, device=dev)
         o = self.offs
-        self.h[:] = 0
-        self.h[o[2]:o[3]] = np.arange(B)            # token_req: token i belongs to request i
-        self.h[o[3]:o[4]] = np.arange(B + 1)        # q_start
-        self.h[o[7]:o[8]] = np.arange(B)            # every row is wanted
+        for host in self.hosts:
+            h = host.numpy()
+            h[:] = 0
+            h[o[2]:o[3]] = np.arange(B)             # token_req: token i belongs to request i
+            h[o[3]:o[4]] = np.arange(B + 1)         # q_start
+            h[o[7]:o[8]] = np.arange(B)             # every row is wanted
         part = lambda i: self.dev[int(o[i]):int(o[i + 1])]
         tables = {gi: part(8 + gi).view(B, self.width) for gi in range(len(cache.groups))}
         self.ctx = StepContext(
             n_tokens=B, n_requests=B, token_ids=part(0), positions=part(1), token_req=part(2), q_start=part(3),
             start_pos=part(4), ctx_len=part(5), state_slots=part(6), block_tables=tables, want_rows=part(7),
             n_want=B, host_n_new=[1] * B, host_start_pos=[0] * B, max_new=1, max_ctx=runner.max_seq,
-            all_single=True, split_bound=runner.max_seq)
+            all_single=True, split_bound=runner.max_seq, last_token=runner.last_token)
         self.caches = cache.layer_caches(tables)
         self.graph = None
         self.logits = None
         self.launches = 0
-        self.copied = None          # event after the last copy of the pinned buffer to the device
 
     def fill(self, entries: Sequence["StepEntry"]) -> None:
-        # the pinned buffer is reused: the copy of the step before must have read it
-        # (a caller that does not read a step's logits back could be that far ahead)
-        if self.copied is not None:
-            self.copied.synchronize()
-        o, h, B, W = self.offs, self.h, self.batch, self.width
-        h[o[0]:o[1]] = [int(e.tokens[0]) for e in entries]
+        # a staging buffer is reused every other step: the copy that read it last must be over
+        self.turn ^= 1
+        host = self.hosts[self.turn]
+        if self.copied[self.turn] is not None:
+            self.copied[self.turn].synchronize()
+        o, h, B, W = self.offs, host.numpy(), self.batch, self.width
+        h[o[0]:o[1]] = [-(e.request.state_slot + 1) if e.deferred else int(e.tokens[0]) for e in entries]
         start = [e.request.length for e in entries]
         h[o[1]:o[2]] = start
         h[o[4]:o[5]] = start
@@ -99,11 +106,11 @@ class GraphedDecode:
             for si, e in enumerate(entries):
                 t = e.request.tables[gi]
                 tab[si, :len(t)] = t
-        self.dev.copy_(self.host, non_blocking=True)
-        if self.copied is None:
-            self.copied = torch.cuda.Event()
-        self.copied.record()
-        self.runner.last_h2d_bytes = self.host.numel() * 4
+        self.dev.copy_(host, non_blocking=True)
+        if self.copied[self.turn] is None:
+            self.copied[self.turn] = torch.cuda.Event()
+        self.copied[self.turn].record()
+        self.runner.last_h2d_bytes = host.numel() * 4
 
     def run(self, entries: Sequence["StepEntry"]) -> torch.Tensor:
         from .. import kernels
@@ -149,6 +156,10 @@ class StepRunner:
         self.last_h2d_bytes = 0     # bytes of the last step's host-to-device copy
         self.use_graphs = bool(use_graphs) and self.device.type == "cuda" and getattr(model, "graph_safe", True)
         self.graphs = {}            # batch size -> GraphedDecode
+        # what the sampler chose last for every request slot: a step may be launched
+        # before the host has read the tokens of the step before
+        self.last_token = torch.zeros(cache.max_requests, dtype=torch.int32, device=self.device)
+        self.last_ctx = None        # the batch of the step that ran last, as the device holds it
 
     # ---- validation --------------------------------------------------------
     def release_graphs(self) -> None:
@@ -176,7 +187,9 @@ class StepRunner:
             if r.length + n > self.max_seq:
                 raise StepError(f"request {r.rid}: positions [{r.length},{r.length + n}) exceed the "
                                 f"sequence limit {self.max_seq}")
-            for t in e.tokens:
+            if e.deferred and n != 1:
+                raise StepError(f"request {r.rid}: a deferred entry brings exactly one token")
+            for t in (() if e.deferred else e.tokens):
                 if not (0 <= int(t) < self.vocab):
                     raise StepError(f"request {r.rid}: token id {t} outside the vocabulary of {self.vocab}")
             for w in e.want:
@@ -205,7 +218,8 @@ class StepRunner:
         offs = np.concatenate([[0], np.cumsum(sizes)])
         host = torch.empty(int(offs[-1]), dtype=torch.int32, pin_memory=self.device.type == "cuda")
         h = host.numpy()
-        h[offs[0]:offs[1]] = np.fromiter((int(t) for e in entries for t in e.tokens), dtype=np.int32, count=n)
+        h[offs[0]:offs[1]] = np.fromiter((-(e.request.state_slot + 1) if e.deferred else int(t)
+                                          for e in entries for t in e.tokens), dtype=np.int32, count=n)
         h[offs[1]:offs[2]] = np.concatenate([np.arange(s, s + c, dtype=np.int32) for s, c in zip(start, n_new)])
         h[offs[2]:offs[3]] = np.repeat(np.arange(S, dtype=np.int32), n_new)
         h[offs[3]:offs[4]] = q_start
@@ -231,7 +245,8 @@ class StepRunner:
             q_start=part(3), start_pos=part(4), ctx_len=part(5), state_slots=part(6),
             block_tables=tables, want_rows=part(7)[:R], n_want=R,
             host_n_new=n_new, host_start_pos=start, max_new=max(n_new),
-            max_ctx=max(s + c for s, c in zip(start, n_new)), all_single=all(c == 1 for c in n_new))
+            max_ctx=max(s + c for s, c in zip(start, n_new)), all_single=all(c == 1 for c in n_new),
+            last_token=self.last_token)
 
     # ---- run ---------------------------------------------------------------
     def run(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
@@ -253,9 +268,11 @@ class StepRunner:
                 if g is None:
                     g = self.graphs[len(entries)] = GraphedDecode(self, len(entries))
                 logits = g.run(entries)
+                self.last_ctx = g.ctx
             else:
                 ctx = self.build_context(entries)
                 logits = self.model.forward(ctx, self.cache.layer_caches(ctx.block_tables))
+                self.last_ctx = ctx
         except Exception:
             for r, _ in wants:
                 self.cache.trim_reservation(r)

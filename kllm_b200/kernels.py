@@ -61,17 +61,21 @@ def _i32(t: Optional[torch.Tensor], what: str):
         raise KernelError(f"{what} must be a contiguous int32 tensor")
 
 
-def embed(out_x: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
-    """out_x[t,:] = float32(table[ids[t],:]); out_x float32 [n, d]."""
-    _cuda(out_x, table, ids)
-    _i32(ids, "ids")
+def embed(out_x: torch.Tensor, table: torch.Tensor, ids: torch.Tensor,
+          last_token: Optional[torch.Tensor] = None) -> None:
+    """out_x[t,:] = float32(table[ids[t],:]); out_x float32 [n, d].  With ``last_token``
+    (int32, one entry per request slot) an id -(s + 1) means last_token[s], the token
+    that ``sample`` stored there."""
+    _cuda(out_x, table, ids, last_token)
+    _i32(ids, "ids"); _i32(last_token, "last_token")
     n, d = out_x.shape
     if out_x.dtype != torch.float32 or not out_x.is_contiguous() or not table.is_contiguous():
         raise KernelError("embed: residual stream must be contiguous float32")
     if table.shape[1] != d or ids.numel() != n:
         raise KernelError("embed: shapes do not agree")
     lib = load_library("embedding")
-    rc = lib.kllm_embed(_p(out_x), _p(table), _p(ids), n, d, table.shape[0], dtype_code(table.dtype), _stream())
+    rc = lib.kllm_embed(_p(out_x), _p(table), _p(ids), _p(last_token), n, d, table.shape[0], dtype_code(table.dtype),
+                        _stream())
     _check(lib, "embedding", rc)
 
 
@@ -389,10 +393,14 @@ def silu_mul(out: torch.Tensor, gate: torch.Tensor, up: torch.Tensor) -> None:
 
 
 def sample(out: torch.Tensor, logits: torch.Tensor, temperature: Optional[torch.Tensor],
-           uniform: Optional[torch.Tensor]) -> None:
-    """out[r] = argmax (temperature[r] <= 0) or the inverse CDF of softmax(z/T) at uniform[r]."""
-    _cuda(out, logits, temperature, uniform)
-    _i32(out, "out")
+           uniform: Optional[torch.Tensor], last_token: Optional[torch.Tensor] = None,
+           slots: Optional[torch.Tensor] = None) -> None:
+    """out[r] = argmax (temperature[r] <= 0) or the inverse CDF of softmax(z/T) at uniform[r];
+    with ``last_token`` and ``slots`` (int32 [rows]) also last_token[slots[r]] = out[r]."""
+    _cuda(out, logits, temperature, uniform, last_token, slots)
+    _i32(out, "out"); _i32(last_token, "last_token"); _i32(slots, "slots")
+    if (last_token is None) != (slots is None) or (slots is not None and slots.numel() != logits.shape[0]):
+        raise KernelError("sample: last_token and slots [rows] go together")
     if logits.dtype != torch.float32 or logits.stride(1) != 1:
         raise KernelError("sample: logits must be float32 with dense rows")
     for t in (temperature, uniform):
@@ -400,7 +408,7 @@ def sample(out: torch.Tensor, logits: torch.Tensor, temperature: Optional[torch.
             raise KernelError("sample: temperature and uniform must be float32 [rows]")
     lib = load_library("sampling")
     rc = lib.kllm_sample(_p(out), _p(logits), ctypes.c_int64(logits.stride(0)), logits.shape[0],
-                         logits.shape[1], _p(temperature), _p(uniform), _stream())
+                         logits.shape[1], _p(temperature), _p(uniform), _p(last_token), _p(slots), _stream())
     _check(lib, "sampling", rc)
 
 

@@ -18,7 +18,9 @@ class StepContext:
     request s; ``start_pos[s]`` is its cache length before the step and
     ``ctx_len[s]`` after it.  ``block_tables[g]`` is the [requests, max_blocks]
     table of cache group g (-1 where a request holds no page); ``state_slots[s]``
-    is the request's slot in every per-request state tensor.
+    is the request's slot in every per-request state tensor.  A negative token id
+    -(slot + 1) stands for the token that was sampled for that request slot in the step
+    before and is still on the device, in ``last_token[slot]``.
     """
     n_tokens: int
     n_requests: int
@@ -39,6 +41,7 @@ class StepContext:
     max_ctx: int = 0
     all_single: bool = False   # every request brings exactly one token
     split_bound: int = 0       # context bound that fixes launch shapes (0: use max_ctx)
+    last_token: Optional[torch.Tensor] = None   # int32 [request slots]: the sampler's latest choice per slot
 
 
 @dataclass

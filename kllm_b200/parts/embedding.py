@@ -30,9 +30,9 @@ class TokenEmbedding:
     def bind(self, tensors):
         self.table = tensors[self.name]
 
-    def forward(self, ids):
+    def forward(self, ids, last_token=None):
         x = torch.empty((ids.numel(), self.width), dtype=torch.float32, device=ids.device)
-        kernels.embed(x, self.table, ids)
+        kernels.embed(x, self.table, ids, last_token)
         return x
 
 

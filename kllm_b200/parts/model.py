@@ -98,7 +98,7 @@ class DecoderModel:
     def forward(self, ctx: StepContext, caches: List[LayerCache]) -> Optional[torch.Tensor]:
         """Logits float32 [ctx.n_want, vocab] at ``ctx.want_rows`` (None when no row
         is wanted; the cache is still filled)."""
-        x = self.embedding.forward(ctx.token_ids)
+        x = self.embedding.forward(ctx.token_ids, ctx.last_token)
         pending = None
         for call in self.schedule:
             cache = caches[call.cache]
