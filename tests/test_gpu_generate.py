@@ -138,6 +138,39 @@ def test_scheduler_on_the_gpu_with_pages_running_out(tmp_path):
     eng.close()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_pipelined_loop_equals_the_plain_loop_when_requests_end_early(tmp_path, dtype):
+    """The scheduler launches a step before it has read the tokens of the step before.
+    With an EOS id that requests really produce (taken from a first run), a request's end
+    is seen one step late: the token of the step in flight is dropped and the other
+    requests go on.  Tokens, ends and the pool equal the plain loop's."""
+    from kllm_b200.engine import Engine, Options, Scheduler
+    cfg, w = make_weights("A", dtype)
+    d = write_model_dir(str(tmp_path / "m"), cfg, w)
+    prompts = prompts_for(cfg, [7, 19, 3, 30, 11], seed=31)
+    eng = Engine(d, Options(dtype=dtype, max_seq=128, block_size=4, num_blocks=96, max_batch=4, max_step_tokens=32))
+
+    def run(pipelined, eos=(), max_new=24):
+        sched = Scheduler(eng, eos_token_ids=list(eos), pipelined=pipelined)
+        reqs = [sched.submit(p, max_new if i != 1 else 5) for i, p in enumerate(prompts)]   # one ends on its count
+        sched.run()
+        assert all(r.status == "finished" for r in reqs)
+        eng.cache.audit()
+        assert eng.cache.free_pages() == [96]
+        return [r.generated for r in reqs]
+
+    free = run(False)
+    assert run(True) == free
+    eos = free[0][6]                                   # what request 0 says as its 7th token
+    plain_loop, piped = run(False, [eos]), run(True, [eos])
+    assert piped == plain_loop
+    assert plain_loop[0][-1] == eos and len(plain_loop[0]) <= 7
+    for got, full in zip(plain_loop, free):
+        cut = full.index(eos) + 1 if eos in full else len(full)
+        assert got == full[:cut]
+    eng.close()
+
+
 def test_command_line(tmp_path):
     cfg, w = make_weights("A")
     d = write_model_dir(str(tmp_path / "m"), cfg, w)
