@@ -101,8 +101,18 @@ class PlannedEntry:
 class _InFlight:
     """A launched step whose tokens the host has not read."""
     rows: List[Tuple[Request, int]]     # per sampled row: the request and where in its tokens the result goes
-    tokens: Any                         # pinned host int32 [rows], filled by an asynchronous copy
-    event: Any                          # recorded after that copy
+    result: Any                         # what ``launch`` returned: ``result.tokens()`` waits and gives the list
+
+
+class _EngineResult:
+    """Sampled ids on their way to pinned host memory."""
+
+    def __init__(self, pinned, event):
+        self.pinned, self.event = pinned, event
+
+    def tokens(self) -> List[int]:
+        self.event.synchronize()
+        return self.pinned.tolist()
 
 
 class Scheduler:
@@ -110,16 +120,25 @@ class Scheduler:
                  execute: Optional[Callable] = None, max_batch: Optional[int] = None,
                  max_step_tokens: Optional[int] = None, max_seq: Optional[int] = None,
                  eos_token_ids: Sequence[int] = (), on_pages_out: str = "preempt",
-                 pipelined: Optional[bool] = None):
+                 pipelined: Optional[bool] = None, launch: Optional[Callable] = None):
         """With an ``Engine`` everything is taken from it.  Tests pass ``cache`` (a
-        CacheManager, possibly without device memory) and ``execute(entries, requests)
-        -> list of next tokens`` for the entries that want logits."""
+        CacheManager, possibly without device memory) and either ``execute(entries,
+        requests) -> list of next tokens`` for the entries that want logits (plain loop)
+        or ``launch(entries, requests, keys) -> result`` whose ``result.tokens()`` gives
+        that list later (pipelined loop; ``keys`` are the sampler's (seed, request id,
+        index) per wanting entry, and a ``deferred`` entry's token is a placeholder for
+        what the step before sampled for that request)."""
         if on_pages_out not in ("preempt", "fail"):
             raise ValueError("on_pages_out is 'preempt' or 'fail'")
         self.engine = engine
-        self.pipelined = (engine is not None and execute is None) if pipelined is None else bool(pipelined)
-        if self.pipelined and (engine is None or execute is not None):
-            raise ValueError("the pipelined loop needs an engine and its own executor")
+        if pipelined is None:
+            pipelined = launch is not None or (engine is not None and execute is None)
+        self.pipelined = bool(pipelined)
+        if self.pipelined and launch is None:
+            if engine is None or execute is not None:
+                raise ValueError("the pipelined loop needs an engine or a launch function")
+            launch = self._launch_on_engine
+        self.launch = launch
         self._inflight: Deque[_InFlight] = deque()
         if engine is not None:
             cache = engine.cache
@@ -264,8 +283,27 @@ class Scheduler:
         return eng.sampler.sample(logits, temps, keys).tolist()
 
     # ---- the pipelined loop ----------------------------------------------------
-    def _launch(self, plan: List[PlannedEntry]) -> None:
+    def _launch_on_engine(self, entries: List[StepEntry], requests: List[Request], keys):
+        import torch
         eng = self.engine
+        logits = eng.runner.run(entries)
+        if logits is None:
+            return None
+        wanting = [r for r, e in zip(requests, entries) if e.want]
+        if len(wanting) == len(requests):
+            slots = eng.runner.last_ctx.state_slots
+        else:
+            slots = torch.tensor([r.cache.state_slot for r in wanting], dtype=torch.int32).to(
+                logits.device, non_blocking=True)
+        out = eng.sampler.sample(logits, [r.temperature for r in wanting], keys,
+                                 last_token=eng.runner.last_token, slots=slots)
+        pinned = torch.empty(out.shape[0], dtype=torch.int32, pin_memory=True)
+        pinned.copy_(out, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return _EngineResult(pinned, event)
+
+    def _launch(self, plan: List[PlannedEntry]) -> None:
         entries, requests = [], []
         for p in plan:
             r = p.request
@@ -273,25 +311,9 @@ class Scheduler:
             entries.append(StepEntry(r.cache, toks, [p.n_tokens - 1] if p.wants_logits else [],
                                      deferred=(p.n_tokens == 1 and toks[0] == PENDING)))
             requests.append(r)
+        keys = [(r.seed, r.rid, r.sampled) for r, e in zip(requests, entries) if e.want]
         try:
-            logits = eng.runner.run(entries)
-            wanting = [r for r, e in zip(requests, entries) if e.want]
-            pinned = event = None
-            if logits is not None:
-                import torch
-                ctx = eng.runner.last_ctx
-                if len(wanting) == len(requests):
-                    slots = ctx.state_slots
-                else:
-                    slots = torch.tensor([r.cache.state_slot for r in wanting], dtype=torch.int32).to(
-                        logits.device, non_blocking=True)
-                out = eng.sampler.sample(logits, [r.temperature for r in wanting],
-                                         [(r.seed, r.rid, r.sampled) for r in wanting],
-                                         last_token=eng.runner.last_token, slots=slots)
-                pinned = torch.empty(out.shape[0], dtype=torch.int32, pin_memory=True)
-                pinned.copy_(out, non_blocking=True)
-                event = torch.cuda.Event()
-                event.record()
+            result = self.launch(entries, requests, keys)
         except Exception as e:  # a failed step fails its requests (scheduler.go:197-203)
             for r in requests:
                 if r.cache is not None and not r.cache.closed:
@@ -316,12 +338,11 @@ class Scheduler:
                 r.sampled += 1
                 r.no_more = r.sampled >= r.max_new
         if rows:
-            self._inflight.append(_InFlight(rows, pinned, event))
+            self._inflight.append(_InFlight(rows, result))
 
     def _collect(self, rec: _InFlight) -> List[Tuple[Request, int]]:
-        rec.event.synchronize()
         events: List[Tuple[Request, int]] = []
-        for (r, idx), tok in zip(rec.rows, rec.tokens.tolist()):
+        for (r, idx), tok in zip(rec.rows, rec.result.tokens()):
             if r.status != "running":        # ended on an EOS id a step earlier: this token is not its
                 continue
             r.tokens[idx] = tok
@@ -416,7 +437,8 @@ class Scheduler:
             before = (len(self.waiting), len(self.running), self.metrics.steps)
             self.step()
             steps += 1
-            if (len(self.waiting), len(self.running), self.metrics.steps) == before and not self.running:
+            if ((len(self.waiting), len(self.running), self.metrics.steps) == before and not self.running
+                    and not self._inflight and self.waiting):
                 # nothing live, nothing admitted: the head of the queue can never fit
                 r = self.waiting.popleft()
                 self._fail(r, "request cannot be admitted: no pages")

@@ -200,3 +200,105 @@ def test_random_workloads_match_solo_runs(seed):
         assert r.status == "finished" and r.generated == solo(r.prompt, r.max_new), r.rid
     assert cache.free_pages() == [g.pool.n for g in cache.groups]
     cache.audit()
+
+
+# ---- the pipelined loop: a step is launched before the tokens of the step before are read ----
+
+class FakeLauncher(FakeExecutor):
+    """Like the GPU with the pipelined loop: it runs a step when it is launched, keeps
+    what it sampled per request (the device's table of last tokens) and hands the host a
+    result that is read later.  A deferred entry's token is a placeholder; the real one
+    is what this launcher sampled for that request in its step before."""
+
+    def __init__(self, cache, budget, planted_eos=None):
+        super().__init__(cache, budget, planted_eos)
+        self.real = {}            # request id -> every token as the device knows it
+
+    def launch(self, entries, requests, keys):
+        from kllm_b200.engine.scheduler import PENDING
+        assert sum(len(e.tokens) for e in entries) <= self.budget
+        assert self.cache.can_reserve_all([(e.request, len(e.tokens)) for e in entries])
+        self.batches.append([(r.rid, len(e.tokens), bool(e.want)) for e, r in zip(entries, requests)])
+        out, keys = [], list(keys)
+        for e, r in zip(entries, requests):
+            known = self.real.setdefault(r.rid, list(r.prompt))
+            if r.fed == 0:                                   # a new or recomputed request: its tokens are on the host
+                known[:] = [t for t in r.tokens if t != PENDING]
+            toks = list(e.tokens)
+            if e.deferred:
+                assert toks == [PENDING] and len(known) == r.fed + 1
+            else:
+                assert PENDING not in toks and toks == known[r.fed:r.fed + len(toks)]
+            assert e.request.length == r.fed
+            self.cache.reserve(e.request, len(toks))
+            self.cache.commit(e.request, len(toks))
+            if e.want:
+                seed, rid, index = keys.pop(0)
+                assert rid == r.rid and index == len(known) - len(r.prompt)
+                tok = EOS if self.planted_eos.get(r.rid) == index else next_token(known[:r.fed + len(toks)])
+                known.append(tok)
+                out.append(tok)
+        self.cache.audit()
+
+        class Result:
+            def tokens(_):
+                return out
+        return Result()
+
+
+def make_pipelined(num_pages=64, page_size=4, max_batch=4, budget=32, max_seq=256, planted=None):
+    cache = CacheManager(NEED, page_size, num_pages, max_requests=max_batch, allocate=False)
+    ex = FakeLauncher(cache, budget, planted)
+    s = Scheduler(cache=cache, launch=ex.launch, max_batch=max_batch, max_step_tokens=budget, max_seq=max_seq,
+                  eos_token_ids=[EOS])
+    assert s.pipelined
+    return s, ex, cache
+
+
+def test_pipelined_loop_gives_the_solo_tokens_and_lags_one_step():
+    s, ex, cache = make_pipelined()
+    r = s.submit([1, 2, 3, 4, 5], 4)
+    assert s.step() == []                      # launched, nothing read yet
+    ev = s.step()                              # second step launched, first one read
+    assert [t for _, t in ev] == solo([1, 2, 3, 4, 5], 1)
+    s.run()
+    assert r.status == "finished" and r.generated == solo([1, 2, 3, 4, 5], 4)
+    # the count is known in advance: exactly four steps, no step for a fifth token
+    assert ex.batches == [[(0, 5, True)], [(0, 1, True)], [(0, 1, True)], [(0, 1, True)]]
+    assert cache.free_pages() == [64]
+
+
+def test_pipelined_loop_drops_the_token_in_flight_after_an_eos():
+    s, ex, cache = make_pipelined(planted={0: 2})
+    a, b = s.submit([5, 6, 7], 10), s.submit([8, 9], 6)
+    s.run()
+    assert a.generated == solo([5, 6, 7], 2) + [EOS]
+    assert b.generated == solo([8, 9], 6)
+    # a's EOS was sampled in step 2 and read after step 3 was launched: a is in step 3, not in step 4
+    assert [x[0] for x in ex.batches[3]] == [0, 1] and [x[0] for x in ex.batches[4]] == [1]
+    assert a.tokens == [5, 6, 7] + a.generated and cache.free_pages() == [64]
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_pipelined_loop_under_random_load_and_few_pages(seed):
+    """Random prompts, budgets and planted ends with so few pages that requests are
+    preempted: before any preemption what is in flight is read, so every request still
+    says what it says alone."""
+    rng = random.Random(seed)
+    planted = {i: rng.randrange(1, 8) for i in range(12) if rng.random() < 0.4}
+    s, ex, cache = make_pipelined(num_pages=rng.choice([10, 14, 24]), page_size=4, max_batch=rng.choice([2, 3, 4]),
+                                  budget=rng.choice([8, 16, 32]), max_seq=64, planted=planted)
+    reqs = []
+    for i in range(12):
+        reqs.append(s.submit([rng.randrange(90) for _ in range(rng.randrange(1, 20))], rng.randrange(1, 12)))
+        for _ in range(rng.randrange(0, 3)):
+            s.step()
+    s.run()
+    for r in reqs:
+        assert r.status == "finished"
+        want = solo(r.prompt, r.max_new)
+        if r.rid in planted and planted[r.rid] < r.max_new:
+            want = want[:planted[r.rid]] + [EOS]
+        assert r.generated == want, r.rid
+    cache.audit()
+    assert cache.free_pages() == [cache.num_pages] and not s._inflight
