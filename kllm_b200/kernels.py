@@ -488,6 +488,21 @@ def skinny_gemm(weight: torch.Tensor, *, x: Optional[torch.Tensor] = None, x_f32
     return out
 
 
+def linear_add(acc: torch.Tensor, x: torch.Tensor, weight: torch.Tensor) -> None:
+    """acc += x @ weight^T through the vendor GEMM library, acc float32 (the residual
+    stream), the sum formed in float32 inside the product's epilogue: what the reference
+    does in a kernel of its own after cublasSgemm (backend/model.cu:97-110)."""
+    _cuda(acc, x, weight)
+    if torch.backends.cuda.matmul.allow_tf32:
+        raise KernelError("TF32 matmul mode is on; the float32 path must stay true 32-bit")
+    if acc.dtype != torch.float32 or not acc.is_contiguous():
+        raise KernelError("linear_add: the matrix added into must be contiguous float32")
+    if x.dtype == torch.float32:
+        torch.addmm(acc, x, weight.t(), out=acc)
+    else:
+        torch.addmm(acc, x, weight.t(), out_dtype=torch.float32, out=acc)
+
+
 def _gemm_args(x, weight, weight_up, out, epilogue):
     return (_p(x), ctypes.c_int64(x.stride(0)), _p(weight), ctypes.c_int64(weight.stride(0)), _p(weight_up),
             x.shape[0], weight.shape[0], x.shape[1], _p(out), ctypes.c_int64(out.stride(0)), _EPI[epilogue])

@@ -130,10 +130,13 @@ class PagedAttention:
 
     def forward_residual(self, x, norm, ctx, cache):
         n = x.shape[0]
+        w = self.w_qkv if cache.writes else self.w_qkv[:self.q_dim]
         if not (getattr(norm, "fusable_rmsnorm", False) and kernels.skinny_fits(n, self.hidden, self.dtype)
                 and kernels.skinny_fits(n, self.q_dim, self.dtype)):
-            return False
-        w = self.w_qkv if cache.writes else self.w_qkv[:self.q_dim]
+            # larger steps: the library's products, the last one adding into the residual stream
+            q, k, v = self._split(kernels.linear(norm.forward(x, None), w), cache.writes)
+            kernels.linear_add(x, self._attend(q, k, v, ctx, cache), self.w_o)
+            return True
         qkv = kernels.skinny_gemm(w, x_f32=x, gain=norm.gain, eps=norm.eps, epilogue="bf16")
         q, k, v = self._split(qkv, cache.writes)
         attn = self._attend(q, k, v, ctx, cache, prefetch=self._target(0))

@@ -61,9 +61,8 @@ class GatedMLP:
     def _target(self, i):
         return self._after[i] if i < len(self._after) else None
 
-    def forward(self, xn, ctx):
-        # gate and up stay float32 until the activation has been applied; the down
-        # projection's float32 result goes into the residual stream unrounded
+    def _activation(self, xn):
+        """silu(gate) * up as a matrix of the model dtype."""
         n = xn.shape[0]
         act = torch.empty((n, self.inter), dtype=self.dtype, device=xn.device)
         w_gate, w_up = self.w_gate_up[:self.inter], self.w_gate_up[self.inter:]
@@ -74,6 +73,12 @@ class GatedMLP:
         else:
             gu = kernels.linear(xn, self.w_gate_up, out_dtype=torch.float32)
             kernels.silu_mul(act, gu[:, :self.inter], gu[:, self.inter:])
+        return act
+
+    def forward(self, xn, ctx):
+        # gate and up stay float32 until the activation has been applied; the down
+        # projection's float32 result goes into the residual stream unrounded
+        act = self._activation(xn)
         return kernels.linear(act, self.w_down, out_dtype=torch.float32)
 
 
@@ -81,7 +86,9 @@ class GatedMLP:
         n = x.shape[0]
         if not (getattr(norm, "fusable_rmsnorm", False) and kernels.skinny_fits(n, self.hidden, self.dtype)
                 and kernels.skinny_fits(n, self.inter, self.dtype)):
-            return False
+            # larger steps: the down product adds into the residual stream
+            kernels.linear_add(x, self._activation(norm.forward(x, None)), self.w_down)
+            return True
         act = kernels.skinny_gemm(self.w_gate_up[:self.inter], weight_up=self.w_gate_up[self.inter:], x_f32=x,
                                   gain=norm.gain, eps=norm.eps, epilogue="swiglu", prefetch=self._target(0))
         kernels.skinny_gemm(self.w_down, x=act, epilogue="add", out=x, prefetch=self._target(1))
