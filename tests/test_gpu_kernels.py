@@ -50,6 +50,12 @@ def test_embed_and_gather(dtype):
     bad = torch.empty((1, 24), dtype=torch.float32, device="cuda")
     kernels.embed(bad, dev(table, DT[dtype]), dev(np.array([37], dtype=np.int32)))
     assert torch.isnan(bad).all()          # an id outside the table is never looked up
+    # a negative id -(s + 1) is the token that the sampler left for request slot s
+    last = dev(np.array([11, 3, 29], dtype=np.int32))
+    kernels.embed(x, dev(table, DT[dtype]), dev(np.array([-1, 7, -3, -2, 0], dtype=np.int32)), last)
+    assert np.array_equal(x.cpu().numpy().astype(np.float64), as_stored(table, dtype)[[11, 7, 29, 3, 0]])
+    kernels.embed(bad, dev(table, DT[dtype]), dev(np.array([-1], dtype=np.int32)))
+    assert torch.isnan(bad).all()          # without the table of last tokens a negative id is just a bad id
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -408,6 +414,15 @@ def test_sampling_greedy_first_maximum_and_temperature():
             i = got[r]
             lo = cdf[i - 1] if i else 0.0
             assert lo - 1e-5 <= u <= cdf[i] + 1e-5, (r, u, i, lo, cdf[i])
+    # the choice also goes to the request slot's entry of the table that the next embedding reads
+    last = torch.full((10,), -7, dtype=torch.int32, device="cuda")
+    slots = dev(np.array([4, 0, 9, 2, 7, 5], dtype=np.int32))
+    kernels.sample(out, dev(z), dev(temps), dev(np.full(6, 0.3, np.float32)), last, slots)
+    assert last[slots.long()].tolist() == out.tolist() and last[[1, 3, 6, 8]].tolist() == [-7] * 4
+    kernels.sample(out, dev(z), None, None, last, slots)
+    assert last[slots.long()].tolist() == [plain.argmax_first(r) for r in z]
+    with pytest.raises(kernels.KernelError, match="go together"):
+        kernels.sample(out, dev(z), None, None, last, None)
     # many draws follow the distribution
     zz = np.array([[2.0, 1.0, 0.0, -1.0, 3.0]], dtype=np.float32).repeat(4000, 0)
     us = ((np.arange(4000) + 0.5) / 4000).astype(np.float32)
