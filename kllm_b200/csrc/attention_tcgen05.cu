@@ -5,24 +5,28 @@
 // operands, float32 accumulation.
 //
 // A CTA takes 128 rows = (tokens of one request's portion) x (heads of one kv group) and
-// walks that portion's keys in tiles of 64.  Its six warps have three roles that meet
-// only at mbarriers, so loading, the tensor core and the softmax of neighbouring tiles
-// run at the same time:
+// walks that portion's keys in tiles of 64.  Its warps have four roles that meet only at
+// mbarriers, so loading, the tensor core and the softmax of neighbouring tiles run at the
+// same time (issuing one tcgen05.mma keeps a thread busy for a hundred cycles and more,
+// so each of the two products has an issuing warp of its own):
 //
-//   warp 5   loader: K and V tiles by cp.async into a ring of stages, written directly in
+//   warp 6   loader: K and V tiles by cp.async into a ring of stages, written directly in
 //            the 128-byte-swizzled layout that the MMA's shared-memory descriptors name
 //            (rows of 64 elements, 8-row groups of 1024 bytes, the 16-byte piece index
 //            XORed with the row index modulo 8; head sizes above 64 as panels of 64
 //            dims); the copies' completion arrives on the stage's mbarrier;
-//   warp 4   one lane issues the tcgen05.mma: Q.K^T of tile j+1 (M=128, N=64, K=16 per
-//            instruction) into one of two score buffers in TMEM as soon as that buffer
-//            has been read out and the tile has landed, that is while the softmax warps
-//            still work on tile j; then P.V of tile j (V as the MN-major operand) into
-//            the output tile in TMEM once the probabilities are in shared memory;
+//   warp 4   one lane issues Q.K^T of a tile (M=128, N=64, K=16 per instruction) into one
+//            of two score buffers in TMEM as soon as that buffer has been read out and
+//            the tile has landed, that is up to two tiles ahead of the softmax;
+//   warp 5   one lane issues P.V of a tile (V as the MN-major operand), accumulating into
+//            the output in TMEM, once the tile's probabilities are in shared memory, and
+//            hands the stage back to the loader;
 //   warps 0-3  softmax: every thread owns one row, reads its 64 scores from TMEM
 //            (tcgen05.ld 32x32b), applies the mask and the online-softmax recurrence
 //            without any cross-thread traffic, and writes its probabilities as bfloat16
-//            into one of two swizzled shared-memory tiles.
+//            into a swizzled shared-memory tile.
+// The softmax warps are one warp group, the others (with an idle warp) a second one that
+// hands most of its registers to the first (setmaxnreg), so that two CTAs fit an SM.
 //
 // The output accumulates in TMEM over all tiles (P.V with accumulation); a row's
 // probabilities are taken relative to a reference maximum that is only moved when the
@@ -52,13 +56,13 @@ static_assert(HD == 64 || HD == 128, "head size 64 or 128");
 constexpr int PANELS = HD / 64;            // 64-dim panels of a row
 constexpr int ROWS = 128;                  // query rows per CTA = TMEM lanes
 constexpr int TILE = 64;                   // keys per tile
-constexpr int THREADS = 192;                          // 4 softmax warps, the MMA warp, the loader warp
+constexpr int THREADS = 256;                          // 4 softmax warps; the two MMA-issuing warps, the loader warp, an idle one
 constexpr int SOFTMAX_THREADS = 128;
 constexpr int Q_BYTES = PANELS * ROWS * 128;          // [panel][128 rows][64 dims]
 constexpr int KV_BYTES = PANELS * TILE * 128;         // [panel][64 keys][64 dims]
-constexpr int P_BYTES = ROWS * 128;                   // [128 rows][64 keys], two of them
-constexpr int STAGES = HD == 64 ? 3 : 2;
-constexpr int SMEM_BYTES = 1024 + Q_BYTES + 2 * P_BYTES + STAGES * 2 * KV_BYTES;
+constexpr int P_BYTES = ROWS * 128;                   // [128 rows][64 keys]
+constexpr int STAGES = HD == 64 ? 4 : 2;
+constexpr int SMEM_BYTES = 1024 + Q_BYTES + P_BYTES + STAGES * 2 * KV_BYTES;
 constexpr float kRescaleAt = 8.f;                     // move a row's reference when its maximum grew by 2^8
 constexpr int TMEM_COLS = 256;                        // two score buffers (2 x 64) + output tile (HD): a power of two
 constexpr long long kCycleLimit = 4000000000LL;       // about two seconds
@@ -232,7 +236,7 @@ attn_prefill_tc5_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int6
                         int n_kv, int page_size, int window, float scale_log2e, int tokens_per_tile, int* status) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bar_kv_full[STAGES], bar_kv_empty[STAGES], bar_q_full, bar_s_full[2], bar_s_free[2],
-        bar_p_full[2], bar_o_full[2];
+        bar_p_full, bar_o_full;
     __shared__ unsigned s_tmem;
     __shared__ int s_req, s_tok0, s_abort;
     const int g = blockIdx.y;
@@ -250,8 +254,8 @@ attn_prefill_tc5_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int6
         for (int s = 0; s < STAGES; s++) { mbar_init(&bar_kv_full[s], 32); mbar_init(&bar_kv_empty[s], 1); }
         mbar_init(&bar_q_full, 32);
         for (int b = 0; b < 2; b++) { mbar_init(&bar_s_full[b], 1); mbar_init(&bar_s_free[b], SOFTMAX_THREADS); }
-        for (int b = 0; b < 2; b++) mbar_init(&bar_p_full[b], SOFTMAX_THREADS);
-        for (int b = 0; b < 2; b++) mbar_init(&bar_o_full[b], 1);
+        mbar_init(&bar_p_full, SOFTMAX_THREADS);
+        mbar_init(&bar_o_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncthreads();
@@ -276,10 +280,16 @@ attn_prefill_tc5_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int6
     const int ntiles = (hi - lo + TILE - 1) / TILE;      // at least 1: a row sees its own key
     volatile int* abort_flag = &s_abort;
 
-    const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;       // swizzled tiles want 1024-byte alignment
-    const unsigned sQ = base, sP = base + Q_BYTES, sKV = sP + 2 * P_BYTES;
+    // The softmax warps keep 64 scores and more in registers; the other warp group needs
+    // almost none and hands its share over (the kernel is compiled for two CTAs of 256
+    // threads per SM, 128 registers each).
 
-    if (warp == 5) {
+    const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;       // swizzled tiles want 1024-byte alignment
+    const unsigned sQ = base, sP = base + Q_BYTES, sKV = sP + P_BYTES;
+
+    if (warp >= 4) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 64;\n" ::);
+      if (warp == 6) {
         // ---- loader ----------------------------------------------------------------
         for (int c = lane; c < ROWS * (HD / 8); c += 32) {     // Q tile: each row's HD dims, zero for unused rows
             const int r = c / (HD / 8), piece = c - r * (HD / 8);
@@ -296,18 +306,15 @@ attn_prefill_tc5_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int6
             cp_async_arrive(&bar_kv_full[s]);
         }
         cp_async_wait<0>();                    // nothing of this warp is in flight when the CTA ends
-    } else if (warp == 4) {
-        // ---- tensor-core issuer ----------------------------------------------------
-        // (every barrier is waited on by parity, so none may complete twice before its
-        // waiter has looked: the probabilities' barrier, like their buffer, exists twice,
-        // and a buffer's next round needs the product that this warp issues)
+      } else if (warp == 4) {
+        // ---- issuer of the scores ---------------------------------------------------
         constexpr uint32_t IDESC_S = make_idesc(ROWS, TILE, false);
-        constexpr uint32_t IDESC_O = make_idesc(ROWS, HD, true);
         bool ok = mbar_wait(&bar_q_full, 0, abort_flag, status, 2);
-        auto issue_scores = [&](int j) -> bool {            // scores of tile j into buffer j & 1
+        for (int j = 0; ok && j < ntiles; j++) {            // scores of tile j into buffer j & 1, up to two tiles ahead
             const int s = j % STAGES, b = j & 1;
-            if (!mbar_wait(&bar_kv_full[s], ((unsigned)(j / STAGES)) & 1u, abort_flag, status, 3)) return false;
-            if (!mbar_wait(&bar_s_free[b], (((unsigned)(j >> 1)) & 1u) ^ 1u, abort_flag, status, 4)) return false;
+            ok = mbar_wait(&bar_kv_full[s], ((unsigned)(j / STAGES)) & 1u, abort_flag, status, 3) &&
+                 mbar_wait(&bar_s_free[b], (((unsigned)(j >> 1)) & 1u) ^ 1u, abort_flag, status, 4);
+            if (!ok) break;
             fence_async_smem();                // the copies landed through the generic proxy
             tc_fence_after();
             if (lane == 0) {
@@ -321,28 +328,35 @@ attn_prefill_tc5_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int6
                 umma_commit(&bar_s_full[b]);
             }
             __syncwarp();
-            return true;
-        };
-        if (ok) ok = issue_scores(0);
+        }
+      } else if (warp == 5) {
+        // ---- issuer of the output products --------------------------------------------
+        constexpr uint32_t IDESC_O = make_idesc(ROWS, HD, true);
+        bool ok = true;
         for (int j = 0; ok && j < ntiles; j++) {
-            if (j + 1 < ntiles) { ok = issue_scores(j + 1); if (!ok) break; }     // runs while tile j is in the softmax
-            ok = mbar_wait(&bar_p_full[j & 1], ((unsigned)(j >> 1)) & 1u, abort_flag, status, 5);
+            const int s = j % STAGES;
+            // the stage's arrival was seen by the other issuer; this warp has to see it too
+            ok = mbar_wait(&bar_kv_full[s], ((unsigned)(j / STAGES)) & 1u, abort_flag, status, 5) &&
+                 mbar_wait(&bar_p_full, (unsigned)j & 1u, abort_flag, status, 5);
             if (!ok) break;
+            fence_async_smem();
             tc_fence_after();
             if (lane == 0) {                   // output += P . V
-                const unsigned st = sKV + (unsigned)(j % STAGES) * 2u * KV_BYTES;
+                const unsigned st = sKV + (unsigned)s * 2u * KV_BYTES;
 #pragma unroll
                 for (int kk = 0; kk < TILE / 16; kk++) {
-                    const unsigned a = sP + (unsigned)((j & 1) * P_BYTES + kk * 32);
+                    const unsigned a = sP + (unsigned)(kk * 32);
                     const unsigned bb = st + KV_BYTES + (unsigned)(kk * 2048);
                     umma(tmem + 128, make_desc(a, 16, 1024), make_desc(bb, TILE * 128, 1024), IDESC_O, j > 0 || kk > 0);
                 }
-                umma_commit(&bar_o_full[j & 1]);
-                umma_commit(&bar_kv_empty[j % STAGES]);
+                umma_commit(&bar_o_full);
+                umma_commit(&bar_kv_empty[s]);
             }
             __syncwarp();
         }
+      }                                        // warp 7 only fills the warp group
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 184;\n" ::);
         // ---- softmax: this thread's row is (token, head of the group) ---------------
         const int row = threadIdx.x;
         const int tt = row / gs, hh = row - tt * gs;
@@ -388,12 +402,24 @@ attn_prefill_tc5_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int6
                 corr = (m_ref == -INFINITY) ? 0.f : exp2f((m_ref - mx) * scale_log2e);
                 m_ref = mx;
             }
+            const float neg = (m_ref == -INFINITY) ? 0.f : -m_ref * scale_log2e;   // p = 2^(s * scale - m * scale): one FMA each
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int jj = 0; jj < TILE; jj++) {
+                s[jj] = fast_exp2(fmaf(s[jj], scale_log2e, neg));
+                sum4[jj & 3] += s[jj];
+            }
+            l_run = l_run * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            if (j > 0) {
+                // the product of tile j - 1 read the P tile that is written below, and must be
+                // over before the accumulator is rescaled; it has had this long to finish
+                ok = mbar_wait(&bar_o_full, (unsigned)(j - 1) & 1u, abort_flag, status, 7);
+                if (!ok) break;
+            }
             if (j > 0 && __any_sync(0xffffffffu, move)) {
                 // rows of this warp rescale what the products so far have added up (rows that
-                // did not move multiply by one); the product of tile j - 1 must be over, the
-                // one of tile j waits for this thread's probabilities
-                ok = mbar_wait(&bar_o_full[(j - 1) & 1], ((unsigned)((j - 1) >> 1)) & 1u, abort_flag, status, 7);
-                if (!ok) break;
+                // did not move multiply by one); the product of tile j - 1 is over (see above),
+                // the one of tile j waits for this thread's probabilities
                 tc_fence_after();
 #pragma unroll
                 for (int cb = 0; cb < HD / 32; cb++) {
@@ -406,19 +432,7 @@ attn_prefill_tc5_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int6
                 }
                 tmem_st_wait();
             }
-            const float neg = (m_ref == -INFINITY) ? 0.f : -m_ref * scale_log2e;   // p = 2^(s * scale - m * scale): one FMA each
-            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int jj = 0; jj < TILE; jj++) {
-                s[jj] = fast_exp2(fmaf(s[jj], scale_log2e, neg));
-                sum4[jj & 3] += s[jj];
-            }
-            l_run = l_run * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-            if (j >= 2) {                      // this P buffer was read by the product of tile j - 2
-                ok = mbar_wait(&bar_o_full[b], ((unsigned)((j - 2) >> 1)) & 1u, abort_flag, status, 8);
-                if (!ok) break;
-            }
-            const unsigned sPb = sP + (unsigned)(b * P_BYTES);
+            const unsigned sPb = sP;
 #pragma unroll
             for (int c = 0; c < 8; c++) {      // 8 keys = 16 bytes per piece, swizzled like an operand row
                 uint4 pk;
@@ -430,9 +444,9 @@ attn_prefill_tc5_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int6
             }
             fence_async_smem();
             tc_fence_before();
-            mbar_arrive(&bar_p_full[b]);       // P of tile j is in shared memory, the accumulator is rescaled
+            mbar_arrive(&bar_p_full);          // P of tile j is in shared memory, the accumulator is rescaled
         }
-        if (ok) ok = mbar_wait(&bar_o_full[(ntiles - 1) & 1], ((unsigned)((ntiles - 1) >> 1)) & 1u, abort_flag, status, 9);
+        if (ok) ok = mbar_wait(&bar_o_full, (unsigned)(ntiles - 1) & 1u, abort_flag, status, 9);
         if (ok) {
             tc_fence_after();
             const float inv = 1.f / l_run;
