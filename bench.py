@@ -72,7 +72,7 @@ class ClockSampler:
         exe = shutil.which("nvidia-smi")
         if exe:
             self.proc = subprocess.Popen([exe, f"--id={device}", f"--query-gpu={self.QUERY}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -286,11 +286,12 @@ def main():
             sched.step()
         torch.cuda.synchronize()
         e2e_ms = (time.perf_counter() - w0) * 1e3 / steps
+        t2 = time.time()
         csum = None
         if clocks:
             time.sleep(0.15)
             clocks.stop()
-            csum = clocks.summary(t0, t1)
+            csum = clocks.summary(t0, t2)          # both timed regions: device-timed and end-to-end
         assert len(sched.running) == batch, "a request ended inside the timed region"
         h2d = eng.runner.last_h2d_bytes
         sched.stop()

@@ -28,7 +28,7 @@ __device__ __forceinline__ void take_better(float& v, int& i, float v2, int i2) 
 __global__ void __launch_bounds__(kThreads)
 sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int64_t row_stride,
               int vocab, const float* __restrict__ temperature, const float* __restrict__ uniform,
-              int* __restrict__ last_token, const int* __restrict__ slots) {
+              int* __restrict__ last_token, const int* __restrict__ slots, int* __restrict__ host_out) {
     __shared__ float s_val[kWarps];
     __shared__ int s_idx[kWarps];
     __shared__ float s_sum[kWarps];
@@ -79,6 +79,7 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int64_t r
         if (tid == 0) {
             out[r] = s_choice;
             if (last_token) last_token[slots[r]] = s_choice;
+            if (host_out) { host_out[r] = s_choice; __threadfence_system(); }
         }
         return;
     }
@@ -147,6 +148,7 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int64_t r
         if (choice < 0) choice = (hi > lo) ? hi - 1 : s_choice;
         out[r] = choice;
         if (last_token) last_token[slots[r]] = choice;
+        if (host_out) { host_out[r] = choice; __threadfence_system(); }
     }
 }
 
@@ -156,14 +158,27 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int64_t r
 // temperature, uniform [rows] float32 (temperature may be NULL: all greedy).
 // last_token, slots: optional; row r's choice is also stored at last_token[slots[r]], where
 // the embedding kernel of the next step finds it (see embedding.cu).
+// host_out: optional, pinned host memory that the device can address [rows]: the choices are
+// also written there by the kernel itself, which saves the copy that would follow it; the host
+// may read them once an event recorded after this launch has completed.
 extern "C" int kllm_sample(int* out, const float* logits, int64_t row_stride, int rows, int vocab,
                            const float* temperature, const float* uniform, int* last_token, const int* slots,
-                           void* stream) {
+                           int* host_out, void* stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) KLLM_FAIL("sample: vocabulary %d", vocab);
     if (temperature && !uniform) KLLM_FAIL("sample: temperature given without uniform numbers");
     if (last_token && !slots) KLLM_FAIL("sample: a token table without the rows' slots");
+    if (host_out) {                      // the address under which the device sees that host memory
+        void* mapped = nullptr;
+        const cudaError_t e = cudaHostGetDevicePointer(&mapped, host_out, 0);
+        if (e != cudaSuccess || !mapped) {
+            (void)cudaGetLastError();
+            KLLM_FAIL("sample: the host buffer for the choices is not pinned memory that the device can address (%s)",
+                      cudaGetErrorString(e));
+        }
+        host_out = (int*)mapped;
+    }
     kllm_launch((sample_kernel), dim3(rows), dim3(kThreads), 0, (cudaStream_t)stream, out, logits, row_stride, vocab,
-                                                             temperature, uniform, last_token, slots);
+                                                             temperature, uniform, last_token, slots, host_out);
     KLLM_LAUNCH_STATUS();
 }

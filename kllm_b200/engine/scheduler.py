@@ -295,10 +295,10 @@ class Scheduler:
         else:
             slots = torch.tensor([r.cache.state_slot for r in wanting], dtype=torch.int32).to(
                 logits.device, non_blocking=True)
-        out = eng.sampler.sample(logits, [r.temperature for r in wanting], keys,
-                                 last_token=eng.runner.last_token, slots=slots)
-        pinned = torch.empty(out.shape[0], dtype=torch.int32, pin_memory=True)
-        pinned.copy_(out, non_blocking=True)
+        # the sampling kernel writes its choices into pinned host memory itself: no copy after it
+        pinned = torch.empty(len(wanting), dtype=torch.int32, pin_memory=True)
+        eng.sampler.sample(logits, [r.temperature for r in wanting], keys,
+                           last_token=eng.runner.last_token, slots=slots, host_out=pinned)
         event = torch.cuda.Event()
         event.record()
         return _EngineResult(pinned, event)

@@ -394,10 +394,14 @@ def silu_mul(out: torch.Tensor, gate: torch.Tensor, up: torch.Tensor) -> None:
 
 def sample(out: torch.Tensor, logits: torch.Tensor, temperature: Optional[torch.Tensor],
            uniform: Optional[torch.Tensor], last_token: Optional[torch.Tensor] = None,
-           slots: Optional[torch.Tensor] = None) -> None:
+           slots: Optional[torch.Tensor] = None, host_out: Optional[torch.Tensor] = None) -> None:
     """out[r] = argmax (temperature[r] <= 0) or the inverse CDF of softmax(z/T) at uniform[r];
-    with ``last_token`` and ``slots`` (int32 [rows]) also last_token[slots[r]] = out[r]."""
+    with ``last_token`` and ``slots`` (int32 [rows]) also last_token[slots[r]] = out[r];
+    with ``host_out`` (pinned host int32 [rows]) the kernel also writes the choices there itself."""
     _cuda(out, logits, temperature, uniform, last_token, slots)
+    if host_out is not None and (host_out.is_cuda or not host_out.is_pinned() or host_out.dtype != torch.int32
+                                 or not host_out.is_contiguous() or host_out.numel() < logits.shape[0]):
+        raise KernelError("sample: host_out must be a pinned, contiguous int32 host tensor of [rows]")
     _i32(out, "out"); _i32(last_token, "last_token"); _i32(slots, "slots")
     if (last_token is None) != (slots is None) or (slots is not None and slots.numel() != logits.shape[0]):
         raise KernelError("sample: last_token and slots [rows] go together")
@@ -408,7 +412,7 @@ def sample(out: torch.Tensor, logits: torch.Tensor, temperature: Optional[torch.
             raise KernelError("sample: temperature and uniform must be float32 [rows]")
     lib = load_library("sampling")
     rc = lib.kllm_sample(_p(out), _p(logits), ctypes.c_int64(logits.stride(0)), logits.shape[0],
-                         logits.shape[1], _p(temperature), _p(uniform), _p(last_token), _p(slots), _stream())
+                         logits.shape[1], _p(temperature), _p(uniform), _p(last_token), _p(slots), _p(host_out), _stream())
     _check(lib, "sampling", rc)
 
 

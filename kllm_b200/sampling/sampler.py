@@ -43,22 +43,23 @@ class Sampler:
         self.device = torch.device(device)
 
     def sample(self, logits: torch.Tensor, temperatures: Sequence[float],
-               keys: Sequence[Tuple[int, int, int]], last_token=None, slots=None) -> torch.Tensor:
+               keys: Sequence[Tuple[int, int, int]], last_token=None, slots=None, host_out=None) -> torch.Tensor:
         """int32 [rows] on the device.  Row r is greedy when temperatures[r] <= 0,
         else drawn with the uniform number of keys[r] = (seed, request id, index).
         ``last_token`` / ``slots``: see ``kernels.sample`` (the choice also goes to the
-        request slot's entry, for a next step that is launched before this one is read)."""
+        request slot's entry, for a next step that is launched before this one is read;
+        ``host_out``: pinned host memory that the kernel also writes the choices to)."""
         rows = logits.shape[0]
         out = torch.empty(rows, dtype=torch.int32, device=logits.device)
         if all(t <= 0 for t in temperatures):
-            kernels.sample(out, logits, None, None, last_token, slots)
+            kernels.sample(out, logits, None, None, last_token, slots, host_out)
             return out
         host = torch.empty((2, rows), dtype=torch.float32, pin_memory=logits.is_cuda)
         for r in range(rows):
             host[0, r] = float(temperatures[r])
             host[1, r] = uniform_for(*keys[r]) if temperatures[r] > 0 else 0.0
         dev = host.to(logits.device, non_blocking=True)
-        kernels.sample(out, logits, dev[0], dev[1], last_token, slots)
+        kernels.sample(out, logits, dev[0], dev[1], last_token, slots, host_out)
         return out
 
     def greedy(self, logits: torch.Tensor) -> torch.Tensor:

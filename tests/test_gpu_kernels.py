@@ -423,6 +423,13 @@ def test_sampling_greedy_first_maximum_and_temperature():
     assert last[slots.long()].tolist() == [plain.argmax_first(r) for r in z]
     with pytest.raises(kernels.KernelError, match="go together"):
         kernels.sample(out, dev(z), None, None, last, None)
+    # the kernel can also leave its choices in pinned host memory by itself
+    pinned = torch.full((6,), -1, dtype=torch.int32).pin_memory()
+    kernels.sample(out, dev(z), None, None, host_out=pinned)
+    torch.cuda.synchronize()
+    assert pinned.tolist() == out.tolist() == [plain.argmax_first(r) for r in z]
+    with pytest.raises(kernels.KernelError, match="pinned"):
+        kernels.sample(out, dev(z), None, None, host_out=torch.zeros(6, dtype=torch.int32))
     # many draws follow the distribution
     zz = np.array([[2.0, 1.0, 0.0, -1.0, 3.0]], dtype=np.float32).repeat(4000, 0)
     us = ((np.arange(4000) + 0.5) / 4000).astype(np.float32)
