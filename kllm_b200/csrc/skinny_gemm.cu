@@ -84,6 +84,14 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem, boo
 __device__ __forceinline__ void cp_async_wait_all() {
     asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
 }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+// wait until at most `pending` of this thread's latest copy groups are still in flight
+__device__ __forceinline__ void cp_async_wait_pending(int pending) {
+    if (pending >= 3) asm volatile("cp.async.wait_group 3;\n" ::: "memory");
+    else if (pending == 2) asm volatile("cp.async.wait_group 2;\n" ::: "memory");
+    else if (pending == 1) asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+    else asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+}
 
 __host__ __device__ inline int x_row_elems(int K) {      // row stride of X in shared memory, elements
     return K + (((K * 2) % 128 == 0) ? 32 : 0);           // bytes = 64 (mod 128): 16-byte reads of 8 rows x 4
@@ -145,14 +153,22 @@ skinny_gemm_kernel(const Args a) {
     TL_MARK(1);
 
     // ---- prologue: X into shared memory as bfloat16, rows past n are zero ----
+    int x_groups = 0;            // X_BF16: copy groups of X, one per batch of k-steps (the last takes the rest)
     if (PRO == X_BF16) {
-        // all copies in flight at once, one wait
-        const int chunks = K / 8;
-        for (int c = threadIdx.x; c < 8 * NT * chunks; c += THREADS) {
-            const int r = c / chunks, ch = c - r * chunks;
-            cp_async16(xs + r * XS + ch * 8, a.x_bf16 + (int64_t)(r < n ? r : 0) * a.x_stride + ch * 8, r < n);
+        // All copies in flight at once, in groups by the k range that a batch of the main
+        // loop needs: the first tile's batch b waits for groups 0..b only, so a long X is
+        // still arriving while its first part is already being multiplied.
+        constexpr int KB = UNROLL * WARPS * 32;
+        x_groups = min(nb, 4);
+        for (int gi = 0; gi < x_groups; gi++) {
+            const int k_lo = gi * KB, k_hi = (gi == x_groups - 1) ? K : min(K, (gi + 1) * KB);
+            const int pieces = (k_hi - k_lo) / 8;
+            for (int c = threadIdx.x; c < 8 * NT * pieces; c += THREADS) {
+                const int r = c / pieces, ch = c - r * pieces;
+                cp_async16(xs + r * XS + k_lo + ch * 8, a.x_bf16 + (int64_t)(r < n ? r : 0) * a.x_stride + k_lo + ch * 8, r < n);
+            }
+            cp_async_commit();
         }
-        cp_async_wait_all();
     } else {
         // WARPS / (8*NT) warps share a row: each takes a contiguous part of it, the
         // parts' sums of squares are added in part order
@@ -214,7 +230,7 @@ skinny_gemm_kernel(const Args a) {
             for (int k = lo_k + lane * 8; k < lo_k + span; k += 256) *reinterpret_cast<uint4*>(dst + k) = make_uint4(0, 0, 0, 0);
         }
     }
-    __syncthreads();
+    if (PRO != X_BF16) __syncthreads();
     TL_MARK(2);
 
     // ---- tiles ----
@@ -229,6 +245,12 @@ skinny_gemm_kernel(const Args a) {
         int nxt_tile = cur_tile, nxt_b = cur_b + 1;
         if (nxt_b == nb) { nxt_b = 0; nxt_tile += gridDim.x; }
         if (nxt_tile < n_tiles) load_batch(ya, yb, nxt_tile, nxt_b);
+        if (PRO == X_BF16 && x_groups > 0) {                 // the first tile: the part of X that this batch reads
+            const int have = min(cur_b, x_groups - 1) + 1;
+            cp_async_wait_pending(x_groups - have);
+            __syncthreads();
+            if (have == x_groups) x_groups = 0;
+        }
 #pragma unroll
         for (int u = 0; u < UNROLL; u++) {
             const int s = cur_b * UNROLL + u;
@@ -284,6 +306,7 @@ skinny_gemm_kernel(const Args a) {
         if (cur_tile >= n_tiles) break;
         phase(buf1a, buf1b, buf0a, buf0b);
     }
+    if (PRO == X_BF16) cp_async_wait_pending(0);            // a CTA without a tile: nothing in flight at its end
     TL_MARK(3);
     TL_END(a.tl_slot, 100 + PRO * 10 + EPI);        // marks: start, dependency wait over, X ready, tiles done
 }
