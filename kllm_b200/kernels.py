@@ -204,19 +204,35 @@ def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: 
     kernel that fits: bfloat16 with a head size in TC_HEAD_DIMS runs on tensor cores
     (the decode form when every request brings one token, else the prefill form: on
     tcgen05 for head sizes 64 and 128, on mma.sync for the other multiples of 16);
-    float32, other head sizes or very wide groups run the generic kernel."""
+    float32, other head sizes or very wide groups run the generic kernel.  A mixed
+    step whose first requests bring one token each (the scheduler puts decoding requests
+    first) is cut in two: those tokens take the decode form, which spreads a long context
+    over many CTAs, the portions after them the prefill form, in which a single token
+    would walk its whole context with one CTA of 128 rows, 127 of them idle."""
     group = n_heads // max(1, n_kv)
     tc = q.dtype == torch.bfloat16 and head_dim in TC_HEAD_DIMS
     if tc and ctx.all_single and group <= 16:
         return attention_decode(out, q, kcache, vcache, ctx.positions, ctx.token_req, block_table, n_heads,
                                 n_kv, head_dim, window, scale,
                                 decode_splits(ctx.n_tokens, n_kv, ctx.split_bound or ctx.max_ctx))
+    singles = 0
+    if tc and group <= 16 and ctx.host_n_new:
+        while singles < ctx.n_requests and ctx.host_n_new[singles] == 1:
+            singles += 1
+    if 0 < singles < ctx.n_requests:
+        # token t of the first `singles` is request t: no token-to-request table needed
+        attention_decode(out[:singles], q[:singles], kcache, vcache, ctx.positions[:singles], None,
+                         block_table[:singles], n_heads, n_kv, head_dim, window, scale,
+                         decode_splits(singles, n_kv, ctx.max_ctx))
+    q_start, start_pos, table, n_req = ctx.q_start, ctx.start_pos, block_table, ctx.n_requests
+    if 0 < singles < ctx.n_requests:
+        q_start, start_pos, table, n_req = q_start[singles:], start_pos[singles:], block_table[singles:], n_req - singles
     if tc and USE_TCGEN05 and head_dim in TCGEN05_HEAD_DIMS and group <= 128:
-        return attention_prefill_tcgen05(out, q, kcache, vcache, ctx.q_start, ctx.start_pos, block_table,
-                                         ctx.n_requests, n_heads, n_kv, head_dim, window, scale)
+        return attention_prefill_tcgen05(out, q, kcache, vcache, q_start, start_pos, table,
+                                         n_req, n_heads, n_kv, head_dim, window, scale)
     if tc and group <= 64:
-        return attention_prefill(out, q, kcache, vcache, ctx.q_start, ctx.start_pos, block_table,
-                                 ctx.n_requests, n_heads, n_kv, head_dim, window, scale)
+        return attention_prefill(out, q, kcache, vcache, q_start, start_pos, table,
+                                 n_req, n_heads, n_kv, head_dim, window, scale)
     return attention_generic(out, q, kcache, vcache, ctx.positions, ctx.token_req, block_table, n_heads, n_kv,
                              head_dim, window, scale)
 

@@ -163,6 +163,16 @@ def attention_case(dtype, H, G, hd, page_size, lengths, n_new, window, seed, pla
     elif kernel == "decode":
         kernels.attention_decode(out, q, kc, vc, dev(np.array(pos, np.int32)), dev(np.array(req, np.int32)), table,
                                  H, G, hd, window or 0, scale, splits)
+    elif kernel == "dispatch":
+        # the way the attention part calls it: the kernel is chosen from the step's shape
+        from types import SimpleNamespace
+        ctx = SimpleNamespace(
+            n_tokens=len(pos), n_requests=len(lengths), positions=dev(np.array(pos, np.int32)),
+            token_req=dev(np.array(req, np.int32)), q_start=dev(np.concatenate([[0], np.cumsum(n_new)]).astype(np.int32)),
+            start_pos=dev(np.array([L - nn for L, nn in zip(lengths, n_new)], dtype=np.int32)),
+            host_n_new=list(n_new), all_single=all(c == 1 for c in n_new), max_ctx=max(lengths), split_bound=0)
+        kernels.attention(out, q, kc, vc, ctx, table, H, G, hd, window or 0, scale)
+        kernels.check_status("cuda")
     else:
         q_start = np.concatenate([[0], np.cumsum(n_new)]).astype(np.int32)
         start_pos = np.array([L - nn for L, nn in zip(lengths, n_new)], dtype=np.int32)
@@ -203,6 +213,32 @@ def test_tcgen05_attention_shapes_pages_and_mixed_query_lengths(H, G, hd, page):
     got, want = attention_case("bfloat16", H, G, hd, page, lengths, n_new, None, seed=H * hd, kernel="tcgen05")
     assert not torch.isnan(got.float()).any(), "a slot beyond a request's length was read"
     close(got, want, "bfloat16")
+
+
+@pytest.mark.parametrize("H,G,hd,page", [(8, 2, 64, 16), (32, 4, 128, 64), (6, 2, 80, 8), (3, 1, 32, 5)])
+@pytest.mark.parametrize("window", [None, 40])
+def test_attention_of_a_mixed_step_is_cut_into_decode_and_prefill_forms(H, G, hd, page, window, monkeypatch):
+    """Decoding requests first, then portions, as the scheduler orders a step: the first
+    take the decode kernel, the others the prefill kernel (tcgen05 for head sizes 64 and
+    128, mma.sync else); a single-token request after a portion stays with the portions."""
+    from kllm_b200 import kernels
+    calls = []
+    for name in ("attention_decode", "attention_prefill", "attention_prefill_tcgen05"):
+        real = getattr(kernels, name)
+        monkeypatch.setattr(kernels, name, lambda *a, _n=name, _r=real, **k: calls.append((_n, a[1].shape[0])) or _r(*a, **k))
+    lengths, n_new = [300, 1, 129, 77, 200, 31], [1, 1, 1, 77, 64, 1]
+    got, want = attention_case("bfloat16", H, G, hd, page, lengths, n_new, window, seed=H + hd, kernel="dispatch")
+    assert not torch.isnan(got.float()).any()
+    close(got, want, "bfloat16")
+    assert calls[0] == ("attention_decode", 3)
+    assert calls[1][0] == ("attention_prefill_tcgen05" if hd in (64, 128) else "attention_prefill")
+    # all single: the decode form alone; none single first: the prefill form alone
+    calls.clear()
+    got, want = attention_case("bfloat16", H, G, hd, page, [40, 300, 7], [1, 1, 1], window, seed=3, kernel="dispatch")
+    close(got, want, "bfloat16")
+    got, want = attention_case("bfloat16", H, G, hd, page, [40, 300, 7], [9, 1, 1], window, seed=4, kernel="dispatch")
+    close(got, want, "bfloat16")
+    assert [c[0] for c in calls][0] == "attention_decode" and len(calls) == 2
 
 
 @pytest.mark.parametrize("kernel,splits", [("decode", 1), ("decode", 5), ("prefill", 1), ("tcgen05", 1)])
