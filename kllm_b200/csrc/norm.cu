@@ -104,6 +104,63 @@ add_rmsnorm_vec4_kernel(float* __restrict__ x, const float* __restrict__ res, bf
     }
 }
 
+// Many rows (a prompt portion): one warp per row, the row in registers, no block-wide
+// synchronisation; 8 rows per CTA.  Width a multiple of 4 up to 32 * 4 * kWarpVec.  Lane l
+// adds the squares of its float4 l, l + 32, ... in that order, then the lanes are added
+// in a fixed tree.
+constexpr int kWarpVec = 16;
+
+__global__ void __launch_bounds__(256)
+add_rmsnorm_warp_kernel(float* __restrict__ x, const float* __restrict__ res, bf16* __restrict__ out,
+                        const float* __restrict__ gain, int n_rows, int d, float eps) {
+    griddep_wait();
+    griddep_launch();
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (r >= n_rows) return;
+    float4* xr = reinterpret_cast<float4*>(x + (int64_t)r * d);
+    const float4* rr = res ? reinterpret_cast<const float4*>(res + (int64_t)r * d) : nullptr;
+    const float4* g4 = reinterpret_cast<const float4*>(gain);
+    const int n4 = d >> 2;
+    float4 v[kWarpVec];
+#pragma unroll
+    for (int k = 0; k < kWarpVec; k++) {
+        const int i = lane + k * 32;
+        if (i < n4) v[k] = xr[i];
+    }
+    if (rr) {
+#pragma unroll
+        for (int k = 0; k < kWarpVec; k++) {
+            const int i = lane + k * 32;
+            if (i < n4) {
+                const float4 a = rr[i];
+                v[k].x += a.x; v[k].y += a.y; v[k].z += a.z; v[k].w += a.w;
+                xr[i] = v[k];
+            }
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < kWarpVec; k++)
+        if (lane + k * 32 < n4) ss += (v[k].x * v[k].x + v[k].y * v[k].y) + (v[k].z * v[k].z + v[k].w * v[k].w);
+    ss = warp_sum(ss);
+    const float scale = rsqrtf(ss / (float)d + eps);
+    uint2* orow = reinterpret_cast<uint2*>(out + (int64_t)r * d);
+#pragma unroll
+    for (int k = 0; k < kWarpVec; k++) {
+        const int i = lane + k * 32;
+        if (i < n4) {
+            const float4 g = g4[i];
+            __nv_bfloat162 lo = __floats2bfloat162_rn(v[k].x * scale * g.x, v[k].y * scale * g.y);
+            __nv_bfloat162 hi = __floats2bfloat162_rn(v[k].z * scale * g.z, v[k].w * scale * g.w);
+            uint2 pk;
+            pk.x = *reinterpret_cast<uint32_t*>(&lo);
+            pk.y = *reinterpret_cast<uint32_t*>(&hi);
+            orow[i] = pk;
+        }
+    }
+}
+
 }  // namespace
 
 // dtype: element type of out; res_dtype: element type of res (ignored when res is NULL).
@@ -116,6 +173,11 @@ extern "C" int kllm_add_rmsnorm(void* x, const void* res, void* out, const void*
     auto aligned = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
     if (dtype == KLLM_BF16 && (res == nullptr || res_dtype == KLLM_F32) && rows == nullptr && (d & 3) == 0 &&
         d <= kThreads * 4 * kVec && aligned(x) && aligned(res) && aligned(gain) && ((uintptr_t)out & 7) == 0) {
+        if (n_rows >= 512 && d <= 32 * 4 * kWarpVec) {
+            kllm_launch((add_rmsnorm_warp_kernel), dim3((n_rows + 7) / 8), dim3(256), 0, s, (float*)x, (const float*)res,
+                        (bf16*)out, (const float*)gain, n_rows, d, eps);
+            KLLM_LAUNCH_STATUS();
+        }
         kllm_launch((add_rmsnorm_vec4_kernel), dim3(n_rows), dim3(kThreads), 0, s, (float*)x, (const float*)res, (bf16*)out,
                     (const float*)gain, d, eps);
         KLLM_LAUNCH_STATUS();

@@ -58,6 +58,23 @@ def test_embed_and_gather(dtype):
     assert torch.isnan(bad).all()          # without the table of last tokens a negative id is just a bad id
 
 
+@pytest.mark.parametrize("d", [2048, 200, 2052])
+def test_add_rmsnorm_of_many_rows(d):
+    """600 rows: widths up to 2048 take the kernel with a warp per row, wider ones the block per row."""
+    from kllm_b200 import kernels
+    rng = np.random.default_rng(d)
+    n, eps = 600, 1e-5
+    x0 = (rng.standard_normal((n, d)) * 2).astype(np.float32)
+    res = rng.standard_normal((n, d)).astype(np.float32)
+    gain = (1 + 0.2 * rng.standard_normal(d)).astype(np.float32)
+    x, out = dev(x0), torch.empty((n, d), dtype=torch.bfloat16, device="cuda")
+    kernels.add_rmsnorm(x, dev(res), out, dev(gain), eps)
+    close(x, x0.astype(np.float64) + res, "float32", "residual sum")
+    close(out, plain.rmsnorm(x0.astype(np.float64) + res, gain, eps), "bfloat16", "norm after the sum")
+    kernels.add_rmsnorm(x, None, out, dev(gain), eps)
+    close(out, plain.rmsnorm(x0.astype(np.float64) + res, gain, eps), "bfloat16", "norm alone")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("d", [100, 2048 + 16, 7])
 def test_add_rmsnorm(dtype, d):
