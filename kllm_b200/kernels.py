@@ -179,6 +179,9 @@ USE_TCGEN05 = os.environ.get("KLLM_B200_TCGEN05", "1") != "0"
 SM_COUNT = 148
 
 
+_FORCED_SPLITS = int(os.environ.get("KLLM_B200_DECODE_SPLITS", "0") or 0)
+
+
 def decode_splits(n_tokens: int, n_kv: int, ctx_bound: int) -> int:
     """Into how many key ranges the decode kernel cuts a token's context.
 
@@ -186,7 +189,9 @@ def decode_splits(n_tokens: int, n_kv: int, ctx_bound: int) -> int:
     whole 64-key tiles, as many as fill the SMs in ONE wave (a second wave of short
     CTAs would double the kernel's time), at most 16, all the same length.  When one
     range per token would be long, two are used even if that spills into a second
-    wave: long CTAs hide it."""
+    wave: long CTAs hide it.  KLLM_B200_DECODE_SPLITS=<n> fixes the number (for measuring)."""
+    if _FORCED_SPLITS:
+        return max(1, min(_FORCED_SPLITS, max(1, -(-ctx_bound // 64))))
     slots = 2 * SM_COUNT
     tiles = max(1, -(-ctx_bound // 64))
     base = max(1, n_tokens * n_kv)
