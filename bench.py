@@ -20,9 +20,13 @@ step of the whole batch.  One JSON line is printed:
 
 Weights are random and token ids synthetic (there is neither a checkpoint nor a
 dataset here).  Every decode step reads about 2.4 GB, far more than the 126 MB of
-L2, so nothing is flushed between steps.  ``--impl reference`` would run the
-reference project itself; it is a Go program with a CUDA backend and cannot be
-installed here, so that arm says so and exits 0.
+L2, so nothing is flushed between steps.  ``--impl reference`` runs the reference's
+own CUDA backend (float32, built unmodified by baseline/build_reference.py) through
+its C ABI for the same metric and sizes, or says why it cannot.
+
+``--shape`` picks the layer sizes of another Llama (with ``--layers`` for fewer of
+them) and ``--prefill-tokens`` another prompt length: measurements at further sizes,
+printed in the same form but not the bench line.
 """
 from __future__ import annotations
 
@@ -44,6 +48,15 @@ TINYLLAMA = {
     "num_hidden_layers": 22, "hidden_size": 2048, "num_attention_heads": 32, "num_key_value_heads": 4,
     "head_dim": 64, "intermediate_size": 5632, "vocab_size": 32000, "rope_theta": 10000.0,
     "rms_norm_eps": 1e-5, "max_position_embeddings": 2048, "tie_word_embeddings": False,
+}
+SHAPES = {
+    "tinyllama-1.1b": TINYLLAMA,
+    "llama2-7b": dict(TINYLLAMA, num_hidden_layers=32, hidden_size=4096, num_attention_heads=32,
+                      num_key_value_heads=32, head_dim=128, intermediate_size=11008, vocab_size=32000,
+                      max_position_embeddings=4096),
+    "llama3-8b": dict(TINYLLAMA, num_hidden_layers=32, hidden_size=4096, num_attention_heads=32,
+                      num_key_value_heads=8, head_dim=128, intermediate_size=14336, vocab_size=128256,
+                      rope_theta=500000.0, max_position_embeddings=8192),
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
@@ -163,7 +176,7 @@ def print_timeline(rows, dev_ms):
     # larger than any inside a step (the host's work between steps)
     last = [rows[-1]]
     for r in reversed(rows[:-1]):
-        if last[0]["start"] - r["end"] > 60_000 or r["start"] > last[0]["start"]:
+        if last[0]["start"] - r["end"] > 400_000 or r["start"] > last[0]["start"]:
             break
         last.insert(0, r)
     t0 = last[0]["start"]
@@ -192,6 +205,9 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0: all)")
+    ap.add_argument("--shape", default="tinyllama-1.1b", choices=sorted(SHAPES),
+                    help="layer sizes; other than the default it is a measurement at further sizes, not the bench line")
+    ap.add_argument("--prefill-tokens", type=int, default=2048, help="length of the timed prompt")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and the prefill")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="decode: the batch's decode run alone; prefill: the 2048-token prompt alone (partial "
@@ -219,11 +235,14 @@ def main():
     from kllm_b200.engine import Engine, Options, Scheduler
     from kllm_b200.weights import write_random_model
 
-    cfg = dict(TINYLLAMA)
+    cfg = dict(SHAPES[args.shape])
+    cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], args.context, args.prefill_tokens)
     layers_full = cfg["num_hidden_layers"]
     layers = args.layers or layers_full
     cfg["num_hidden_layers"] = layers
     B, ctx, K, W = args.batch, args.context, args.steps, args.warmup
+    shape_name = {"tinyllama-1.1b": "TinyLlama 1.1B shape", "llama2-7b": "Llama-2 7B shape",
+                  "llama3-8b": "Llama-3 8B shape"}[args.shape]
     pk = peaks()
     tmp = tempfile.mkdtemp(prefix="kllm_b200_bench_")
     try:
@@ -232,9 +251,9 @@ def main():
         print(f"[bench] random weights written in {time.time() - t_w:.1f} s", file=sys.stderr, flush=True)
         page = 64
         max_b = max(B, 64 if not args.no_points else B)
-        pages = max_b * (-(-ctx // page)) + 8
-        eng = Engine(tmp, Options(dtype="bfloat16", max_seq=ctx, block_size=page, num_blocks=pages,
-                                  max_batch=max_b, max_step_tokens=max(2048, max_b),
+        pages = max(max_b * (-(-ctx // page)), -(-args.prefill_tokens // page)) + 8
+        eng = Engine(tmp, Options(dtype="bfloat16", max_seq=max(ctx, args.prefill_tokens), block_size=page, num_blocks=pages,
+                                  max_batch=max_b, max_step_tokens=max(args.prefill_tokens, max_b),
                                   cuda_graphs=not args.no_graphs))
     finally:
         shutil.rmtree(tmp, ignore_errors=True)
@@ -248,10 +267,11 @@ def main():
         """Prefill ``batch`` requests and decode them together so that the furthest
         one ends at context ``ctx``.  Prompts are prefilled one a step while earlier
         requests already decode, so the requests' contexts differ by up to ``batch``
-        tokens; all of them stay live through both timed regions.  Returns (device ms
+        tokens (times the portions of a prompt longer than a step's budget); all of them stay live through both timed regions.  Returns (device ms
         per step, e2e ms per step, launches, h2d, d2h, clocks, cached tokens in the
         middle of the device-timed region)."""
-        total = 2 * (steps + warm) + batch + 2
+        portions = -(-ctx // eng.runner.max_step_tokens)       # steps that one prompt's prefill takes
+        total = 2 * (steps + warm) + batch * portions + 2
         plen = ctx - total
         sched = Scheduler(eng)
         for p in prompts(batch, plen):
@@ -297,7 +317,7 @@ def main():
         sched.stop()
         return dev_ms, e2e_ms, launches, h2d, batch * 4, csum, cached
 
-    def prefill_run(T=2048):
+    def prefill_run(T=args.prefill_tokens):
         from kllm_b200.engine import StepEntry
         ids = prompts(1, T)[0]
         times = []
@@ -337,15 +357,16 @@ def main():
         step_bytes = 2 * weight_elems + kv_bytes
         achieved = step_bytes / (dev_ms * 1e-3) / 1e9
         out = {
-            "metric": "decode tok/s at batch 8 (TinyLlama 1.1B shape, context 2048)",
+            "metric": f"decode tok/s at batch {B} ({shape_name}, context {ctx})",
             "value": round(B / (dev_ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
             "ms_per_step": round(dev_ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic token ids, random weights (seed 4)",
-            "config": {"model": "TinyLlama-1.1B shape", "global_batch": B, "seq_len": ctx, "parallelism": "single GPU",
+            "config": {"model": shape_name.replace("TinyLlama 1.1B", "TinyLlama-1.1B"), "global_batch": B, "seq_len": ctx, "parallelism": "single GPU",
                        "layers": layers, "layers_of_config": layers_full, "hidden": cfg["hidden_size"],
                        "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                        "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
-                       "vocab": cfg["vocab_size"], "page_size": 64, "l2": "step reads 2.4 GB > 126 MB L2, no flush",
+                       "vocab": cfg["vocab_size"], "page_size": 64,
+                       "l2": f"step reads {step_bytes / 1e9:.1f} GB > 126 MB L2, no flush",
                        "peaks": pk["source"]},
             "clocks": clocks,
             "e2e": {"value": round(B / (e2e_ms * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),

@@ -104,9 +104,12 @@ static inline bool kllm_pdl_enabled() {
     return v == 1;
 }
 
+// `early`: the grid may start before the kernel before it in the stream has ended (it
+// then waits in griddep_wait for that kernel's results); without it the grid starts
+// after that kernel as usual and griddep_wait returns at once.
 template <typename... KArgs, typename... Args>
-static inline cudaError_t kllm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                                      cudaStream_t stream, Args&&... args) {
+static inline cudaError_t kllm_launch_dep(bool early, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                          cudaStream_t stream, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -116,8 +119,14 @@ static inline cudaError_t kllm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = kllm_pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = (early && kllm_pdl_enabled()) ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t kllm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                      cudaStream_t stream, Args&&... args) {
+    return kllm_launch_dep(true, kernel, grid, block, smem, stream, static_cast<Args&&>(args)...);
 }
 
 // ---- warming L2 for the kernel after this one ---------------------------------

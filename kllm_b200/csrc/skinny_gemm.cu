@@ -38,13 +38,18 @@ constexpr int THREADS = 512;       // one CTA per SM: X is prepared once per SM,
 constexpr int WARPS = 16;
 constexpr int UNROLL = 4;          // k-steps of 32 in flight per lane and buffer
 constexpr int NORM_F4 = 16;        // float4 a lane may hold in the one-pass norm prologue
+#ifndef KLLM_SKINNY_EARLY_TILES
+#define KLLM_SKINNY_EARLY_TILES 3
+#endif
+constexpr int EARLY_START_TILES = KLLM_SKINNY_EARLY_TILES;   // most tiles per CTA of a kernel that starts early
 
 enum { X_BF16 = 0, X_F32_NORM = 1 };
 enum { STORE_BF16 = 0, STORE_F32 = 1, ADD_F32 = 2, SWIGLU = 3 };
 
 struct Args {
-    const bf16* w;        // [N, K]; SWIGLU: the gate matrix [F, K]
-    const bf16* w_up;     // SWIGLU: the up matrix [F, K]
+    const bf16* w;        // [N, K] at w_stride; SWIGLU: the gate matrix [F, K]
+    const bf16* w_up;     // SWIGLU: the up matrix [F, K] at w_stride
+    int w_stride;         // elements between weight rows (K, or more for a slice of columns)
     int N;                // output columns (SWIGLU: F)
     int K;
     int n;                // rows of X (tokens)
@@ -102,7 +107,7 @@ __global__ void __launch_bounds__(THREADS)
 skinny_gemm_kernel(const Args a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     TL_BEGIN();
-    const int K = a.K, N = a.N, n = a.n;
+    const int K = a.K, N = a.N, n = a.n, WS = a.w_stride;
     const int XS = x_row_elems(K);
     bf16* xs = reinterpret_cast<bf16*>(smem_raw);                         // [8*NT][XS]
     float* red = reinterpret_cast<float*>(smem_raw + (size_t)8 * NT * XS * 2);   // [WARPS][16][8*NT]
@@ -118,11 +123,11 @@ skinny_gemm_kernel(const Args a) {
     auto row_ptrs = [&](int tile, const bf16*& pa, const bf16*& pb) {
         if (EPI == SWIGLU) {
             const int r = min(tile * 8 + g, N - 1);
-            pa = a.w + (int64_t)r * K + 8 * t;
-            pb = a.w_up + (int64_t)r * K + 8 * t;
+            pa = a.w + (int64_t)r * WS + 8 * t;
+            pb = a.w_up + (int64_t)r * WS + 8 * t;
         } else {
-            pa = a.w + (int64_t)min(tile * 16 + g, N - 1) * K + 8 * t;
-            pb = a.w + (int64_t)min(tile * 16 + g + 8, N - 1) * K + 8 * t;
+            pa = a.w + (int64_t)min(tile * 16 + g, N - 1) * WS + 8 * t;
+            pb = a.w + (int64_t)min(tile * 16 + g + 8, N - 1) * WS + 8 * t;
         }
     };
     // Two register buffers of UNROLL k-steps each take turns: while one is being
@@ -234,6 +239,9 @@ skinny_gemm_kernel(const Args a) {
     TL_MARK(2);
 
     // ---- tiles ----
+#ifdef KLLM_SKINNY_TLDETAIL       // instrumented builds only: marks 3..6 are the ends of the first four batches
+    int tl_n = 3;
+#endif
     float acc[NT][4];
 #pragma unroll
     for (int i = 0; i < NT; i++)
@@ -264,6 +272,10 @@ skinny_gemm_kernel(const Args a) {
                 }
             }
         }
+#ifdef KLLM_SKINNY_TLDETAIL
+        if (tl_n == 3) TL_MARK(3); else if (tl_n == 4) TL_MARK(4); else if (tl_n == 5) TL_MARK(5); else if (tl_n == 6) TL_MARK(6);
+        tl_n++;
+#endif
         if (cur_b == nb - 1) {
             // the warps' partial tiles, added in warp order
             const int tile = cur_tile;
@@ -307,7 +319,11 @@ skinny_gemm_kernel(const Args a) {
         phase(buf1a, buf1b, buf0a, buf0b);
     }
     if (PRO == X_BF16) cp_async_wait_pending(0);            // a CTA without a tile: nothing in flight at its end
+#ifdef KLLM_SKINNY_TLDETAIL
+    TL_MARK(7);
+#else
     TL_MARK(3);
+#endif
     TL_END(a.tl_slot, 100 + PRO * 10 + EPI);        // marks: start, dependency wait over, X ready, tiles done
 }
 
@@ -338,7 +354,13 @@ int launch(const Args& a, cudaStream_t s) {
     const int rows_per_tile = (EPI == SWIGLU) ? 8 : 16;
     const int n_tiles = (a.N + rows_per_tile - 1) / rows_per_tile;
     const int grid = min(n_tiles, max_grid);
-    kllm_launch((kern), dim3(grid), dim3(THREADS), smem, s, a);
+    // A kernel of a few tiles per CTA starts early, beside the tail of the kernel before it,
+    // so that its first weights and the next kernel's share of L2 are on their way while it
+    // waits.  One with many tiles gains nothing from that and was measured to stream
+    // slower when it got an early start (at 12 tiles per CTA and K = 4096 at half speed:
+    // 235 MB in 72 us instead of 45), so it starts when the kernel before it has ended.
+    const bool early = n_tiles <= EARLY_START_TILES * grid;
+    kllm_launch_dep(early, (kern), dim3(grid), dim3(THREADS), smem, s, a);
     KLLM_LAUNCH_STATUS();
 }
 
@@ -368,9 +390,12 @@ extern "C" int kllm_skinny_gemm_fits(int n, int K) {
 // rows[r] when rows is given), normalised with gain [K] and eps.
 // epilogue 0/3: y_bf16 [n, N] at y_stride (3: w = gate [N, K], w_up = up [N, K]);
 // epilogue 1: y_f32 written; epilogue 2: y_f32 += result.
+// w_stride: elements from one weight row to the next (>= K; more than K when the call
+// multiplies a slice of the columns of a wider matrix, which is how a K too long for
+// shared memory is taken: one call per slice, each adding into y_f32).
 // prefetch: optional, `prefetch_bytes` bytes that a later kernel will stream; they are
 // requested into L2 before this kernel's own work.
-extern "C" int kllm_skinny_gemm(const void* w, const void* w_up, int N, int K, int n, const void* x_bf16,
+extern "C" int kllm_skinny_gemm(const void* w, const void* w_up, int64_t w_stride, int N, int K, int n, const void* x_bf16,
                                 int64_t x_stride, const float* x_f32, const float* gain, const int* rows,
                                 float eps, void* y_bf16, float* y_f32, int64_t y_stride, int prologue,
                                 int epilogue, const void* prefetch, int64_t prefetch_bytes, void* stream) {
@@ -382,11 +407,12 @@ extern "C" int kllm_skinny_gemm(const void* w, const void* w_up, int N, int K, i
         KLLM_FAIL("skinny_gemm: bfloat16 X must be 16-byte aligned with a row stride that is a multiple of 8");
     if (prologue == X_F32_NORM && (!x_f32 || !gain || ((uintptr_t)x_f32 & 15) || ((uintptr_t)gain & 15)))
         KLLM_FAIL("skinny_gemm: float32 X and gain must be 16-byte aligned");
-    if ((uintptr_t)w & 15) KLLM_FAIL("skinny_gemm: weights must be 16-byte aligned");
+    if (((uintptr_t)w & 15) || w_stride < K || (w_stride % 8) || w_stride > INT32_MAX)
+        KLLM_FAIL("skinny_gemm: weights must be 16-byte aligned, their row stride a multiple of 8 and at least K");
     if (epilogue == SWIGLU && (!w_up || ((uintptr_t)w_up & 15))) KLLM_FAIL("skinny_gemm: SWIGLU needs the up matrix");
     if ((epilogue == STORE_BF16 || epilogue == SWIGLU) ? !y_bf16 : !y_f32) KLLM_FAIL("skinny_gemm: no output buffer");
     Args a;
-    a.w = (const bf16*)w; a.w_up = (const bf16*)w_up; a.N = N; a.K = K; a.n = n;
+    a.w = (const bf16*)w; a.w_up = (const bf16*)w_up; a.w_stride = (int)w_stride; a.N = N; a.K = K; a.n = n;
     a.x_bf16 = (const bf16*)x_bf16; a.x_stride = x_stride; a.x_f32 = x_f32; a.gain = gain; a.rows = rows; a.eps = eps;
     a.y_bf16 = (bf16*)y_bf16; a.y_f32 = y_f32; a.y_stride = y_stride;
     if (prefetch && ((uintptr_t)prefetch & 15)) KLLM_FAIL("skinny_gemm: the matrix to prefetch must be 16-byte aligned");

@@ -175,6 +175,9 @@ def attention_generic(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, 
 TC_HEAD_DIMS = tuple(range(16, 129, 16))     # head sizes of the tensor-core attention library
 TCGEN05_HEAD_DIMS = (64, 128)                # head sizes of the tcgen05 prefill attention
 PREFETCH_L2 = os.environ.get("KLLM_B200_PREFETCH", "1") != "0"   # kernels warm L2 for the kernel after them
+# ... with at most this much of the next matrix: what is asked for beyond a fraction of the
+# 126 MB of L2 pushes out lines that are still needed and is read from HBM twice
+PREFETCH_L2_BYTES = int(float(os.environ.get("KLLM_B200_PREFETCH_MB", "24")) * 2 ** 20)
 USE_TCGEN05 = os.environ.get("KLLM_B200_TCGEN05", "1") != "0"
 SM_COUNT = 148
 
@@ -442,13 +445,24 @@ _PRO = {"bf16": 0, "norm": 1}
 _EPI = {"bf16": 0, "f32": 1, "add": 2, "swiglu": 3}
 
 
-def skinny_fits(n: int, k: int, dtype: torch.dtype) -> bool:
-    """Whether the weight-streaming product takes n rows of width k in this dtype."""
+def skinny_fits(n: int, k: int, dtype: torch.dtype, sliced: bool = False) -> bool:
+    """Whether the weight-streaming product takes n rows of width k in this dtype.
+    ``sliced``: the caller adds into a float32 matrix from bfloat16 rows, where a width
+    too long for shared memory is taken slice by slice (any multiple of 32 fits then)."""
     if dtype != torch.bfloat16 or not (1 <= n <= SKINNY_MAX_ROWS) or k < 32 or k % 32:
         return False
+    return sliced or k <= _skinny_max_width(n)
+
+
+def _skinny_max_width(n: int) -> int:
+    """Largest width (a multiple of 32) whose X rows, the 16 warps' partial tiles and the
+    norm's gain fit the 227 KB of shared memory (smem_bytes in csrc/skinny_gemm.cu)."""
     nt = 1 if n <= 8 else 2
-    row = k + (32 if (k * 2) % 128 == 0 else 0)
-    return 8 * nt * row * 2 + 16 * 16 * 8 * nt * 4 <= 227 * 1024     # X rows + the 16 warps' partial tiles
+    room = 227 * 1024 - 16 * 16 * 8 * nt * 4
+    k = room // (8 * nt * 2 + 4) // 32 * 32
+    while 8 * nt * (k + (32 if (k * 2) % 128 == 0 else 0)) * 2 + k * 4 > room:
+        k -= 32
+    return k
 
 
 def _prefetch_args(t: Optional[torch.Tensor]):
@@ -456,7 +470,7 @@ def _prefetch_args(t: Optional[torch.Tensor]):
         return None, ctypes.c_int64(0)
     if not t.is_contiguous():
         raise KernelError("prefetch: the tensor to bring into L2 must be contiguous")
-    return _p(t), ctypes.c_int64(t.numel() * t.element_size())
+    return _p(t), ctypes.c_int64(min(t.numel() * t.element_size(), PREFETCH_L2_BYTES) // 16 * 16)
 
 
 def skinny_gemm(weight: torch.Tensor, *, x: Optional[torch.Tensor] = None, x_f32: Optional[torch.Tensor] = None,
@@ -471,11 +485,26 @@ def skinny_gemm(weight: torch.Tensor, *, x: Optional[torch.Tensor] = None, x_f32
     ``weight_up`` as up matrix and stores silu(gate) * up as bfloat16 [n, N].
     ``prefetch``: a contiguous tensor that a later kernel will stream (the next weight
     matrix); the kernel asks for it to be brought into L2 before its own work.
+    A width K too long for shared memory is taken in column slices, one launch each, when
+    X is bfloat16 and the epilogue is "add" (the slices' sums meet in ``out``, always in
+    the same order).
     """
     _cuda(weight, x, x_f32, gain, rows, weight_up, out, prefetch)
     N, K = weight.shape
-    if weight.dtype != torch.bfloat16 or not weight.is_contiguous():
-        raise KernelError("skinny_gemm: the weight must be contiguous bfloat16")
+    if weight.dtype != torch.bfloat16 or weight.stride(1) != 1 or weight.stride(0) % 8:
+        raise KernelError("skinny_gemm: the weight must be bfloat16 with dense rows at a stride that is a multiple of 8")
+    if weight_up is not None and weight_up.stride() != weight.stride():
+        raise KernelError("skinny_gemm: the up matrix must be laid out like the gate matrix")
+    if x is not None and epilogue == "add" and out is not None and K % 32 == 0 and 1 <= x.shape[0] <= SKINNY_MAX_ROWS \
+            and K > _skinny_max_width(x.shape[0]):
+        widest = _skinny_max_width(x.shape[0])
+        parts = -(-K // widest)
+        width = -(-K // parts // 32) * 32
+        for lo in range(0, K, width):
+            hi = min(K, lo + width)
+            skinny_gemm(weight[:, lo:hi], x=x[:, lo:hi], epilogue="add", out=out,
+                        prefetch=prefetch if hi == K else None)
+        return out
     if x is not None:
         pro, n = 0, x.shape[0]
         if x.dtype != torch.bfloat16 or x.stride(1) != 1 or x.shape[1] != K:
@@ -492,7 +521,7 @@ def skinny_gemm(weight: torch.Tensor, *, x: Optional[torch.Tensor] = None, x_f32
     if not skinny_fits(n, K, torch.bfloat16):
         raise KernelError(f"skinny_gemm: {n} rows of width {K} are not supported")
     epi = _EPI[epilogue]
-    if epilogue == "swiglu" and (weight_up is None or weight_up.shape != weight.shape or not weight_up.is_contiguous()
+    if epilogue == "swiglu" and (weight_up is None or weight_up.shape != weight.shape
                                  or weight_up.dtype != torch.bfloat16):
         raise KernelError("skinny_gemm: swiglu needs an up matrix like the gate matrix")
     if out is None:
@@ -505,7 +534,7 @@ def skinny_gemm(weight: torch.Tensor, *, x: Optional[torch.Tensor] = None, x_f32
     lib = load_library("skinny_gemm")
     y16 = out if want == torch.bfloat16 else None
     y32 = out if want == torch.float32 else None
-    rc = lib.kllm_skinny_gemm(_p(weight), _p(weight_up), N, K, n, _p(x),
+    rc = lib.kllm_skinny_gemm(_p(weight), _p(weight_up), ctypes.c_int64(weight.stride(0)), N, K, n, _p(x),
                               ctypes.c_int64(x.stride(0) if x is not None else 0), _p(x_f32), _p(gain), _p(rows),
                               ctypes.c_float(eps), _p(y16), _p(y32), ctypes.c_int64(out.stride(0)), pro, epi,
                               *_prefetch_args(prefetch), _stream())

@@ -132,7 +132,7 @@ class PagedAttention:
         n = x.shape[0]
         w = self.w_qkv if cache.writes else self.w_qkv[:self.q_dim]
         if not (getattr(norm, "fusable_rmsnorm", False) and kernels.skinny_fits(n, self.hidden, self.dtype)
-                and kernels.skinny_fits(n, self.q_dim, self.dtype)):
+                and kernels.skinny_fits(n, self.q_dim, self.dtype, sliced=True)):
             # larger steps: the library's products, the last one adding into the residual stream
             q, k, v = self._split(kernels.linear(norm.forward(x, None), w), cache.writes)
             kernels.linear_add(x, self._attend(q, k, v, ctx, cache), self.w_o)

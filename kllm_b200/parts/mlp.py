@@ -85,7 +85,7 @@ class GatedMLP:
     def forward_residual(self, x, norm, ctx):
         n = x.shape[0]
         if not (getattr(norm, "fusable_rmsnorm", False) and kernels.skinny_fits(n, self.hidden, self.dtype)
-                and kernels.skinny_fits(n, self.inter, self.dtype)):
+                and kernels.skinny_fits(n, self.inter, self.dtype, sliced=True)):
             # larger steps: the down product adds into the residual stream
             kernels.linear_add(x, self._activation(norm.forward(x, None)), self.w_down)
             return True

@@ -598,6 +598,31 @@ def test_skinny_gemm_refusals():
         kernels.skinny_gemm(w, x=torch.zeros(17, 64, device="cuda", dtype=torch.bfloat16))
     assert not kernels.skinny_fits(8, 64, torch.float32) and kernels.skinny_fits(16, 5632, torch.bfloat16)
     assert not kernels.skinny_fits(16, 14336, torch.bfloat16)
+    assert kernels.skinny_fits(16, 14336, torch.bfloat16, sliced=True)
+    assert not kernels.skinny_fits(16, 14336 + 8, torch.bfloat16, sliced=True)
+
+
+@pytest.mark.parametrize("n,N,K", [(8, 72, 14336), (13, 40, 14336), (16, 24, 6016), (3, 50, 11200)])
+def test_skinny_gemm_adds_a_long_k_in_slices(n, N, K):
+    """A width too long for shared memory: the adding product takes it in column slices
+    of the weight matrix (rows at a stride), and a far column still counts."""
+    from kllm_b200 import kernels
+    rng = np.random.default_rng(n + N + K)
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    x = rng.standard_normal((n, K)).astype(np.float32)
+    w[:, K - 1] = 0.5                                   # the last column alone moves every output
+    x[:, K - 1] = 8.0
+    ws, xs = as_stored(w, "bfloat16"), as_stored(x, "bfloat16")
+    base = rng.standard_normal((n, N)).astype(np.float32)
+    acc = dev(base)
+    kernels.skinny_gemm(dev(w, torch.bfloat16), x=dev(x, torch.bfloat16), epilogue="add", out=acc)
+    close(acc, base.astype(np.float64) + xs @ ws.T, "float32", "sliced residual add")
+    # a slice of columns given by the caller: rows at a stride, start not at the matrix's first column
+    lo, hi = 64, 64 + 4096
+    acc2 = dev(base)
+    kernels.skinny_gemm(dev(w, torch.bfloat16)[:, lo:hi], x=dev(x, torch.bfloat16)[:, lo:hi], epilogue="add", out=acc2)
+    close(acc2, base.astype(np.float64) + xs[:, lo:hi] @ ws[:, lo:hi].T, "float32", "strided weight rows")
+    kernels.check_status("cuda")
 
 
 def test_kernels_refuse_what_they_cannot_take():
