@@ -359,7 +359,11 @@ int launch(const Args& a, cudaStream_t s) {
     // waits.  One with many tiles gains nothing from that and was measured to stream
     // slower when it got an early start (at 12 tiles per CTA and K = 4096 at half speed:
     // 235 MB in 72 us instead of 45), so it starts when the kernel before it has ended.
+#ifdef KLLM_SKINNY_EARLY_MASK      // measurements: which kinds of kernel start early (bit = PRO * 4 + EPI)
+    const bool early = (KLLM_SKINNY_EARLY_MASK >> (PRO * 4 + EPI)) & 1;
+#else
     const bool early = n_tiles <= EARLY_START_TILES * grid;
+#endif
     kllm_launch_dep(early, (kern), dim3(grid), dim3(THREADS), smem, s, a);
     KLLM_LAUNCH_STATUS();
 }
