@@ -96,3 +96,19 @@ def test_registering_another_architecture():
     register_architecture("ToyTestModel", ToyConfig, lambda c: ("spec of", c.width))
     c = parse_config({"architectures": ["ToyTestModel"], "width": 24})
     assert build_model_spec(c) == ("spec of", 24)
+
+
+def test_bench_shapes_are_configurations_of_the_architecture():
+    """The layer sizes that bench.py offers parse as configurations and build a spec."""
+    import importlib.util
+    import os
+    spec = importlib.util.spec_from_file_location(
+        "kllm_bench", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    from kllm_b200.config.base import build_model_spec, parse_config
+    assert "tinyllama-1.1b" in bench.SHAPES and len(bench.SHAPES) >= 3
+    for name, d in bench.SHAPES.items():
+        cfg = parse_config(dict(d))
+        model = build_model_spec(cfg)
+        assert len(model.blocks) == len(model.schedule) == d["num_hidden_layers"], name
