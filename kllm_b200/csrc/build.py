@@ -24,7 +24,7 @@ CSRC = os.path.dirname(os.path.abspath(__file__))
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ARCH_FLAGS + ["-lineinfo", "-O3", "-std=c++17", "-shared", "-Xcompiler", "-fPIC",
                            "--expt-relaxed-constexpr"]
-HEADERS = ["common.cuh", "attention_tc_static.h"]
+HEADERS = ["common.cuh", "attention_tc_static.h", "tc5_common.cuh"]
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()

@@ -36,17 +36,14 @@
 // memory and returns.
 #include "common.cuh"
 
-#include <cuda.h>  // CUtensorMap and its enums; the encoder itself is looked up at run time
-
-#include <mutex>
-#include <unordered_map>
-
 KLLM_EXPORT_LAST_ERROR(gemm_tcgen05)
+
+#include "tc5_common.cuh"
 
 namespace {
 
 constexpr int BM = 128;                    // rows of a tile = lanes of tensor memory
-constexpr int BK = 64;                     // k block: 64 bfloat16 = one 128-byte swizzled row
+constexpr int BK = TC5_BK;                 // k block: 64 bfloat16 = one 128-byte swizzled row
 constexpr int THREADS = 320;
 constexpr int EPI_THREADS = 256;
 constexpr int A_BYTES = BM * 128;
@@ -54,99 +51,8 @@ constexpr int MAX_BN = 256;                // accumulators sit 256 columns apart
 constexpr int TMEM_COLS = 2 * MAX_BN;
 constexpr int MAX_STAGES = 8;
 constexpr int SMEM_BYTES = 1024 + 4 * (A_BYTES + MAX_BN * 128);    // four stages of the widest tile
-constexpr long long kCycleLimit = 4000000000LL;   // about two seconds
 
 enum Epilogue { EPI_BF16 = 0, EPI_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU = 3 };
-
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
-    unsigned ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-
-// Bounded wait.  Returns false (and raises the flags) when the limit ran out or
-// another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag, int* status, int where) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    unsigned spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 255u) == 0) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > kCycleLimit) {
-                *abort_flag = 1;
-                if (status) atomicCAS(status, 0, where);
-                return false;
-            }
-        }
-    }
-    return true;
-}
-
-// one 2-D tile by TMA: box (64 elements of k) x (rows), landing 128-byte swizzled
-__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
-                 ::"r"(dst), "l"((uint64_t)map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void prefetch_map(const CUtensorMap* map) {
-    asm volatile("prefetch.tensormap [%0];\n" ::"l"((uint64_t)map) : "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major operand in the 128-byte swizzled layout:
-// 8-row groups 1024 bytes apart, descriptor version 1, layout type 2.
-__device__ __forceinline__ uint64_t make_desc(unsigned addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr >> 4) & 0x3FFF);
-    d |= (uint64_t)(16 >> 4) << 16;
-    d |= (uint64_t)(1024 >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
-// float32 accumulator, bfloat16 A and B (both K-major), M x N
-__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-__device__ __forceinline__ void umma(unsigned d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((unsigned)accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(unsigned taddr, float (&v)[32]) {
-    uint32_t* r = reinterpret_cast<uint32_t*>(v);
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
-
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
-__device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.f + expf(-g))) * u; }
 
 // 32 consecutive results of one row, columns col..col+31 of the output, those below
 // `limit` (the end of the tile or of the matrix); res: what the float32 destination held
@@ -362,78 +268,6 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 }
 
 // ---- host side -----------------------------------------------------------------
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encoder() {
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    }
-    return fn;
-}
-
-struct MapKey {
-    const void* ptr;
-    int64_t ld;
-    int rows, cols, box_rows;
-    bool operator==(const MapKey& o) const {
-        return ptr == o.ptr && ld == o.ld && rows == o.rows && cols == o.cols && box_rows == o.box_rows;
-    }
-};
-struct MapKeyHash {
-    size_t operator()(const MapKey& k) const {
-        size_t h = (size_t)(uintptr_t)k.ptr;
-        h = h * 1000003u ^ (size_t)k.ld;
-        h = h * 1000003u ^ (size_t)k.rows;
-        h = h * 1000003u ^ (size_t)k.cols;
-        h = h * 1000003u ^ (size_t)k.box_rows;
-        return h;
-    }
-};
-
-// Descriptor of a row-major [rows, cols] bfloat16 matrix (cols contiguous, row stride ld
-// elements) read in boxes of 64 columns x box_rows rows.  A descriptor holds no data, only
-// the address and the shape, so it is kept for the next call with the same matrix.
-int tensor_map(CUtensorMap* out, const void* ptr, int64_t ld, int rows, int cols, int box_rows) {
-    static std::mutex mu;
-    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-    const MapKey key{ptr, ld, rows, cols, box_rows};
-    std::lock_guard<std::mutex> lock(mu);
-    auto it = cache.find(key);
-    if (it != cache.end()) { *out = it->second; return 0; }
-    EncodeTiledFn fn = encoder();
-    if (!fn) KLLM_FAIL("gemm (tcgen05): the driver does not offer cuTensorMapEncodeTiled");
-    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) KLLM_FAIL("gemm (tcgen05): tensor map for a %d x %d matrix (row stride %lld) refused: %d", rows, cols, (long long)ld, (int)r);
-    if (cache.size() >= 4096) cache.clear();
-    cache.emplace(key, *out);
-    return 0;
-}
-
-int sm_count() {
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-            n = 148;
-    }
-    return n;
-}
 
 // Accumulator width: a tile's time does not shrink with its width (see the top of the
 // file), so the widest one with the fewest waves of tiles wins.
