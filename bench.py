@@ -133,6 +133,9 @@ def reference_arm(args):
     if args.gpus != 1:
         print(f"bench.py: the reference runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.shape != "tinyllama-1.1b" or args.prefill_tokens != 2048:
+        print("bench.py: the reference arm measures the default shape and prompt length only")
+        return 2
     cfg = dict(TINYLLAMA)
     layers_full = cfg["num_hidden_layers"]
     cfg["num_hidden_layers"] = args.layers or layers_full
