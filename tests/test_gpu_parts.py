@@ -150,6 +150,37 @@ def test_embedding_and_head_parts(dtype):
     close(logits, stored(table, dtype)[[52, 0, 7]] @ stored(table, dtype).T, dtype)
 
 
+@pytest.mark.parametrize("n", [6, 12])
+def test_feed_forward_part_fused_route_with_a_width_that_needs_slices(n):
+    """The decode route (norm inside the gate/up kernel, down product adding into the
+    residual stream) with an intermediate width too long for the down kernel's shared
+    memory at 12 rows: that product runs over column slices."""
+    from kllm_b200 import kernels
+    from kllm_b200.parts.spec import PartSpec, part_factory
+    rng = np.random.default_rng(n)
+    d, f = 64, 6016
+    assert not kernels.skinny_fits(12, f, torch.bfloat16) and kernels.skinny_fits(6, f, torch.bfloat16)
+    env = env_for("bfloat16", d)
+    part = part_factory("feed_forward", "gated_mlp")(
+        PartSpec("gated_mlp", "ff", {"hidden": d, "intermediate": f, "activation": "silu"}), env)
+    norm = part_factory("norm", "rmsnorm")(PartSpec("rmsnorm", "n", {"width": d, "eps": 1e-5}), env)
+    w = {f"ff.{k}_proj.weight": (rng.standard_normal(s) * 0.05).astype(np.float32)
+         for k, s in (("gate", (f, d)), ("up", (f, d)), ("down", (d, f)))}
+    w["ff.down_proj.weight"][:, f - 1] = 0.5          # the last column of the last slice counts
+    gain = (1 + 0.2 * rng.standard_normal(d)).astype(np.float32)
+    bind(part, w, "bfloat16")
+    bind(norm, {"n.weight": gain}, "bfloat16")
+    x0 = rng.standard_normal((n, d)).astype(np.float32)
+    x = torch.from_numpy(x0).cuda()
+    assert part.forward_residual(x, norm, None) is True
+    ws = {k: stored(v, "bfloat16") for k, v in w.items()}
+    xn = plain.round_act_bf16(plain.rmsnorm(x0, gain, 1e-5))
+    want = x0 + plain.swiglu(xn, ws["ff.gate_proj.weight"], ws["ff.up_proj.weight"], ws["ff.down_proj.weight"],
+                             plain.round_act_bf16)
+    close(x, want, "bfloat16", "residual stream after the fused feed-forward")
+    kernels.check_status("cuda")
+
+
 @pytest.mark.parametrize("n", [40, 300])
 def test_feed_forward_part_on_the_tensor_core_route(n, monkeypatch):
     """The gated feed-forward with gate, up and activation in one tcgen05 kernel, the
