@@ -83,3 +83,25 @@ def portions(total: int, sizes):
         done += n
         i += 1
     return out
+
+
+def run_on_engine(eng, builder: TraceBuilder):
+    """The same trace through an ``Engine`` of this process (its step function, cache
+    manager and kernels), without the replay program.  Returns {(rid, position): row}."""
+    from kllm_b200.engine import StepEntry
+    live, out = {}, {}
+    for rec in builder.steps:
+        entries = []
+        for e in rec["entries"]:
+            if e["id"] not in live:
+                live[e["id"]] = eng.cache.open()
+            entries.append(StepEntry(live[e["id"]], e["tokens"], e["want"]))
+        logits = eng.step(entries)
+        if logits is not None:
+            arr = logits.cpu().numpy()
+            for i, key in enumerate(builder.rows[rec["step"]]):
+                assert key not in out, f"row {key} written twice"
+                out[key] = arr[i]
+        for rid in rec["end"]:
+            eng.cache.close(live.pop(rid))
+    return out
