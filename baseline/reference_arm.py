@@ -38,7 +38,10 @@ def available() -> str:
 
 
 class Reference:
-    def __init__(self, cfg: dict, max_seqs: int, max_seq: int, block: int = 16, seed: int = 4):
+    def __init__(self, cfg: dict, max_seqs: int, max_seq: int, block: int = 16, seed: int = 4, weights=None):
+        """``weights``: tensor name -> float32 array to upload instead of random ones (a tied
+        model's embedding goes in under ``lm_head.weight`` too, as tools/convert_hf.py:81-82
+        resolves tying offline).  The backend holds one model per process."""
         self.lib = ctypes.CDLL(LIB)
         self.cfg, self.block, self.max_seq = cfg, block, max_seq
         self.blocks_per_seq = -(-max_seq // block)
@@ -55,7 +58,12 @@ class Reference:
         qd, kd = c.n_heads * c.head_dim, c.n_kv_heads * c.head_dim
 
         def load(name, shape, gain=False):
-            a = np.ones(shape, np.float32) if gain else (rng.standard_normal(shape, dtype=np.float32) * 0.02)
+            if weights is not None:
+                src = "model.embed_tokens.weight" if name == "lm_head.weight" and name not in weights else name
+                a = np.ascontiguousarray(weights[src], np.float32)
+                assert a.shape == tuple(shape), f"{name}: {a.shape} is not {tuple(shape)}"
+            else:
+                a = np.ones(shape, np.float32) if gain else (rng.standard_normal(shape, dtype=np.float32) * 0.02)
             self._ok(self.lib.te_model_load_tensor(name.encode(), a.ctypes.data_as(ctypes.c_void_p),
                                                    ctypes.c_int64(a.size)))
 
@@ -90,6 +98,23 @@ class Reference:
         p = lambda a: a.ctypes.data_as(ctypes.c_void_p)
         self._ok(self.lib.te_forward_batch(ctypes.c_int64(n_seqs), p(tok), p(nt), p(ps), p(tb),
                                            ctypes.c_int64(tb.shape[1]), p(out)))
+        return out
+
+    def debug(self, on: bool):
+        """Switch the backend's debug taps (backend/shim.h:128-136)."""
+        self._ok(self.lib.te_debug_set(ctypes.c_int64(1 if on else 0)))
+
+    def taps(self):
+        """What the last forward captured: the embedding output, the residual stream after
+        every layer and the final norm's output, each [tokens of the step * hidden]."""
+        self.lib.te_debug_count.restype = ctypes.c_int64
+        self.lib.te_debug_size.restype = ctypes.c_int64
+        out = []
+        for i in range(int(self.lib.te_debug_count())):
+            n = int(self.lib.te_debug_size(ctypes.c_int64(i)))
+            a = np.empty(n, np.float32)
+            self._ok(self.lib.te_debug_read(ctypes.c_int64(i), a.ctypes.data_as(ctypes.c_void_p), ctypes.c_int64(n)))
+            out.append(a)
         return out
 
     def tables(self, n_seqs):

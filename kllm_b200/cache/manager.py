@@ -163,9 +163,26 @@ class CacheManager:
 
     # ---- sizes -----------------------------------------------------------
     def bytes_per_page(self) -> int:
+        """Device bytes that one more page in EVERY group's pool costs: keys and values of
+        all layers of all groups (the pools have the same number of pages)."""
         esize = torch.empty((), dtype=self.dtype).element_size()
         return sum(len(g.slots) * 2 * g.need.n_kv_heads * self.page_size * g.need.head_dim * esize
                    for g in self.groups)
+
+    @classmethod
+    def pages_within(cls, needs: Sequence, page_size: int, dtype: torch.dtype, budget_bytes: int) -> int:
+        """How many pages per pool fit ``budget_bytes`` of device memory: the budget over
+        ``bytes_per_page()`` (the reference's rule, pages = budget / (layers * 2 * page *
+        kv width * element size); it sized a pool by a fixed count first and ran out of
+        memory on a larger model, docs/JOURNAL.md:364-367, tools/modal_lab.py:232-240).
+        Raises when not even one page fits."""
+        per = cls(needs, page_size, 1, max_requests=1, dtype=dtype, allocate=False).bytes_per_page()
+        if per == 0:
+            return 1                  # no paged cache in this model: one page that nobody takes
+        pages = int(budget_bytes) // per
+        if pages < 1:
+            raise ValueError(f"a cache budget of {int(budget_bytes)} bytes holds no page ({per} bytes each)")
+        return pages
 
     def bytes_per_token_full(self) -> int:
         """Cache bytes that one more token of context costs in the groups that keep
@@ -173,6 +190,21 @@ class CacheManager:
         esize = torch.empty((), dtype=self.dtype).element_size()
         return sum(len(g.slots) * 2 * g.need.n_kv_heads * g.need.head_dim * esize
                    for g in self.groups if g.window is None)
+
+    def pages_ever_needed(self, total_tokens: int) -> List[int]:
+        """Per group, the most pages a request of ``total_tokens`` tokens must hold at one
+        time if it is fed in portions as small as need be.  A group that keeps every key
+        needs a page for each ``page_size`` tokens; a window group only the pages that the
+        window of one query can touch (the window's width, whatever its alignment, plus the
+        page of the token being written), since the pages behind the window come back at
+        every commit.  A model without any paged group needs none."""
+        out = []
+        for g in self.groups:
+            pages = -(-int(total_tokens) // self.page_size)
+            if g.window is not None:
+                pages = min(pages, (g.window - 1) // self.page_size + 2)
+            out.append(pages)
+        return out
 
     def free_pages(self) -> List[int]:
         return [g.pool.free_count for g in self.groups]

@@ -7,7 +7,7 @@ same two output lines.
 ``--backend`` named the CUDA backend library there; here the kernels are built
 from source on first use, and the option names the folder where the built
 libraries are kept.  Added: ``--temperature``, ``--seed``, ``--dtype``,
-``--block-size``, ``--num-blocks``, ``--max-step-tokens``, and ``--random-config``
+``--block-size``, ``--num-blocks``, ``--cache-gb``, ``--max-step-tokens``, and ``--random-config``
 to write a random-weights model folder first.
 """
 from __future__ import annotations
@@ -45,7 +45,10 @@ def main(argv=None) -> int:
     ap.add_argument("--seed", type=int, default=0, help="sampler seed")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
-    ap.add_argument("--num-blocks", type=int, default=0, help="cache pages (0: 4 * max-seq / block-size)")
+    ap.add_argument("--num-blocks", type=int, default=0,
+                    help="cache pages (0: from --cache-gb, else 4 * max-seq / block-size)")
+    ap.add_argument("--cache-gb", type=float, default=0.0,
+                    help="device memory for the paged cache in GB; sizes the pool when --num-blocks is 0")
     ap.add_argument("--max-step-tokens", type=int, default=0, help="token budget of one step (0: max-seq)")
     ap.add_argument("--random-config", default="", help="a config.json: write random weights for it into --model first")
     ap.add_argument("--random-seed", type=int, default=0, help="seed of --random-config")
@@ -65,6 +68,7 @@ def main(argv=None) -> int:
         from .engine import Engine, Options
         eng = Engine(args.model, Options(device=args.device, max_seq=args.max_seq, dtype=args.dtype,
                                          block_size=args.block_size, num_blocks=args.num_blocks,
+                                         cache_bytes=int(args.cache_gb * 1e9),
                                          max_step_tokens=args.max_step_tokens))
         try:
             out = eng.generate(prompt, max_new_tokens=args.steps, temperature=args.temperature, seed=args.seed)

@@ -104,10 +104,11 @@ add_rmsnorm_vec4_kernel(float* __restrict__ x, const float* __restrict__ res, bf
     }
 }
 
-// Many rows (a prompt portion): one warp per row, the row in registers, no block-wide
-// synchronisation; 8 rows per CTA.  Width a multiple of 4 up to 32 * 4 * kWarpVec.  Lane l
-// adds the squares of its float4 l, l + 32, ... in that order, then the lanes are added
-// in a fixed tree.
+// One warp per row, the row in registers, no block-wide synchronisation; 8 rows per CTA.
+// Width a multiple of 4 up to 32 * 4 * kWarpVec.  Lane l adds the squares of its float4 l,
+// l + 32, ... in that order, then the lanes are added in a fixed tree.  Which of the two
+// vectorised kernels runs is decided by the width alone, never by the number of rows, so
+// a row is summed in the same order whatever else the step holds.
 constexpr int kWarpVec = 16;
 
 __global__ void __launch_bounds__(256)
@@ -173,7 +174,7 @@ extern "C" int kllm_add_rmsnorm(void* x, const void* res, void* out, const void*
     auto aligned = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
     if (dtype == KLLM_BF16 && (res == nullptr || res_dtype == KLLM_F32) && rows == nullptr && (d & 3) == 0 &&
         d <= kThreads * 4 * kVec && aligned(x) && aligned(res) && aligned(gain) && ((uintptr_t)out & 7) == 0) {
-        if (n_rows >= 512 && d <= 32 * 4 * kWarpVec) {
+        if (d <= 32 * 4 * kWarpVec) {
             kllm_launch((add_rmsnorm_warp_kernel), dim3((n_rows + 7) / 8), dim3(256), 0, s, (float*)x, (const float*)res,
                         (bf16*)out, (const float*)gain, n_rows, d, eps);
             KLLM_LAUNCH_STATUS();

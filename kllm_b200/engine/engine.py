@@ -4,7 +4,8 @@ Build-up as in the reference (engine/engine.go:48-97): read and type the
 configuration, pick the model by its architecture name, build it from parts, bind
 the weights by name, size the cache.  ``Options`` keeps the reference's knobs and
 defaults (engine/engine.go:16-33): ``max_seq`` 256, ``block_size`` 16, ``num_blocks``
-4 * max_seq / block_size; the per-step token budget and the batch limit are knobs
+4 * max_seq / block_size; ``cache_bytes`` sizes the pools from a memory budget and
+the model's layers instead; the per-step token budget and the batch limit are knobs
 of their own here (the reference reuses max_seq for the first and fixes the second
 in its scheduler, engine/scheduler.go:43-46).
 """
@@ -33,7 +34,8 @@ class Options:
     device: int = 0
     max_seq: int = 256            # most tokens one request may hold
     block_size: int = 16          # tokens per cache page
-    num_blocks: int = 0           # pages per cache group; 0: 4 * max_seq / block_size
+    num_blocks: int = 0           # pages per cache group; 0: from cache_bytes, else 4 * max_seq / block_size
+    cache_bytes: int = 0          # device memory for the paged cache; sizes the pools when num_blocks is 0
     max_step_tokens: int = 0      # token budget of one step; 0: max_seq
     max_batch: int = 8            # most requests in one step
     dtype: str = "bfloat16"       # "bfloat16" (serving) or "float32" (true 32-bit)
@@ -46,7 +48,8 @@ class Options:
         if o.block_size <= 0:
             o.block_size = 16
         if o.num_blocks <= 0:
-            o.num_blocks = max(1, 4 * o.max_seq // o.block_size)
+            # with a byte budget the count follows from the model's layers (Engine.__init__)
+            o.num_blocks = 0 if o.cache_bytes > 0 else max(1, 4 * o.max_seq // o.block_size)
         if o.max_step_tokens <= 0:
             o.max_step_tokens = o.max_seq
         if o.max_batch <= 0:
@@ -69,8 +72,10 @@ class Sequence_:
         return self.cache.length
 
     def forward(self, tokens: Sequence[int]) -> torch.Tensor:
+        """The caller's own tensor: a replayed decode step writes its logits into a buffer
+        that the next step overwrites."""
         logits = self.engine.runner.run([StepEntry(self.cache, list(tokens), [len(tokens) - 1])])
-        return logits[0]
+        return logits[0].clone()
 
     def release(self) -> None:
         if not self.cache.closed:
@@ -96,6 +101,9 @@ class Engine:
             tensors = load_weights(model_dir, self.model.tensor_specs(), self.dtype, self.device)
             self.model.bind(tensors)
             del tensors
+            if opts.num_blocks <= 0:
+                opts.num_blocks = CacheManager.pages_within(self.model.cache_needs(), opts.block_size,
+                                                            self.dtype, opts.cache_bytes)
             self.cache = CacheManager(self.model.cache_needs(), opts.block_size, opts.num_blocks,
                                       max_requests=opts.max_batch, dtype=self.dtype, device=self.device)
         self.runner = StepRunner(self.model, self.cache, opts.max_step_tokens, opts.max_batch, opts.max_seq,

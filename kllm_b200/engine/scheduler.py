@@ -168,9 +168,12 @@ class Scheduler:
         if total > self.max_seq:
             raise ValueError(f"scheduler: prompt of {len(prompt)} tokens plus {max_new} new ones exceeds "
                              f"the sequence limit {self.max_seq}")
-        pages = -(-total // self.cache.page_size)
-        if pages > self.cache.num_pages:
-            raise ValueError(f"scheduler: the request needs {pages} pages, the pool has {self.cache.num_pages}")
+        # can it ever fit?  Asked of the cache manager group by group: a window group
+        # needs only its window's pages however long the request is
+        for g, pages in zip(self.cache.groups, self.cache.pages_ever_needed(total)):
+            if pages > g.pool.n:
+                raise ValueError(f"scheduler: the request needs {pages} pages of cache group {g.index}, "
+                                 f"its pool has {g.pool.n}")
         r = Request(rid=self._next_rid, prompt=prompt, max_new=int(max_new),
                     temperature=float(temperature), seed=int(seed), tokens=list(prompt))
         self._next_rid += 1

@@ -3,7 +3,13 @@
 params: ``hidden``, ``n_heads``, ``n_kv_heads``, ``head_dim``; optional ``window``
 (None: every earlier key is visible; W: the last W keys, the query's own included),
 ``scale`` (default 1/sqrt(head_dim)), ``position`` (a PartSpec of the position
-family, e.g. rotary; None for no position encoding).
+family, e.g. rotary; None for no position encoding), ``qk_transform`` (a PartSpec of
+the qk_transform family, None for Llama: something applied to the projected queries
+and keys before the position encoding, such as a norm per head or a bias; interface
+``tensor_specs()``, ``bind(tensors)``, ``apply(q, k, ctx, n_heads, n_kv_heads,
+head_dim)`` which changes q [n, H*hd] and k [n, G*hd] (None when the layer reads
+another layer's cache) in place; with one, a decode step takes the separate rotary
+and attention kernels, since the fused kernel rotates the raw projections itself).
 Tensors: ``<prefix>.{q,k,v,o}_proj.weight`` with shapes [H*hd, d], [G*hd, d],
 [G*hd, d], [d, H*hd]; no bias (reference backend/model.cu:1090-1104).  At bind time
 q, k and v are stacked into one [(H+2G)*hd, d] matrix so the three projections are
@@ -50,9 +56,15 @@ class PagedAttention:
         self.dtype = env.dtype
         pos = p.get("position")
         self.position = part_factory("position", pos.kind)(pos, env) if pos is not None else None
+        qt = p.get("qk_transform")
+        self.qk_transform = part_factory("qk_transform", qt.kind)(qt, env) if qt is not None else None
         self.w_qkv = None
         self.w_o = None
-        self._counters = None      # zeroed scratch of the fused decode kernel, which keeps it zero
+        # Zeroed scratch of the fused decode kernel, which leaves it zero.  A captured decode
+        # graph holds the address of the buffer it was recorded with, so a buffer is never
+        # freed once it has been used: a larger step gets a new one and the old ones stay.
+        self._counters = None
+        self._counters_kept = []
         self._after = []           # weights streamed right after this part (see set_prefetch_targets)
 
     def _names(self):
@@ -64,7 +76,8 @@ class PagedAttention:
                 TensorSpec(n["k"], (self.kv_dim, self.hidden)),
                 TensorSpec(n["v"], (self.kv_dim, self.hidden)),
                 TensorSpec(n["o"], (self.hidden, self.q_dim))] + \
-            (self.position.tensor_specs() if self.position else [])
+            (self.position.tensor_specs() if self.position else []) + \
+            (self.qk_transform.tensor_specs() if self.qk_transform else [])
 
     def bind(self, tensors):
         n = self._names()
@@ -72,6 +85,8 @@ class PagedAttention:
         self.w_o = tensors[n["o"]]
         if self.position:
             self.position.bind(tensors)
+        if self.qk_transform:
+            self.qk_transform.bind(tensors)
 
     def cache_need(self):
         return PagedKVNeed(self.n_kv, self.head_dim, self.window)
@@ -99,11 +114,16 @@ class PagedAttention:
         n = q.shape[0]
         group = self.n_heads // self.n_kv
         table = getattr(self.position, "full_rotary_table", lambda: None)() if self.position is not None else None
+        if self.qk_transform is not None:
+            self.qk_transform.apply(q, k if cache.writes else None, ctx, self.n_heads, self.n_kv, self.head_dim)
+            table = None          # the fused decode kernel takes the raw projections
         if (table is not None and cache.writes and ctx.all_single and self.dtype == torch.bfloat16 and group <= 16
                 and self.head_dim in kernels.TC_HEAD_DIMS and self.head_dim % 32 == 0):
             # decode: rotary encoding, cache write and attention in one kernel
             if self._counters is None or self._counters.numel() < n * self.n_kv:
-                self._counters = torch.zeros(max(64, n) * self.n_kv, dtype=torch.int32, device=q.device)
+                if self._counters is not None:
+                    self._counters_kept.append(self._counters)
+                self._counters = torch.zeros(max(256, 2 * n) * self.n_kv, dtype=torch.int32, device=q.device)
             attn = torch.empty((n, self.q_dim), dtype=self.dtype, device=q.device)
             kernels.attention_decode_fused(
                 attn, q, k, v, table, cache.k, cache.v, ctx.positions, None, cache.block_table,   # token t is request t

@@ -9,9 +9,12 @@ Interface of a block: ``forward(x, pending, ctx, cache) -> pending'``.  x is the
 float32 residual stream, updated in place; ``pending`` (float32 or model dtype, or
 None) is what is still to be added to x.
 
-A mixer or feed-forward may offer ``forward_residual`` (norm and residual sum inside
-its own kernels); the block tries it whenever nothing is pending and falls back to
-norm -> part -> pending otherwise.  Both routes compute the same sums.
+A mixer or feed-forward may offer ``forward_residual`` (the part applies the norm and
+adds its result into x itself, in whichever kernels fit the step's size); the block
+uses it whenever nothing is pending.  The built-in attention and gated feed-forward
+both offer it and always accept, so a Llama layer never hands anything on as
+``pending``.  A part without it, or one that returns False, gets norm -> ``forward``
+-> pending.  Both routes compute the same sums.
 
 Two more optional methods let a part's kernels warm L2 for the kernels after them:
 ``streamed_weights()`` (the matrices a part streams in a small step, in kernel order)

@@ -97,14 +97,14 @@ class StateNeed:
 # ---- registries -----------------------------------------------------------
 
 _KINDS: Dict[str, Dict[str, Callable]] = {
-    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {},
+    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "qk_transform": {}, "block": {},
     "embedding": {}, "head": {},
 }
 
 
 def register_part(family: str, kind: str, factory: Callable) -> None:
     """``factory(spec: PartSpec, env: BuildEnv)`` returns the part.  ``family`` is one
-    of mixer, feed_forward, norm, position, block, embedding, head."""
+    of mixer, feed_forward, norm, position, qk_transform, block, embedding, head."""
     if family not in _KINDS:
         raise KeyError(f"unknown part family {family!r}; families: {sorted(_KINDS)}")
     _KINDS[family][kind] = factory

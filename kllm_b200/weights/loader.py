@@ -6,11 +6,20 @@ by name and keeps it in the model's dtype: bfloat16 for serving, float32 for the
 integer tables become int32.  Files may hold F32, BF16 or F16 (the reference takes
 F32 only, engine/engine.go:140-141).  Everything that is wrong with the set of
 tensors is reported in ONE ``WeightError`` that lists the missing names, the
-unexpected names and the wrong shapes (the reference stops at the first missing
-name or element count, backend/model.cu:510-519, and ignores extras).
+unexpected names, the wrong shapes and the wrong dtypes (the reference stops at the
+first missing name or element count, backend/model.cu:510-519).
+
+Tensors that the model does not ask for are not a fault by themselves: the reference
+uploads whatever a file holds and uses what it needs (backend/model.cu:747-765; its
+converter drops the rest offline, tools/convert_hf.py:86-93), and older checkpoints
+carry tables such as ``rotary_emb.inv_freq``.  They are left unread, counted, and
+named in a ``UserWarning``; the error for a folder with real faults names them too,
+since a misspelt tensor shows up as one missing and one unexpected name.
+``strict=True`` makes them a fault of their own.
 """
 from __future__ import annotations
 
+import warnings
 from typing import Dict, Iterable, List, Tuple
 
 import torch
@@ -53,7 +62,9 @@ def stored_dtype(spec: TensorSpec, model_dtype: torch.dtype) -> torch.dtype:
     raise ValueError(f"tensor {spec.name}: unknown store {spec.store!r}")
 
 
-def check_names(files: ModelFiles, specs: Iterable[TensorSpec], model_dir: str) -> None:
+def check_names(files: ModelFiles, specs: Iterable[TensorSpec], model_dir: str, strict: bool = False) -> List[str]:
+    """Raise ONE ``WeightError`` for everything that is wrong; return the names the model
+    does not ask for (an error of their own only when ``strict``)."""
     specs = list(specs)
     by_name = {s.name: s for s in specs}
     have = set(files.names())
@@ -67,17 +78,24 @@ def check_names(files: ModelFiles, specs: Iterable[TensorSpec], model_dir: str) 
         ok = _INTS if by_name[name].store == "int32" else _FLOATS
         if e.dtype not in ok:
             wrong_dtype.append((name, str(e.dtype)))
-    if missing or unexpected or wrong_shape or wrong_dtype:
+    if missing or wrong_shape or wrong_dtype or (strict and unexpected):
         raise WeightError(model_dir, missing, unexpected, wrong_shape, wrong_dtype)
+    return unexpected
 
 
 def load_weights(model_dir: str, specs: Iterable[TensorSpec], model_dtype: torch.dtype,
-                 device) -> Dict[str, torch.Tensor]:
-    """name -> tensor on ``device`` for every expected tensor that the files hold."""
+                 device, strict: bool = False) -> Dict[str, torch.Tensor]:
+    """name -> tensor on ``device`` for every expected tensor that the files hold.
+    Tensors that no part asked for stay unread; a warning counts and names them
+    (``strict``: they are an error)."""
     specs = list(specs)
     out: Dict[str, torch.Tensor] = {}
     with ModelFiles(model_dir) as files:
-        check_names(files, specs, model_dir)
+        extra = check_names(files, specs, model_dir, strict)
+        if extra:
+            shown = ", ".join(extra[:8]) + (", ..." if len(extra) > 8 else "")
+            warnings.warn(f"{model_dir}: {len(extra)} tensor(s) that the model does not use were ignored: {shown}",
+                          stacklevel=2)
         have = set(files.names())
         for s in specs:
             if s.name not in have:

@@ -30,9 +30,13 @@ def pytest_collection_modifyitems(config, items):
 
 def pytest_terminal_summary(terminalreporter):
     try:
-        from helpers import WORST
+        from helpers import CROSS, WORST
     except Exception:
         return
+    for dtype, (diff, what) in sorted(CROSS.items()):
+        terminalreporter.write_line(f"largest difference between two ways of cutting the same request, {dtype}: "
+                                    f"{diff:.2e} of the largest logit"
+                                    + (f" = {diff / 2 ** -24:.0f} float32 ulp" if dtype == "float32" else "") + f" ({what})")
     for dtype, (ratio, what) in sorted(WORST.items()):
         terminalreporter.write_line(f"largest error / tolerance against the plain implementation, {dtype}: "
                                     f"{ratio:.2f} ({what})")

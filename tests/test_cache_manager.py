@@ -79,6 +79,25 @@ def test_reservation_is_all_or_nothing_over_groups():
     m.audit()
 
 
+def test_pool_size_from_a_byte_budget_over_two_groups():
+    """pages = budget / bytes of one page in every pool: two layers that keep all keys
+    (2 kv heads of 16), one window layer with another shape (1 kv head of 32), bfloat16,
+    pages of 4 tokens; a fixed count ran out of memory in the reference
+    (docs/JOURNAL.md:364-367)."""
+    other = PagedKVNeed(1, 32, window=6)
+    needs = [FULL, other, FULL, StateNeed((3,))]
+    per = (2 * 2 * 2 * 4 * 16 + 1 * 2 * 1 * 4 * 32) * 2          # layers * (k, v) * heads * slots * dim * bytes
+    assert CacheManager(needs, 4, 1, 2, dtype=torch.bfloat16, allocate=False).bytes_per_page() == per
+    assert CacheManager.pages_within(needs, 4, torch.bfloat16, 10 * per + per - 1) == 10
+    assert CacheManager.pages_within(needs, 4, torch.float32, 10 * per) == 5
+    with pytest.raises(ValueError, match="holds no page"):
+        CacheManager.pages_within(needs, 4, torch.bfloat16, per - 1)
+    assert CacheManager.pages_within([StateNeed((3,)), None], 4, torch.bfloat16, 100) == 1
+    m = CacheManager(needs, 4, CacheManager.pages_within(needs, 4, torch.bfloat16, 3 * per), 2,
+                     dtype=torch.bfloat16, allocate=True)
+    assert sum(g.storage.numel() * g.storage.element_size() for g in m.groups) == 3 * per
+
+
 def test_window_group_gives_pages_back_when_the_window_has_passed():
     window = PagedKVNeed(1, 16, window=5)
     m = manager(needs=[FULL, window], page_size=4, num_pages=6)

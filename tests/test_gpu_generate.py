@@ -194,3 +194,60 @@ def test_command_line(tmp_path):
                          capture_output=True, text=True, timeout=300)
     assert rnd.returncode == 0, rnd.stderr
     assert os.path.exists(tmp_path / "r" / "model.safetensors") and "generated: [" in rnd.stdout
+
+
+def test_a_captured_decode_graph_survives_a_larger_batch(tmp_path):
+    """Decode graphs hold the addresses of the buffers they were recorded with.  A step of
+    2 requests is captured, then a step of 70 requests runs (more tokens than any scratch
+    buffer sized for the small step), then the 2-request graph is replayed: its logits must
+    still be those of the plain implementation, and the large step's too."""
+    from kllm_b200.engine import Engine, Options, StepEntry
+    cfg, w = make_weights("B", "bfloat16")
+    d = write_model_dir(str(tmp_path / "m"), cfg, w)
+    eng = Engine(d, Options(dtype="bfloat16", max_seq=64, block_size=16, num_blocks=4 * 72, max_batch=72,
+                            max_step_tokens=512))
+    seqs = prompts_for(cfg, [40, 23] + [5] * 70, seed=11)
+    want = [plain_logits(w, cfg, ids, "bfloat16") for ids in seqs[:3]]
+    small = [eng.cache.open() for _ in range(2)]
+    eng.step([StepEntry(r, ids[:-4], []) for r, ids in zip(small, seqs)])
+    rows = {0: [], 1: []}
+
+    def decode_small(k):
+        out = eng.step([StepEntry(r, [ids[len(ids) - 4 + k]], [0]) for r, ids in zip(small, seqs)]).cpu().numpy()
+        for i in range(2):
+            rows[i].append(out[i])
+
+    decode_small(0)                     # eager run and capture of the 2-request step
+    decode_small(1)                     # replay
+    assert 2 in eng.runner.graphs and eng.runner.graphs[2].graph is not None
+    many = [eng.cache.open() for _ in range(70)]
+    eng.step([StepEntry(r, ids[:-1], []) for r, ids in zip(many[:35], seqs[2:37])])
+    eng.step([StepEntry(r, ids[:-1], []) for r, ids in zip(many[35:], seqs[37:])])
+    big = eng.step([StepEntry(r, ids[-1:], [0]) for r, ids in zip(many, seqs[2:])]).cpu().numpy()
+    assert_close(big[0], want[2][-1], "bfloat16", "first request of the 70-request step")
+    decode_small(2)                     # the old graph again, after the scratch grew
+    decode_small(3)
+    for i in range(2):
+        assert_close(np.stack(rows[i]), want[i][-4:], "bfloat16", f"request {i} decoded by the replayed graph")
+    for r in small + many:
+        eng.cache.close(r)
+    eng.cache.audit()
+    eng.close()
+
+
+def test_sequence_logits_stay_valid_over_the_next_step(tmp_path):
+    """``Sequence_.forward`` hands out the caller's own tensor: the logits of step t are
+    unchanged after step t + 1 has replayed the same decode graph."""
+    from kllm_b200.engine import Engine, Options
+    cfg, w = make_weights("A", "float32")
+    d = write_model_dir(str(tmp_path / "m"), cfg, w)
+    eng = Engine(d, Options(dtype="float32", max_seq=64))
+    ids = prompts_for(cfg, [12], seed=2)[0]
+    want = plain_logits(w, cfg, ids, "float32")
+    seq = eng.new_sequence()
+    seq.forward(ids[:8])
+    kept = [seq.forward([t]) for t in ids[8:]]        # four single-token steps: eager, capture, replays
+    for i, row in enumerate(kept):
+        assert_close(row.cpu().numpy(), want[8 + i], "float32", f"kept logits of step {i}")
+    seq.release()
+    eng.close()

@@ -75,6 +75,24 @@ def test_add_rmsnorm_of_many_rows(d):
     close(out, plain.rmsnorm(x0.astype(np.float64) + res, gain, eps), "bfloat16", "norm alone")
 
 
+@pytest.mark.parametrize("d", [2048, 4096, 200])
+def test_add_rmsnorm_of_a_row_does_not_depend_on_the_number_of_rows(d):
+    """The same row normalised alone, among 511 and among 512 rows: bit-equal, since the
+    kernel and with it the order of the sum are chosen by the width alone."""
+    from kllm_b200 import kernels
+    rng = np.random.default_rng(d + 1)
+    x0 = (rng.standard_normal((512, d)) * 2).astype(np.float32)
+    res = rng.standard_normal((512, d)).astype(np.float32)
+    gain = dev((1 + 0.2 * rng.standard_normal(d)).astype(np.float32))
+    outs = []
+    for n in (1, 511, 512):
+        x, out = dev(x0[:n]), torch.empty((n, d), dtype=torch.bfloat16, device="cuda")
+        kernels.add_rmsnorm(x, dev(res[:n]), out, gain, 1e-5)
+        outs.append((x[0].clone(), out[0].clone()))
+    for x_row, out_row in outs[1:]:
+        assert torch.equal(x_row, outs[0][0]) and torch.equal(out_row, outs[0][1])
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("d", [100, 2048 + 16, 7])
 def test_add_rmsnorm(dtype, d):
@@ -297,8 +315,24 @@ def test_fused_decode_attention_rotates_appends_and_merges(H, G, hd, page, split
     """Against the separate kernels' math: rotate q and the new k, store k and v at the
     token's slot, attend over everything.  Run twice on one counter buffer: with the
     token-to-request table, then without it (token t is request t)."""
+    fused_decode_case(H, G, hd, page, splits, None)
+
+
+@pytest.mark.parametrize("H,G,hd,page", [(8, 2, 64, 16), (3, 1, 32, 5), (32, 4, 128, 64)])
+@pytest.mark.parametrize("splits", [1, 3, 8])
+@pytest.mark.parametrize("window", [1, 5, 64, 65, 200])
+def test_fused_decode_attention_with_a_window(H, G, hd, page, splits, window):
+    """The same with a window: several key ranges inside the window, window edges that
+    cross 64-key tiles and pages, a first range that does not start at a tile's edge.
+    The pages that the window has passed are -1 in the block table, as the cache manager
+    leaves them, and every cached key and value before the window is NaN: neither may be
+    read."""
+    fused_decode_case(H, G, hd, page, splits, window)
+
+
+def fused_decode_case(H, G, hd, page, splits, window):
     from kllm_b200 import kernels
-    rng = np.random.default_rng(H * hd + splits)
+    rng = np.random.default_rng(H * hd + splits + (window or 0))
     lengths = [70, 1, 33, 129, 300]
     theta, max_pos = 1e4, 320
     j = np.arange(hd // 2, dtype=np.float64)
@@ -318,19 +352,27 @@ def test_fused_decode_attention_rotates_appends_and_merges(H, G, hd, page, split
             k_all = np.concatenate([kq[:-1].reshape(L - 1, G * hd), k_last_rot])
             # attention of the single query over all L keys (causal mask is the loop bound)
             sc_q = np.concatenate([np.zeros((L - 1, H * hd)), q_rot])
-            full = plain.attention(sc_q, k_all, vq.reshape(L, G * hd), H, G, hd, rnd_p=plain.round_act_bf16)
+            full = plain.attention(sc_q, k_all, vq.reshape(L, G * hd), H, G, hd, window=window,
+                                   rnd_p=plain.round_act_bf16)
             want.append(full[-1:])
             hist_k = k.copy(); hist_k[-1] = np.nan          # the slot of the new token holds nothing yet
             hist_v = v.copy(); hist_v[-1] = np.nan
+            if window:
+                hist_k[:max(0, L - window)] = np.nan        # what the window has passed is never read
+                hist_v[:max(0, L - window)] = np.nan
             ks.append(hist_k); vs.append(hist_v)
             qraw.append(q.reshape(1, H * hd)); knew.append(k[-1:].reshape(1, G * hd)); vnew.append(v[-1:].reshape(1, G * hd))
         kc, vc, table = paged(ks, vs, page, sum(-(-L // page) for L in lengths) + 3, rng, "bfloat16", lengths)
+        if window:
+            # pages given back at the commit before this step (cache/manager.py: commit)
+            dead = torch.tensor([[j < max(0, L - window) // page for j in range(table.shape[1])] for L in lengths])
+            table = torch.where(dead.cuda(), torch.full_like(table, -1), table)
         q_t, k_t, v_t = (dev(np.concatenate(a), torch.bfloat16) for a in (qraw, knew, vnew))
         out = torch.empty_like(q_t)
         pos = dev(np.array([L - 1 for L in lengths], np.int32))
         req = dev(np.arange(len(lengths), dtype=np.int32))
         kernels.attention_decode_fused(out, q_t, k_t, v_t, cos_sin, kc, vc, pos, req if rep == 0 else None, table,
-                                       counters, H, G, hd, 0, 1.0 / math.sqrt(hd), splits)
+                                       counters, H, G, hd, window or 0, 1.0 / math.sqrt(hd), splits)
         assert not torch.isnan(out.float()).any()
         close(out, np.concatenate(want), "bfloat16", f"attention, run {rep}")
         assert int(counters.abs().sum()) == 0, "the counters must be zero again"

@@ -87,6 +87,19 @@ def test_feed_forward_part(dtype):
     want = plain.swiglu(stored(x, dtype), ws["ff.gate_proj.weight"], ws["ff.up_proj.weight"],
                         ws["ff.down_proj.weight"], rnd)
     close(out, want, dtype)
+    # the route generation takes: the part reads the float32 residual stream, applies the
+    # norm itself and adds its result (7 rows: weight-streaming products in bfloat16;
+    # 40 rows: library products); both must equal norm -> forward -> sum
+    norm = part_factory("norm", "rmsnorm")(PartSpec("rmsnorm", "n", {"width": d, "eps": 1e-5}), env_for(dtype, d))
+    gain = (1 + 0.2 * rng.standard_normal(d)).astype(np.float32)
+    bind(norm, {"n.weight": gain}, dtype)
+    for n in (7, 40):
+        x0 = rng.standard_normal((n, d)).astype(np.float32)
+        xr = torch.from_numpy(x0).cuda()
+        assert part.forward_residual(xr, norm, None) is True
+        xn = rnd(plain.rmsnorm(x0, gain, 1e-5))
+        close(xr, x0 + plain.swiglu(xn, ws["ff.gate_proj.weight"], ws["ff.up_proj.weight"], ws["ff.down_proj.weight"], rnd),
+              dtype, f"residual stream after forward_residual, {n} rows")
     with pytest.raises(ValueError, match="activation"):
         part_factory("feed_forward", "gated_mlp")(
             PartSpec("gated_mlp", "ff", {"hidden": d, "intermediate": f, "activation": "relu"}), env_for(dtype, d))
@@ -129,6 +142,27 @@ def test_attention_part_in_two_portions(dtype, window):
     close(torch.cat(outs), want, dtype)
     if window:
         assert req.tables[0][0] == -1          # the window has passed the first page
+    # the route generation takes: the part reads the float32 residual stream, applies the
+    # norm in its first kernel and adds its result; a portion of 13 tokens (library
+    # products), then 8 single tokens (weight-streaming products and, in bfloat16 with a
+    # head size that is a multiple of 32, the fused decode kernel; here the separate ones)
+    norm = part_factory("norm", "rmsnorm")(PartSpec("rmsnorm", "n", {"width": d, "eps": 1e-5}), env_for(dtype, d))
+    gain = (1 + 0.2 * rng.standard_normal(d)).astype(np.float32)
+    bind(norm, {"n.weight": gain}, dtype)
+    cache.close(req)
+    req2 = cache.open()
+    xs, start = torch.from_numpy(x).cuda().clone(), 0
+    for cnt in [13] + [1] * 8:
+        cache.reserve(req2, cnt)
+        ctx = one_request_context(cnt, start)
+        table = torch.full((1, 8), -1, dtype=torch.int32)
+        table[0, :len(req2.tables[0])] = torch.tensor(req2.tables[0])
+        lc = cache.layer_caches({0: table.cuda()})[0]
+        assert part.forward_residual(xs[start:start + cnt], norm, ctx, lc) is True
+        cache.commit(req2, cnt)
+        start += cnt
+    xn = rnd(plain.rmsnorm(x, gain, 1e-5))
+    close(xs, x + plain.attention_block(xn, ws, "L", cfg, np.arange(n), rnd), dtype, "forward_residual")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -256,8 +290,11 @@ def test_rotary_part_rotates_and_stores(dtype, rotary_dim):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("n", [3, 40])
 def test_block_part_both_routes(dtype, n):
-    """A whole pre-norm block against the plain layer: n = 3 takes the fused route in
-    bfloat16 (norm and residual sum inside the products), n = 40 the general one."""
+    """A whole pre-norm block against the plain layer.  Both sizes go through the parts'
+    ``forward_residual`` as in generation: n = 3 with the norm and the residual sum inside
+    weight-streaming products (bfloat16), n = 40 with the norm kernel, library products and
+    the sum in the last product's epilogue.  The route norm -> ``forward`` -> pending is
+    what parts without ``forward_residual`` get (the toy mixers below)."""
     from kllm_b200.cache import CacheManager
     from kllm_b200.parts.spec import BlockSpec, PartSpec, part_factory
     rng = np.random.default_rng(8)
@@ -288,8 +325,7 @@ def test_block_part_both_routes(dtype, n):
     rnd = plain.round_act_bf16 if dtype == "bfloat16" else (lambda a: a)
     want = plain.decoder_layer(x0.astype(np.float64), ws, 0, plain.normalise_config(cfg), np.arange(n), rnd)
     close(got, want, dtype, f"block output, {n} tokens")
-    if dtype == "bfloat16" and n == 3:
-        assert pending is None, "a small bfloat16 step is expected to take the fused route"
+    assert pending is None, "both parts add into the residual stream themselves"
 
 
 # ---- a toy architecture defined in the test -----------------------------------
@@ -601,3 +637,90 @@ def test_toy_architecture_with_routed_experts_and_its_own_position_encoding(tmp_
     got += [eng.step([StepEntry(b, ids[t:t + 1], [0])]) for t in range(30, 37)]       # one by one
     close(torch.cat(got), want, dtype, "portions, then token by token")
     eng.close()
+
+
+# ---- a transform of q and k before the position encoding, defined in the test -----------
+
+class HeadRMSNorm:
+    """q and k normalised per head with a learned gain each (a "qk-norm"): a part of the
+    qk_transform family, registered from here.  Plain torch on the strided views."""
+
+    def __init__(self, spec, env):
+        self.prefix, self.hd, self.eps = spec.prefix, spec.params["head_dim"], spec.params["eps"]
+
+    def tensor_specs(self):
+        from kllm_b200.parts.spec import TensorSpec
+        return [TensorSpec(f"{self.prefix}.q_norm.weight", (self.hd,), store="float32", init="gain"),
+                TensorSpec(f"{self.prefix}.k_norm.weight", (self.hd,), store="float32", init="gain")]
+
+    def bind(self, tensors):
+        self.gq, self.gk = tensors[f"{self.prefix}.q_norm.weight"], tensors[f"{self.prefix}.k_norm.weight"]
+
+    def apply(self, q, k, ctx, n_heads, n_kv_heads, head_dim):
+        for t, g, heads in ((q, self.gq, n_heads), (k, self.gk, n_kv_heads)):
+            if t is None:
+                continue
+            v = t.float().reshape(t.shape[0], heads, head_dim)
+            v = v * torch.rsqrt((v * v).mean(-1, keepdim=True) + self.eps) * g
+            t.copy_(v.reshape(t.shape[0], heads * head_dim).to(t.dtype))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_part_with_a_qk_transform_registered_from_outside(dtype):
+    """The attention part with a per-head norm on q and k between the projection and the
+    rotation: a portion of 9 tokens, then 6 single tokens.  Head size 32 in bfloat16 would
+    take the fused decode kernel, which rotates the raw projections itself; with a
+    transform the part must take the separate kernels, and the answers must be the plain
+    formula's with the norm in place."""
+    from kllm_b200 import kernels
+    from kllm_b200.cache import CacheManager
+    from kllm_b200.parts.spec import PartSpec, part_factory, register_part
+    register_part("qk_transform", "toy_head_rmsnorm", HeadRMSNorm)
+    rng = np.random.default_rng(21)
+    d, H, G, hd, n, theta, eps = 64, 4, 2, 32, 15, 300.0, 1e-4
+    spec = PartSpec("paged_attention", "a", {
+        "hidden": d, "n_heads": H, "n_kv_heads": G, "head_dim": hd,
+        "position": PartSpec("rotary", "", {"head_dim": hd, "theta": theta}),
+        "qk_transform": PartSpec("toy_head_rmsnorm", "a", {"head_dim": hd, "eps": eps})})
+    part = part_factory("mixer", "paged_attention")(spec, env_for(dtype, d))
+    assert sorted(s.name for s in part.tensor_specs())[:2] == ["a.k_norm.weight", "a.k_proj.weight"]
+    w = {f"a.{k}_proj.weight": (rng.standard_normal(s) * 0.4).astype(np.float32)
+         for k, s in (("q", (H * hd, d)), ("k", (G * hd, d)), ("v", (G * hd, d)), ("o", (d, H * hd)))}
+    w["a.q_norm.weight"] = (1 + 0.3 * rng.standard_normal(hd)).astype(np.float32)
+    w["a.k_norm.weight"] = (1 + 0.3 * rng.standard_normal(hd)).astype(np.float32)
+    bind(part, w, dtype)
+    norm = part_factory("norm", "rmsnorm")(PartSpec("rmsnorm", "n", {"width": d, "eps": 1e-5}), env_for(dtype, d))
+    gain = (1 + 0.2 * rng.standard_normal(d)).astype(np.float32)
+    bind(norm, {"n.weight": gain}, dtype)
+    cache = CacheManager([part.cache_need()], page_size=4, num_pages=6, max_requests=1, dtype=DT[dtype], device="cuda")
+    req = cache.open()
+    x = rng.standard_normal((n, d)).astype(np.float32)
+    xs, start = torch.from_numpy(x).cuda().clone(), 0
+    calls, real = [], kernels.attention_decode_fused
+    kernels.attention_decode_fused = lambda *a, **k: calls.append(1) or real(*a, **k)
+    try:
+        for cnt in [9] + [1] * 6:
+            cache.reserve(req, cnt)
+            ctx = one_request_context(cnt, start)
+            table = torch.full((1, 4), -1, dtype=torch.int32)
+            table[0, :len(req.tables[0])] = torch.tensor(req.tables[0])
+            assert part.forward_residual(xs[start:start + cnt], norm, ctx, cache.layer_caches({0: table.cuda()})[0])
+            cache.commit(req, cnt)
+            start += cnt
+    finally:
+        kernels.attention_decode_fused = real
+    assert not calls, "the fused decode kernel cannot apply a transform between projection and rotation"
+    rnd = plain.round_act_bf16 if dtype == "bfloat16" else (lambda a: a)
+    ws = {k: stored(v, dtype) for k, v in w.items() if v.ndim == 2}
+    xn = rnd(plain.rmsnorm(x, gain, 1e-5))
+
+    def head_norm(t, g, heads):
+        v = t.reshape(n, heads, hd)
+        return rnd((v / np.sqrt((v * v).mean(-1, keepdims=True) + eps) * g).reshape(n, heads * hd))
+
+    q = head_norm(rnd(xn @ ws["a.q_proj.weight"].T), w["a.q_norm.weight"].astype(np.float64), H)
+    k = head_norm(rnd(xn @ ws["a.k_proj.weight"].T), w["a.k_norm.weight"].astype(np.float64), G)
+    v = rnd(xn @ ws["a.v_proj.weight"].T)
+    q, k = rnd(plain.rope(q, np.arange(n), H, hd, theta)), rnd(plain.rope(k, np.arange(n), G, hd, theta))
+    att = rnd(plain.attention(q, k, v, H, G, hd, rnd_p=None if dtype == "float32" else rnd))
+    close(xs, x + att @ ws["a.o_proj.weight"].T, dtype, "attention with a q/k norm per head")

@@ -302,3 +302,27 @@ def test_pipelined_loop_under_random_load_and_few_pages(seed):
         assert r.generated == want, r.rid
     cache.audit()
     assert cache.free_pages() == [cache.num_pages] and not s._inflight
+
+
+def test_admission_asks_each_group_what_a_request_can_ever_need():
+    """A model whose layers all read a window of 6 keys: a request of 100 tokens fits a pool
+    of 4 pages of 4 tokens (3 pages for the window's reach plus the page being written),
+    although 100 tokens are 25 pages; a group that keeps every key still refuses it."""
+    window = [PagedKVNeed(2, 16, window=6)]
+    cache = CacheManager(window, 4, 4, max_requests=2, allocate=False)
+    assert cache.pages_ever_needed(100) == [3] and cache.pages_ever_needed(5) == [2]
+    ex = FakeExecutor(cache, 8)
+    s = Scheduler(cache=cache, execute=ex, max_batch=2, max_step_tokens=8, max_seq=256, eos_token_ids=[EOS])
+    prompt = [(7 * i) % 90 for i in range(60)]
+    r = s.submit(prompt, 40)
+    s.run()
+    assert r.status == "finished" and r.generated == solo(prompt, 40)
+    assert cache.free_pages() == [4] and max(n for b in ex.batches for _, n, _ in b) <= 8
+    both = CacheManager(window + [PagedKVNeed(2, 16)], 4, 4, max_requests=2, allocate=False)
+    assert both.pages_ever_needed(100) == [3, 25]
+    s2 = Scheduler(cache=both, execute=FakeExecutor(both, 8), max_batch=2, max_step_tokens=8, max_seq=256)
+    with pytest.raises(ValueError, match="25 pages of cache group 1"):
+        s2.submit(prompt, 40)
+    s2.submit(prompt[:10], 6)               # 16 tokens: 4 pages of the group that keeps every key
+    s2.run()
+    assert both.free_pages() == [4, 4]

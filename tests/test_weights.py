@@ -109,6 +109,25 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
         assert needle in msg
 
 
+def test_extra_tensors_are_left_unread_counted_and_named(tmp_path):
+    """A folder that holds more than the model asks for (an older checkpoint's
+    ``rotary_emb.inv_freq``, a tensor of another head) still loads: the reference uploads
+    everything and uses what it needs (backend/model.cu:747-765).  The extras are named in
+    a warning with their count; ``strict=True`` refuses them."""
+    cfg, w = make_weights("A")
+    w = dict(w)
+    w["model.layers.0.self_attn.rotary_emb.inv_freq"] = np.ones(8, dtype=np.float32)
+    w["score.weight"] = np.ones((2, 64), dtype=np.float32)
+    d = write_model_dir(str(tmp_path / "m"), cfg, w)
+    with pytest.warns(UserWarning, match=r"2 tensor\(s\).*inv_freq.*score\.weight"):
+        t = load_weights(d, model_specs(cfg), torch.float32, "cpu")
+    assert "score.weight" not in t and len(t) == len(w) - 2
+    with pytest.raises(WeightError) as e:
+        load_weights(d, model_specs(cfg), torch.float32, "cpu", strict=True)
+    assert e.value.unexpected == ["model.layers.0.self_attn.rotary_emb.inv_freq", "score.weight"]
+    assert not e.value.missing and not e.value.wrong_shape
+
+
 def test_dtype_rules(tmp_path):
     cfg, w = make_weights("A")
     d = write_model_dir(str(tmp_path / "f32"), cfg, w)

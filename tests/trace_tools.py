@@ -47,27 +47,49 @@ class TraceBuilder:
 
 
 def run_trace(model_dir: str, dtype: str, builder: TraceBuilder, out_dir: str, vocab: int,
-              max_tokens: int = 0, timeout: float = 600.0):
+              max_tokens: int = 0, timeout: float = 600.0, trace_file: str = ""):
     """Run bin/trace_run on the trace, feeding a step only after the previous
-    ``done`` line.  Returns {(rid, position): logits row}."""
+    ``done`` line (or handing it the whole trace as ``--trace FILE``).  Returns
+    {(rid, position): logits row}, read from the ``step_<k>.npy`` files by the program's
+    own ``index.json``; the raw ``<k>.f32`` files must hold the same numbers, and the
+    index must name the rows that the trace asked for."""
     cmd = [sys.executable, TRACE_RUN, "--model", model_dir, "--dtype", dtype, "--out", out_dir,
            "--max-tokens", str(max_tokens or builder.peak)]
-    proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, bufsize=1)
-    try:
-        for rec in builder.steps:
-            proc.stdin.write(json.dumps(rec) + "\n")
-            proc.stdin.flush()
-            line = proc.stdout.readline()
-            assert line.strip() == f"done {rec['step']}", f"trace_run answered {line!r} to step {rec['step']}"
-        proc.stdin.close()
-        rc = proc.wait(timeout=timeout)
-    finally:
-        if proc.poll() is None:
-            proc.kill()
-    assert rc == 0, f"trace_run exited with {rc}"
+    if trace_file:
+        with open(trace_file, "w") as f:
+            f.writelines(json.dumps(rec) + "\n" for rec in builder.steps)
+        done = subprocess.run(cmd + ["--trace", trace_file], stdin=subprocess.DEVNULL, capture_output=True,
+                              text=True, timeout=timeout)
+        assert done.returncode == 0, done.stderr[-2000:]
+        assert done.stdout.split("\n")[:-1] == [f"done {rec['step']}" for rec in builder.steps]
+    else:
+        proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, bufsize=1)
+        try:
+            for rec in builder.steps:
+                proc.stdin.write(json.dumps(rec) + "\n")
+                proc.stdin.flush()
+                line = proc.stdout.readline()
+                assert line.strip() == f"done {rec['step']}", f"trace_run answered {line!r} to step {rec['step']}"
+            proc.stdin.close()
+            rc = proc.wait(timeout=timeout)
+        finally:
+            if proc.poll() is None:
+                proc.kill()
+        assert rc == 0, f"trace_run exited with {rc}"
+    with open(os.path.join(out_dir, "index.json")) as f:
+        index = json.load(f)
+    assert index["vocab"] == vocab
+    listed = {}
+    for r in index["rows"]:
+        listed.setdefault(r["step"], []).append((r["row"], r["request"], r["position"]))
+    assert sorted(listed) == sorted(builder.rows), "the index lists other steps than the trace wanted logits in"
     out = {}
     for k, rows in builder.rows.items():
-        arr = np.fromfile(os.path.join(out_dir, f"{k}.f32"), dtype="<f4").reshape(len(rows), vocab)
+        assert [(rid, pos) for _, rid, pos in sorted(listed[k])] == rows, f"index of step {k}"
+        arr = np.load(os.path.join(out_dir, f"step_{k}.npy"))
+        assert arr.dtype == np.dtype("<f4") and arr.shape == (len(rows), vocab) and arr.flags.c_contiguous
+        raw = np.fromfile(os.path.join(out_dir, f"{k}.f32"), dtype="<f4").reshape(len(rows), vocab)
+        assert np.array_equal(raw, arr, equal_nan=True)
         for i, key in enumerate(rows):
             assert key not in out, f"row {key} written twice"
             out[key] = arr[i]
