@@ -16,7 +16,14 @@ step of the whole batch.  One JSON line is printed:
              bfloat16 tensor peak that its flops reach
   roofline   the decode step against HBM bandwidth: every weight once plus the
              cache of the live requests, over the step's time
-  points     decode at batch 1 and at batch 64
+  points     decode at batch 1 and at batch 64, and BASELINE.json's stated decode
+             workload: batch 8, prompts of 512 tokens, 256 tokens generated each, all of
+             them timed
+  points_fp32  the float32 path of this engine on the same model (decode at batch 8,
+             the 2048-token prompt): the reference computes in float32 only, so this is
+             the arm to hold against it at equal precision
+  spread     the K-step region is timed several times over; ``value`` is the median,
+             ``spread`` the fastest and slowest repeat
 
 Weights are random and token ids synthetic (there is neither a checkpoint nor a
 dataset here).  Every decode step reads about 2.4 GB, far more than the 126 MB of
@@ -26,7 +33,10 @@ its C ABI for the same metric and sizes, or says why it cannot.
 
 ``--shape`` picks the layer sizes of another Llama (with ``--layers`` for fewer of
 them) and ``--prefill-tokens`` another prompt length: measurements at further sizes,
-printed in the same form but not the bench line.
+printed in the same form but not the bench line; their weights are drawn on the device.
+``--workload llama2-7b-mixed`` runs BASELINE.json's continuous-batching workload (32
+requests, prompt lengths uniform in [128, 3072], 128 new tokens each) through the
+scheduler and prints a record of its own.
 """
 from __future__ import annotations
 
@@ -199,6 +209,11 @@ def print_timeline(rows, dev_ms):
         prev_end = r["end"]
 
 
+def median(xs):
+    xs = sorted(xs)
+    return xs[len(xs) // 2] if len(xs) % 2 else 0.5 * (xs[len(xs) // 2 - 1] + xs[len(xs) // 2])
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -210,8 +225,11 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0: all)")
     ap.add_argument("--shape", default="tinyllama-1.1b", choices=sorted(SHAPES),
                     help="layer sizes; other than the default it is a measurement at further sizes, not the bench line")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
+                    help="float32: the whole line is measured on the true 32-bit path (not the bench line)")
+    ap.add_argument("--repeats", type=int, default=0, help="how often the K-step region is timed (0: 5, or 3 for K > 40)")
     ap.add_argument("--prefill-tokens", type=int, default=2048, help="length of the timed prompt")
-    ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and the prefill")
+    ap.add_argument("--no-points", action="store_true", help="skip the further points and the prefill")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="decode: the batch's decode run alone; prefill: the 2048-token prompt alone (partial "
                          "records for profiling small cases, not the bench line)")
@@ -219,6 +237,9 @@ def main():
     ap.add_argument("--timeline", action="store_true",
                     help="decode run with the instrumented kernel builds; prints where the last step's time went, "
                          "kernel by kernel (not a bench line)")
+    ap.add_argument("--workload", default="", choices=["", "llama2-7b-mixed"],
+                    help="llama2-7b-mixed: 32 requests, prompts uniform in [128, 3072], 128 new tokens each, through "
+                         "the scheduler (a record of its own, not the bench line)")
     args = ap.parse_args()
     if args.timeline:
         os.environ["KLLM_B200_TIMELINE"] = "1"
@@ -235,8 +256,11 @@ def main():
 
     import torch
     from kllm_b200 import kernels
-    from kllm_b200.engine import Engine, Options, Scheduler
+    from kllm_b200.engine import Engine, Options, Scheduler, StepEntry
     from kllm_b200.weights import write_random_model
+
+    if args.workload:
+        return mixed_workload(args)
 
     cfg = dict(SHAPES[args.shape])
     cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], args.context, args.prefill_tokens)
@@ -244,38 +268,54 @@ def main():
     layers = args.layers or layers_full
     cfg["num_hidden_layers"] = layers
     B, ctx, K, W = args.batch, args.context, args.steps, args.warmup
+    R = args.repeats or (5 if K <= 40 else 3)
     shape_name = {"tinyllama-1.1b": "TinyLlama 1.1B shape", "llama2-7b": "Llama-2 7B shape",
                   "llama3-8b": "Llama-3 8B shape"}[args.shape]
     pk = peaks()
-    tmp = tempfile.mkdtemp(prefix="kllm_b200_bench_")
-    try:
+    page = 64
+    default_line = args.shape == "tinyllama-1.1b" and args.dtype == "bfloat16"
+    full = default_line and not args.no_points            # the further points of the bench line
+    max_b = max(B, 64 if full else B)
+
+    def options(dtype, batch_limit):
+        pages = max(batch_limit * (-(-ctx // page)), -(-args.prefill_tokens // page)) + 8
+        return Options(dtype=dtype, max_seq=max(ctx, args.prefill_tokens), block_size=page, num_blocks=pages,
+                       max_batch=batch_limit, max_step_tokens=max(args.prefill_tokens, batch_limit),
+                       cuda_graphs=not args.no_graphs)
+
+    tmp = None
+    if args.shape == "tinyllama-1.1b":
+        # the default model goes through the random-weights mode's folder and the loader
+        tmp = tempfile.mkdtemp(prefix="kllm_b200_bench_")
         t_w = time.time()
         write_random_model(tmp, cfg, seed=4, dtype=torch.bfloat16)
         print(f"[bench] random weights written in {time.time() - t_w:.1f} s", file=sys.stderr, flush=True)
-        page = 64
-        max_b = max(B, 64 if not args.no_points else B)
-        pages = max(max_b * (-(-ctx // page)), -(-args.prefill_tokens // page)) + 8
-        eng = Engine(tmp, Options(dtype="bfloat16", max_seq=max(ctx, args.prefill_tokens), block_size=page, num_blocks=pages,
-                                  max_batch=max_b, max_step_tokens=max(args.prefill_tokens, max_b),
-                                  cuda_graphs=not args.no_graphs))
-    finally:
-        shutil.rmtree(tmp, ignore_errors=True)
+
+    def make_engine(dtype, batch_limit):
+        if tmp is not None:
+            return Engine(tmp, options(dtype, batch_limit))
+        return Engine(None, options(dtype, batch_limit), config=cfg, random_seed=4)    # drawn on the device
 
     g = torch.Generator().manual_seed(1)
 
     def prompts(n, length):
         return torch.randint(0, cfg["vocab_size"], (n, length), generator=g).tolist()
 
-    def decode_run(batch, steps, warm, sample_clocks=False):
-        """Prefill ``batch`` requests and decode them together so that the furthest
-        one ends at context ``ctx``.  Prompts are prefilled one a step while earlier
-        requests already decode, so the requests' contexts differ by up to ``batch``
-        tokens (times the portions of a prompt longer than a step's budget); all of them stay live through both timed regions.  Returns (device ms
-        per step, e2e ms per step, launches, h2d, d2h, clocks, cached tokens in the
-        middle of the device-timed region)."""
+    def decode_run(eng, batch, steps, warm, repeats, sample_clocks=False):
+        """Prefill ``batch`` requests and decode them together so that the furthest one
+        ends at context ``ctx``.  Prompts are prefilled one a step while earlier requests
+        already decode, so the requests' contexts differ by up to ``batch`` tokens (times
+        the portions of a prompt longer than a step's budget); all of them stay live
+        through every timed region.  The region of ``steps`` decode steps is timed
+        ``repeats`` times, each time by CUDA events on the launching stream (device time)
+        and by the wall clock around the same calls of the public API with a synchronise
+        on both sides (end to end: every step copies its inputs from pinned host memory
+        and the host reads the step's tokens).  Returns a dict."""
         portions = -(-ctx // eng.runner.max_step_tokens)       # steps that one prompt's prefill takes
-        total = 2 * (steps + warm) + batch * portions + 2
+        total = repeats * steps + warm + batch * portions + 2
         plen = ctx - total
+        if plen < 1:
+            raise SystemExit(f"bench.py: {repeats} x {steps} steps do not fit a context of {ctx}")
         sched = Scheduler(eng)
         for p in prompts(batch, plen):
             sched.submit(p, total)
@@ -286,45 +326,66 @@ def main():
             sched.step()
         torch.cuda.synchronize()
         clocks = ClockSampler(eng.options.device) if sample_clocks else None
-        # device-timed
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        l0 = kernels.launches
+        if clocks:
+            time.sleep(0.1)                                    # let the sampler's first rows arrive
+        dev, e2e, launches = [], [], 0
+        cached_mid = 0
         t0 = time.time()
-        ev0.record()
-        for _ in range(steps):
-            sched.step()
-        ev1.record()
-        torch.cuda.synchronize()
+        for rep in range(repeats):
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            l0 = kernels.launches
+            w0 = time.perf_counter()
+            ev0.record()
+            for _ in range(steps):
+                sched.step()
+            ev1.record()
+            torch.cuda.synchronize()
+            w1 = time.perf_counter()
+            dev.append(ev0.elapsed_time(ev1) / steps)
+            e2e.append((w1 - w0) * 1e3 / steps)
+            launches = (kernels.launches - l0) // steps
+            assert len(sched.running) == batch, "a request ended inside the timed region"
+            if rep == repeats // 2:
+                cached_mid = sum(r.cache.length for r in sched.running) - batch * steps // 2
+            if clocks and time.time() - t0 < 0.3 and rep == repeats - 1:
+                time.sleep(0.3 - (time.time() - t0))           # a few more samples of a very short run
         t1 = time.time()
-        dev_ms = ev0.elapsed_time(ev1) / steps
-        launches = (kernels.launches - l0) // steps
-        assert len(sched.running) == batch, "a request ended inside the timed region"
-        cached = sum(r.cache.length for r in sched.running) - batch * steps // 2
-        # end to end: wall clock around the public API, synchronised on both sides
-        for _ in range(warm):
-            sched.step()
-        torch.cuda.synchronize()
-        w0 = time.perf_counter()
-        for _ in range(steps):
-            sched.step()
-        torch.cuda.synchronize()
-        e2e_ms = (time.perf_counter() - w0) * 1e3 / steps
-        t2 = time.time()
         csum = None
         if clocks:
-            time.sleep(0.15)
+            time.sleep(0.1)
             clocks.stop()
-            csum = clocks.summary(t0, t2)          # both timed regions: device-timed and end-to-end
-        assert len(sched.running) == batch, "a request ended inside the timed region"
+            csum = clocks.summary(t0, t1)
         h2d = eng.runner.last_h2d_bytes
         sched.stop()
-        return dev_ms, e2e_ms, launches, h2d, batch * 4, csum, cached
+        i = sorted(range(repeats), key=lambda j: dev[j])[repeats // 2]     # the median repeat
+        return {"dev_ms": dev[i], "e2e_ms": median(e2e), "dev_all": dev, "launches": launches, "h2d": h2d,
+                "d2h": batch * 4, "clocks": csum, "cached": cached_mid}
 
-    def prefill_run(T=args.prefill_tokens):
-        from kllm_b200.engine import StepEntry
+    def decode_512_run(eng, batch=8, plen=512, new=256):
+        """BASELINE.json's decode workload: ``batch`` prompts of 512 tokens, 256 tokens
+        generated each; every decode step is timed (device time between two events)."""
+        times = []
+        for _ in range(2):                                   # the first pass warms up (graphs of the batch sizes)
+            sched = Scheduler(eng)
+            for p in prompts(batch, plen):
+                sched.submit(p, new)
+            while any(r.fed < len(r.prompt) for r in list(sched.running) + list(sched.waiting)):
+                sched.step()
+            torch.cuda.synchronize()
+            d0 = sched.metrics.decode_tokens
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+            sched.run()
+            ev1.record()
+            torch.cuda.synchronize()
+            times.append((sched.metrics.decode_tokens - d0) / (ev0.elapsed_time(ev1) * 1e-3))
+        return round(times[-1], 1)
+
+    def prefill_run(eng, T=args.prefill_tokens):
         ids = prompts(1, T)[0]
         times = []
-        for _ in range(4):
+        for _ in range(6):
             req = eng.cache.open()
             ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
@@ -334,59 +395,182 @@ def main():
             torch.cuda.synchronize()
             times.append(ev0.elapsed_time(ev1))
             eng.cache.close(req)
-        ms = min(times[1:])
+        ms = median(times[1:])
         per_layer, _ = model_bytes_and_flops(cfg, layers)
         qd = cfg["num_attention_heads"] * cfg["head_dim"]
         flops = 2 * T * (per_layer * layers) + 2 * cfg["vocab_size"] * cfg["hidden_size"] \
             + 2 * T * T * qd * layers          # causal attention: QK^T and PV over half the square
-        return {"value": round(T / (ms * 1e-3), 1), "tokens": T, "ms": round(ms, 3),
-                "frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+        out = {"value": round(T / (ms * 1e-3), 1), "tokens": T, "ms": round(ms, 3),
+               "frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+               "spread_ms": [round(min(times[1:]), 3), round(max(times[1:]), 3)]}
+        if eng.dtype != torch.bfloat16:
+            out["frac_of"] = "bf16 tensor peak (the float32 path does not use tensor cores)"
+        return out
 
-    if args.only == "prefill":
-        with torch.no_grad():
-            print(json.dumps({"partial": "prefill only", "layers": layers, "prefill": prefill_run()}))
-        return 0
+    def roofline(eng, run, batch):
+        _, weight_elems = model_bytes_and_flops(cfg, layers)
+        esize = 2 if eng.dtype == torch.bfloat16 else 4
+        step_bytes = esize * weight_elems + run["cached"] * eng.cache.bytes_per_token_full()
+        achieved = step_bytes / (run["dev_ms"] * 1e-3) / 1e9
+        return step_bytes, {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                            "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": step_bytes,
+                            "mean_context": run["cached"] // batch}
 
-    if args.timeline:
+    try:
+        eng = make_engine(args.dtype, max_b)
+        if args.only == "prefill":
+            with torch.no_grad():
+                print(json.dumps({"partial": "prefill only", "layers": layers, "prefill": prefill_run(eng)}))
+            return 0
+        if args.timeline:
+            with torch.no_grad():
+                run = decode_run(eng, B, K, W, 1)
+            print_timeline(kernels.timeline(), run["dev_ms"])
+            return 0
+
         with torch.no_grad():
-            dev_ms = decode_run(B, K, W)[0]
-        print_timeline(kernels.timeline(), dev_ms)
+            run = decode_run(eng, B, K, W, R, sample_clocks=True)
+            step_bytes, roof = roofline(eng, run, B)
+            dt = "bf16" if args.dtype == "bfloat16" else "fp32"
+            out = {
+                "metric": f"decode tok/s at batch {B} ({shape_name}, context {ctx})",
+                "value": round(B / (run["dev_ms"] * 1e-3), 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+                "ms_per_step": round(run["dev_ms"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": dt, "data": "synthetic token ids, random weights (seed 4)",
+                "config": {"model": shape_name.replace("TinyLlama 1.1B", "TinyLlama-1.1B"), "global_batch": B,
+                           "seq_len": ctx, "parallelism": "single GPU",
+                           "layers": layers, "layers_of_config": layers_full, "hidden": cfg["hidden_size"],
+                           "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                           "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
+                           "vocab": cfg["vocab_size"], "page_size": page,
+                           "l2": f"step reads {step_bytes / 1e9:.1f} GB > 126 MB L2, no flush",
+                           "peaks": pk["source"], "repeats": R,
+                           "timing": "median of the repeats of K steps; CUDA events, wall clock for e2e"},
+                "spread": {"repeats": R, "min_ms": round(min(run["dev_all"]), 4), "max_ms": round(max(run["dev_all"]), 4)},
+                "clocks": run["clocks"],
+                "e2e": {"value": round(B / (run["e2e_ms"] * 1e-3), 1), "unit": "tokens/s",
+                        "ms_per_step": round(run["e2e_ms"], 4),
+                        "h2d_bytes_per_step": run["h2d"], "d2h_bytes_per_step": run["d2h"]},
+                "gpu_launches": run["launches"] * K,
+                "roofline": roof,
+            }
+            if not args.no_points:
+                out["prefill"] = prefill_run(eng)
+            if full:
+                pts = {}
+                for b in (1, 64):
+                    pts[f"decode_b{b}"] = round(b / (decode_run(eng, b, K, 3, R)["dev_ms"] * 1e-3), 1)
+                pts["decode_b8_ctx512"] = decode_512_run(eng)
+                out["points"] = pts
+                # the same model on the float32 path: what to hold against the reference, which
+                # has no other precision
+                eng.close()
+                del eng
+                torch.cuda.empty_cache()
+                eng = make_engine("float32", B)
+                r32 = decode_run(eng, B, K, 3, R)
+                _, roof32 = roofline(eng, r32, B)
+                out["points_fp32"] = {"decode_b8": round(B / (r32["dev_ms"] * 1e-3), 1),
+                                      "decode_b8_ms_per_step": round(r32["dev_ms"], 4),
+                                      "decode_b8_e2e": round(B / (r32["e2e_ms"] * 1e-3), 1),
+                                      "decode_b8_hbm_frac": roof32["frac"],
+                                      "prefill": prefill_run(eng)}
+                out["precision"] = ("value and e2e are bfloat16; the reference arm computes in float32, its only "
+                                    "precision: points_fp32 is this engine at that precision")
+        print(json.dumps(out))
         return 0
+    finally:
+        if tmp is not None:
+            shutil.rmtree(tmp, ignore_errors=True)
+
+
+def mixed_workload(args):
+    """BASELINE.json's continuous-batching workload at the layer sizes of Llama-2 7B: 32
+    requests, prompt lengths uniform in [128, 3072] (seeded), 128 new tokens each, greedy,
+    through ``Scheduler.run``'s loop; random bfloat16 weights drawn on the device.  Prints one
+    JSON record: generated tokens a second over the whole run (wall clock, prefill included),
+    steps, preemptions, the pages' high-water mark, and for the steps that held single tokens
+    only their device time against the bytes they had to read (weights once, the cache of the
+    live requests)."""
+    import torch
+    from kllm_b200.engine import Engine, Options, Scheduler
+    cfg = dict(SHAPES["llama2-7b"])
+    layers_full = cfg["num_hidden_layers"]
+    layers = args.layers or layers_full
+    cfg["num_hidden_layers"] = layers
+    pk = peaks()
+    n_req, new = 32, 128
+    rng = torch.Generator().manual_seed(5)
+    lengths = torch.randint(128, 3073, (n_req,), generator=rng).tolist()
+    prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=rng).tolist() for n in lengths]
+    page = 64
+    pages = sum(-(-(n + new) // page) for n in lengths) + 8
+    eng = Engine(None, Options(dtype="bfloat16", max_seq=3072 + new, block_size=page, num_blocks=pages, max_batch=n_req,
+                               max_step_tokens=4096), config=cfg, random_seed=5)
+    _, weight_elems = model_bytes_and_flops(cfg, layers)
+    per_token = eng.cache.bytes_per_token_full()
+
+    def run_once(record):
+        sched = Scheduler(eng)
+        reqs = [sched.submit(p, new) for p in prompts]
+        marks = []
+        torch.cuda.synchronize()
+        w0 = time.perf_counter()
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        marks.append((ev, None))
+        while sched.waiting or sched.running or sched._inflight:
+            before = sched.metrics.steps
+            live = [r for r in sched.running]
+            sched.step()
+            if record and sched.metrics.steps > before:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                prefill = sched.metrics.prefill_tokens
+                marks.append((ev, (prefill, sum(r.cache.length for r in sched.running if r.cache is not None),
+                                   len(sched.running))))
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - w0
+        assert all(r.status == "finished" and len(r.generated) == new for r in reqs)
+        return sched, wall, marks
 
     with torch.no_grad():
-        dev_ms, e2e_ms, launches, h2d, d2h, clocks, cached = decode_run(B, K, W, sample_clocks=True)
-        per_layer, weight_elems = model_bytes_and_flops(cfg, layers)
-        kv_bytes = cached * eng.cache.bytes_per_token_full()
-        step_bytes = 2 * weight_elems + kv_bytes
-        achieved = step_bytes / (dev_ms * 1e-3) / 1e9
-        out = {
-            "metric": f"decode tok/s at batch {B} ({shape_name}, context {ctx})",
-            "value": round(B / (dev_ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
-            "ms_per_step": round(dev_ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic token ids, random weights (seed 4)",
-            "config": {"model": shape_name.replace("TinyLlama 1.1B", "TinyLlama-1.1B"), "global_batch": B, "seq_len": ctx, "parallelism": "single GPU",
-                       "layers": layers, "layers_of_config": layers_full, "hidden": cfg["hidden_size"],
-                       "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
-                       "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
-                       "vocab": cfg["vocab_size"], "page_size": 64,
-                       "l2": f"step reads {step_bytes / 1e9:.1f} GB > 126 MB L2, no flush",
-                       "peaks": pk["source"]},
-            "clocks": clocks,
-            "e2e": {"value": round(B / (e2e_ms * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": launches * K,
-            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                         "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": step_bytes,
-                         "mean_context": cached // B},
-        }
-        if not args.no_points:
-            out["prefill"] = prefill_run()
-            pts = {}
-            for b in (1, 64):
-                dms = decode_run(b, max(8, K // 2), 3)[0]
-                pts[f"decode_b{b}"] = round(b / (dms * 1e-3), 1)
-            out["points"] = pts
+        run_once(False)                                  # warm-up: library set-up, graphs of the batch sizes
+        clocks = ClockSampler(0)
+        t0 = time.time()
+        sched, wall, marks = run_once(True)
+        t1 = time.time()
+        time.sleep(0.15)
+        clocks.stop()
+    # steps whose entries were all single tokens: no prefill token was added by them
+    dec_ms, dec_bytes, dec_steps = 0.0, 0, 0
+    prev_prefill = 0
+    for (e0, _), (e1, info) in zip(marks, marks[1:]):
+        prefill, cached, live = info
+        if prefill == prev_prefill and live > 0:
+            dec_ms += e0.elapsed_time(e1)
+            dec_bytes += 2 * weight_elems + cached * per_token
+            dec_steps += 1
+        prev_prefill = prefill
+    m = sched.metrics
+    out = {"workload": "llama2-7b-mixed", "metric": "generated tok/s, 32 requests, prompts U[128,3072], 128 new tokens each",
+           "value": round(n_req * new / wall, 1), "unit": "tokens/s", "wall_s": round(wall, 3), "dtype": "bf16",
+           "data": "synthetic token ids (seed 5), random weights drawn on the device (seed 5)",
+           "config": {"model": "Llama-2 7B shape", "layers": layers, "layers_of_config": layers_full,
+                      "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                      "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                      "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "requests": n_req,
+                      "prompt_tokens": sum(lengths), "new_tokens_each": new, "page_size": page, "pages": pages,
+                      "max_batch": n_req, "max_step_tokens": 4096, "peaks": pk["source"]},
+           "steps": m.steps, "prefill_tokens": m.prefill_tokens, "decode_tokens": m.decode_tokens,
+           "preemptions": m.preemptions, "pages_high_water": m.pages_high_water,
+           "prompt_tokens_per_s": round(sum(lengths) / wall, 1),
+           "decode_only_steps": {"steps": dec_steps, "ms_per_step": round(dec_ms / max(1, dec_steps), 3),
+                                 "hbm_gbs": round(dec_bytes / max(1e-9, dec_ms * 1e-3) / 1e9, 1),
+                                 "hbm_frac": round(dec_bytes / max(1e-9, dec_ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)},
+           "clocks": clocks.summary(t0, t1)}
     print(json.dumps(out))
+    eng.close()
     return 0
 
 

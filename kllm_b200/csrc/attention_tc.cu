@@ -35,6 +35,7 @@
 // key are zero-filled instead of loaded.  The math is the reference's
 // (backend/model.cu:343-408): keys [max(0, p + 1 - window), p], scale after the
 // dot product, one division by the sum at the end.
+#include <mutex>
 #include "common.cuh"
 #include "attention_tc_static.h"
 
@@ -861,6 +862,7 @@ extern "C" int kllm_attention_decode_fused(void* out, void* part_o, void* part_m
 static __device__ __align__(256) float g_static_scratch[KLLM_ATTN_STATIC_SCRATCH_FLOATS];
 static constexpr int kMaxDevices = 64;
 static float* g_static_scratch_addr[kMaxDevices] = {};
+static std::mutex g_static_scratch_lock;     // threads may make their first call on a device together
 
 extern "C" int kllm_attention_decode_static(void* out, const void* q, int64_t q_stride, const void* kcache,
                                             const void* vcache, const int* positions, const int* token_req,
@@ -887,18 +889,21 @@ extern "C" int kllm_attention_decode_static(void* out, const void* q, int64_t q_
             return (int)e;
         }
         if (dev < 0 || dev >= kMaxDevices) KLLM_FAIL("attention: device ordinal %d not supported", dev);
-        if (g_static_scratch_addr[dev] == nullptr) {
-            float* p = nullptr;
-            e = cudaGetSymbolAddress((void**)&p, g_static_scratch);
-            if (e != cudaSuccess || p == nullptr) {
-                snprintf(g_kllm_err, sizeof(g_kllm_err),
-                         "attention decode (static scratch): cudaGetSymbolAddress on device %d: %s", dev,
-                         cudaGetErrorString(e));
-                return e != cudaSuccess ? (int)e : KLLM_ERR_ARG;
+        {
+            std::lock_guard<std::mutex> hold(g_static_scratch_lock);
+            if (g_static_scratch_addr[dev] == nullptr) {
+                float* p = nullptr;
+                e = cudaGetSymbolAddress((void**)&p, g_static_scratch);
+                if (e != cudaSuccess || p == nullptr) {
+                    snprintf(g_kllm_err, sizeof(g_kllm_err),
+                             "attention decode (static scratch): cudaGetSymbolAddress on device %d: %s", dev,
+                             cudaGetErrorString(e));
+                    return e != cudaSuccess ? (int)e : KLLM_ERR_ARG;
+                }
+                g_static_scratch_addr[dev] = p;
             }
-            g_static_scratch_addr[dev] = p;
+            part_o = g_static_scratch_addr[dev];
         }
-        part_o = g_static_scratch_addr[dev];
         part_ml = part_o + slots * HD;
     }
     return kllm_attention_decode(out, part_o, part_ml, q, q_stride, kcache, vcache, positions, token_req,

@@ -19,7 +19,8 @@
 //
 // First call on a device: the array's device address is looked up once per device
 // (cudaGetSymbolAddress with that device current) and the kernels' shared-memory
-// limit is raised.  Make that first call outside of any stream capture.
+// limit is raised.  Make that first call outside of any stream capture.  The look-up
+// is guarded by a mutex, so threads may make their first calls at the same time.
 //
 // All calls share the one array and it keeps whatever the last call left there.
 // Nothing in it has to start at zero: every slot that a call reads was written by

@@ -70,16 +70,11 @@ def build_dir() -> str:
 
 
 def _with_global(defines):
-    """A library's definitions plus those that the environment asks of every library:
-    KLLM_B200_TIMELINE=1 builds the instrumented variants (see common.cuh);
-    KLLM_B200_DEFINES="NAME=VALUE,..." adds definitions for measurements of a kernel's
-    compile-time choices (variants of their own, built at first use)."""
+    """A library's definitions plus the one that the environment asks of every library:
+    KLLM_B200_TIMELINE=1 builds the instrumented variants (see common.cuh)."""
     d = dict(defines or {})
     if os.environ.get("KLLM_B200_TIMELINE", "0") not in ("", "0"):
         d["KLLM_TIMELINE"] = 1
-    for item in filter(None, os.environ.get("KLLM_B200_DEFINES", "").split(",")):
-        k, _, v = item.partition("=")
-        d[k.strip()] = v.strip() or 1
     return d
 
 

@@ -239,9 +239,6 @@ skinny_gemm_kernel(const Args a) {
     TL_MARK(2);
 
     // ---- tiles ----
-#ifdef KLLM_SKINNY_TLDETAIL       // instrumented builds only: marks 3..6 are the ends of the first four batches
-    int tl_n = 3;
-#endif
     float acc[NT][4];
 #pragma unroll
     for (int i = 0; i < NT; i++)
@@ -272,10 +269,6 @@ skinny_gemm_kernel(const Args a) {
                 }
             }
         }
-#ifdef KLLM_SKINNY_TLDETAIL
-        if (tl_n == 3) TL_MARK(3); else if (tl_n == 4) TL_MARK(4); else if (tl_n == 5) TL_MARK(5); else if (tl_n == 6) TL_MARK(6);
-        tl_n++;
-#endif
         if (cur_b == nb - 1) {
             // the warps' partial tiles, added in warp order
             const int tile = cur_tile;
@@ -319,11 +312,7 @@ skinny_gemm_kernel(const Args a) {
         phase(buf1a, buf1b, buf0a, buf0b);
     }
     if (PRO == X_BF16) cp_async_wait_pending(0);            // a CTA without a tile: nothing in flight at its end
-#ifdef KLLM_SKINNY_TLDETAIL
-    TL_MARK(7);
-#else
     TL_MARK(3);
-#endif
     TL_END(a.tl_slot, 100 + PRO * 10 + EPI);        // marks: start, dependency wait over, X ready, tiles done
 }
 
@@ -359,11 +348,7 @@ int launch(const Args& a, cudaStream_t s) {
     // waits.  One with many tiles gains nothing from that and was measured to stream
     // slower when it got an early start (at 12 tiles per CTA and K = 4096 at half speed:
     // 235 MB in 72 us instead of 45), so it starts when the kernel before it has ended.
-#ifdef KLLM_SKINNY_EARLY_MASK      // measurements: which kinds of kernel start early (bit = PRO * 4 + EPI)
-    const bool early = (KLLM_SKINNY_EARLY_MASK >> (PRO * 4 + EPI)) & 1;
-#else
     const bool early = n_tiles <= EARLY_START_TILES * grid;
-#endif
     kllm_launch_dep(early, (kern), dim3(grid), dim3(THREADS), smem, s, a);
     KLLM_LAUNCH_STATUS();
 }

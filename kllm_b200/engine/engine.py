@@ -19,10 +19,11 @@ import torch
 from .. import kernels
 from .. import models  # noqa: F401  (registers the architectures)
 from ..cache.manager import CacheManager, RequestCache
-from ..config.base import ModelConfig, build_model_spec, load_config
+from ..config.base import ModelConfig, build_model_spec, load_config, parse_config
 from ..parts.model import DecoderModel
 from ..sampling.sampler import Sampler
 from ..weights.loader import load_weights
+from ..weights.random_init import random_tensors
 from .step import StepEntry, StepRunner
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
@@ -83,7 +84,13 @@ class Sequence_:
 
 
 class Engine:
-    def __init__(self, model_dir: str, options: Optional[Options] = None, **kw):
+    def __init__(self, model_dir: Optional[str], options: Optional[Options] = None, *,
+                 config: Union[None, dict, ModelConfig] = None, random_seed: int = 0, **kw):
+        """``model_dir``: a folder with config.json and safetensors.  With ``model_dir``
+        None and a ``config`` (the dict of a config.json, or a typed configuration) the
+        model gets random weights drawn on the device from ``random_seed`` (N(0, 0.02)
+        matrices, gains 1): for measurements at sizes whose files would take longer to
+        write than to measure."""
         opts = (options or Options(**kw)).fill()
         self.options = opts
         if not torch.cuda.is_available():
@@ -94,11 +101,19 @@ class Engine:
         torch.backends.cuda.matmul.allow_tf32 = False   # float32 stays true 32-bit
         torch.backends.cudnn.allow_tf32 = False
         self.dtype = _DTYPES[opts.dtype]
-        self.config: ModelConfig = load_config(model_dir)
+        if model_dir is not None:
+            self.config: ModelConfig = load_config(model_dir)
+        elif config is not None:
+            self.config = parse_config(config) if isinstance(config, dict) else config
+        else:
+            raise ValueError("Engine needs a model folder or a configuration")
         self.spec = build_model_spec(self.config)
         with torch.no_grad():
             self.model = DecoderModel(self.spec, self.dtype, self.device)
-            tensors = load_weights(model_dir, self.model.tensor_specs(), self.dtype, self.device)
+            if model_dir is not None:
+                tensors = load_weights(model_dir, self.model.tensor_specs(), self.dtype, self.device)
+            else:
+                tensors = random_tensors(self.model.tensor_specs(), random_seed, self.dtype, self.device)
             self.model.bind(tensors)
             del tensors
             if opts.num_blocks <= 0:

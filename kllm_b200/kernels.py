@@ -172,6 +172,67 @@ def attention_generic(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, 
     _check(lib, "attention_generic", rc)
 
 
+SIMT_CHUNK = 256      # keys per CTA when a decoding token's context is cut (attention_simt)
+
+
+def attention_simt(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, ctx,
+                   block_table: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, window: int,
+                   scale: float) -> None:
+    """Causal GQA attention of the step's tokens on the CUDA cores, float32 arithmetic
+    (csrc/attention_simt.cu): the attention of the float32 path.  The requests that bring
+    one token each at the head of the batch (decoding requests, which the scheduler puts
+    first) have their contexts cut into chunks of SIMT_CHUNK keys, one CTA each, merged in
+    chunk order; the portions after them run as tiles of up to 64 (token, head) rows."""
+    _cuda(out, q, kcache, vcache, block_table)
+    _i32(block_table, "block_table"); _i32(ctx.q_start, "q_start"); _i32(ctx.start_pos, "start_pos")
+    if q.stride(1) != 1 or not out.is_contiguous() or out.dtype != q.dtype or kcache.dtype != q.dtype:
+        raise KernelError("attention: operands must share a dtype; out contiguous, q rows dense")
+    if not kcache.is_contiguous() or not vcache.is_contiguous() or kcache.shape[1] != n_kv or kcache.shape[3] != head_dim:
+        raise KernelError("attention: cache layout must be [pages, n_kv, page_size, head_dim]")
+    group = n_heads // max(1, n_kv)
+    lib = load_library("attention_simt")
+    n_req = ctx.n_requests
+    singles = n_req if ctx.all_single else 0
+    if not ctx.all_single and ctx.host_n_new:
+        while singles < n_req and ctx.host_n_new[singles] == 1:
+            singles += 1
+    bound = ctx.split_bound or ctx.max_ctx
+    if window:
+        bound = min(bound, int(window))
+    splits = max(1, -(-bound // SIMT_CHUNK))
+    common = (n_heads, n_kv, head_dim, kcache.shape[2], int(window or 0), ctypes.c_float(scale))
+    first = 0
+    global launches
+    if singles and splits > 1:
+        part_o = torch.empty((singles * n_heads, splits, head_dim), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((singles * n_heads, splits, 2), dtype=torch.float32, device=q.device)
+        rc = lib.kllm_attention_simt(_p(out), _p(part_o), _p(part_ml), _p(q), ctypes.c_int64(q.stride(0)), _p(kcache),
+                                     _p(vcache), _p(ctx.q_start), _p(ctx.start_pos), _p(block_table),
+                                     block_table.shape[1], singles, singles, *common, 1, SIMT_CHUNK, splits,
+                                     dtype_code(q.dtype), _stream())
+        _check(lib, "attention_simt", rc)
+        rc = lib.kllm_attention_simt_merge(_p(out), _p(part_o), _p(part_ml), _p(ctx.positions), singles, n_heads,
+                                           head_dim, int(window or 0), SIMT_CHUNK, splits, dtype_code(q.dtype), _stream())
+        _check(lib, "attention_simt", rc)
+        first = singles
+    if first < n_req:
+        qt = max(1, 64 // group)
+        rest = ctx.n_tokens - first
+        rc = lib.kllm_attention_simt(_p(out), None, None, _p(q), ctypes.c_int64(q.stride(0)), _p(kcache), _p(vcache),
+                                     _p(ctx.q_start[first:]), _p(ctx.start_pos[first:]), _p(block_table[first:]),
+                                     block_table.shape[1], n_req - first, rest // qt + (n_req - first), *common, qt, 0, 1,
+                                     dtype_code(q.dtype), _stream())
+        _check(lib, "attention_simt", rc)
+
+
+def simt_fits(q: torch.Tensor, n_heads: int, n_kv: int, head_dim: int) -> bool:
+    """Whether ``attention_simt`` takes these operands: head size a multiple of 4 up to
+    256, at most 64 heads per kv head, rows aligned to four elements."""
+    quad = 4 * q.element_size()
+    return (head_dim % 4 == 0 and 0 < head_dim <= 256 and n_heads // max(1, n_kv) <= 64
+            and q.data_ptr() % quad == 0 and q.stride(0) % 4 == 0)
+
+
 TC_HEAD_DIMS = tuple(range(16, 129, 16))     # head sizes of the tensor-core attention library
 TCGEN05_HEAD_DIMS = (64, 128)                # head sizes of the tcgen05 prefill attention
 PREFETCH_L2 = os.environ.get("KLLM_B200_PREFETCH", "1") != "0"   # kernels warm L2 for the kernel after them
@@ -179,10 +240,15 @@ PREFETCH_L2 = os.environ.get("KLLM_B200_PREFETCH", "1") != "0"   # kernels warm 
 # 126 MB of L2 pushes out lines that are still needed and is read from HBM twice
 PREFETCH_L2_BYTES = int(float(os.environ.get("KLLM_B200_PREFETCH_MB", "24")) * 2 ** 20)
 USE_TCGEN05 = os.environ.get("KLLM_B200_TCGEN05", "1") != "0"
-SM_COUNT = 148
+_sm_count = {}
 
 
-_FORCED_SPLITS = int(os.environ.get("KLLM_B200_DECODE_SPLITS", "0") or 0)
+def sm_count() -> int:
+    """Streaming multiprocessors of the current device (148 on a B200)."""
+    dev = torch.cuda.current_device()
+    if dev not in _sm_count:
+        _sm_count[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+    return _sm_count[dev]
 
 
 def decode_splits(n_tokens: int, n_kv: int, ctx_bound: int) -> int:
@@ -192,10 +258,8 @@ def decode_splits(n_tokens: int, n_kv: int, ctx_bound: int) -> int:
     whole 64-key tiles, as many as fill the SMs in ONE wave (a second wave of short
     CTAs would double the kernel's time), at most 16, all the same length.  When one
     range per token would be long, two are used even if that spills into a second
-    wave: long CTAs hide it.  KLLM_B200_DECODE_SPLITS=<n> fixes the number (for measuring)."""
-    if _FORCED_SPLITS:
-        return max(1, min(_FORCED_SPLITS, max(1, -(-ctx_bound // 64))))
-    slots = 2 * SM_COUNT
+    wave: long CTAs hide it."""
+    slots = 2 * sm_count()
     tiles = max(1, -(-ctx_bound // 64))
     base = max(1, n_tokens * n_kv)
     splits = max(1, min(slots // base, tiles, 16))
@@ -212,7 +276,8 @@ def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: 
     kernel that fits: bfloat16 with a head size in TC_HEAD_DIMS runs on tensor cores
     (the decode form when every request brings one token, else the prefill form: on
     tcgen05 for head sizes 64 and 128, on mma.sync for the other multiples of 16);
-    float32, other head sizes or very wide groups run the generic kernel.  A mixed
+    float32 and other head sizes run on the CUDA cores (``attention_simt``; head sizes
+    that are no multiple of 4 and groups wider than 64 the one-warp-per-row kernel).  A mixed
     step whose first requests bring one token each (the scheduler puts decoding requests
     first) is cut in two: those tokens take the decode form, which spreads a long context
     over many CTAs, the portions after them the prefill form, in which a single token
@@ -241,6 +306,8 @@ def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: 
     if tc and group <= 64:
         return attention_prefill(out, q, kcache, vcache, q_start, start_pos, table,
                                  n_req, n_heads, n_kv, head_dim, window, scale)
+    if simt_fits(q, n_heads, n_kv, head_dim):
+        return attention_simt(out, q, kcache, vcache, ctx, block_table, n_heads, n_kv, head_dim, window, scale)
     return attention_generic(out, q, kcache, vcache, ctx.positions, ctx.token_req, block_table, n_heads, n_kv,
                              head_dim, window, scale)
 
@@ -577,9 +644,6 @@ def gemm_fits(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue
     return bool(lib.kllm_gemm_tcgen05_fits(*_gemm_args(x, weight, weight_up, out, epilogue)))
 
 
-_sm_count = {}
-
-
 def gemm_pays(n: int, N: int, epilogue: str = "bf16", least: int = 75) -> bool:
     """Whether ``gemm``'s tiles of 128 rows x 256 accumulator columns would keep the
     tensor cores of all SMs busy for at least ``least`` percent of the product's time
@@ -587,10 +651,7 @@ def gemm_pays(n: int, N: int, epilogue: str = "bf16", least: int = 75) -> bool:
     better.  Same arithmetic as kllm_gemm_tcgen05_efficiency, without loading the library."""
     if not USE_TCGEN05 or n <= 0 or N <= 0:
         return False
-    dev = torch.cuda.current_device()
-    if dev not in _sm_count:
-        _sm_count[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
-    sms = _sm_count[dev]
+    sms = sm_count()
     nout = 128 if epilogue == "swiglu" else 256
     tiles = -(-n // 128) * -(-N // nout)
     waves = -(-tiles // sms)

@@ -6,6 +6,11 @@ generator draws them (tools/make_test_model.py:59-80: std 0.02, gains 1 + 0.01 N
 Each tensor has a random stream of its own, keyed by (seed, tensor name), so the
 values do not depend on the order of creation or on which other tensors exist.
 The file is streamed, one tensor in memory at a time.
+
+``random_tensors`` fills the same tensors in place of a folder, on the device the
+model lives on: measurements of models with billions of parameters need not write and
+read tens of gigabytes first.  Its streams are keyed the same way but drawn by the
+device's generator, so its numbers are not the file's numbers.
 """
 from __future__ import annotations
 
@@ -27,14 +32,14 @@ def tensor_seed(seed: int, name: str) -> int:
     return int.from_bytes(h[:8], "little") & ((1 << 63) - 1)
 
 
-def random_tensor(spec, seed: int, std: float, gain_std: float, dtype: torch.dtype) -> torch.Tensor:
-    g = torch.Generator(device="cpu")
+def random_tensor(spec, seed: int, std: float, gain_std: float, dtype: torch.dtype, device="cpu") -> torch.Tensor:
+    g = torch.Generator(device=device)
     g.manual_seed(tensor_seed(seed, spec.name))
     if spec.init == "zeros":
-        return torch.zeros(spec.shape, dtype=dtype)
+        return torch.zeros(spec.shape, dtype=dtype, device=device)
     if spec.store == "int32":
         raise ValueError(f"random-weights mode cannot fill the integer table {spec.name}")
-    t = torch.randn(spec.shape, generator=g, dtype=torch.float32)
+    t = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device)
     if spec.init == "gain":
         t = 1.0 + gain_std * t
     elif spec.init == "normal":
@@ -42,6 +47,15 @@ def random_tensor(spec, seed: int, std: float, gain_std: float, dtype: torch.dty
     else:
         raise ValueError(f"tensor {spec.name}: unknown init {spec.init!r}")
     return t.to(dtype)
+
+
+def random_tensors(specs, seed: int, dtype: torch.dtype, device, std: float = 0.02,
+                   gain_std: float = 0.0) -> dict:
+    """name -> random tensor on ``device`` for every tensor of ``specs`` that is not
+    optional, stored as the loader would store it (``dtype`` for matrices, float32 for
+    tensors that stay 32-bit)."""
+    return {s.name: random_tensor(s, seed, std, gain_std, stored_dtype(s, dtype), device)
+            for s in specs if not s.optional}
 
 
 def write_random_model(out_dir: str, config: Union[ModelConfig, dict], seed: int,

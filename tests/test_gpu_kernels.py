@@ -198,7 +198,7 @@ def attention_case(dtype, H, G, hd, page_size, lengths, n_new, window, seed, pla
     elif kernel == "decode":
         kernels.attention_decode(out, q, kc, vc, dev(np.array(pos, np.int32)), dev(np.array(req, np.int32)), table,
                                  H, G, hd, window or 0, scale, splits)
-    elif kernel == "dispatch":
+    elif kernel in ("dispatch", "simt"):
         # the way the attention part calls it: the kernel is chosen from the step's shape
         from types import SimpleNamespace
         ctx = SimpleNamespace(
@@ -206,7 +206,8 @@ def attention_case(dtype, H, G, hd, page_size, lengths, n_new, window, seed, pla
             token_req=dev(np.array(req, np.int32)), q_start=dev(np.concatenate([[0], np.cumsum(n_new)]).astype(np.int32)),
             start_pos=dev(np.array([L - nn for L, nn in zip(lengths, n_new)], dtype=np.int32)),
             host_n_new=list(n_new), all_single=all(c == 1 for c in n_new), max_ctx=max(lengths), split_bound=0)
-        kernels.attention(out, q, kc, vc, ctx, table, H, G, hd, window or 0, scale)
+        fn = kernels.attention if kernel == "dispatch" else kernels.attention_simt
+        fn(out, q, kc, vc, ctx, table, H, G, hd, window or 0, scale)
         kernels.check_status("cuda")
     else:
         q_start = np.concatenate([[0], np.cumsum(n_new)]).astype(np.int32)
@@ -225,6 +226,58 @@ def test_attention_shapes_pages_and_mixed_query_lengths(dtype, H, G, hd, page):
     got, want = attention_case(dtype, H, G, hd, page, lengths, n_new, None, seed=H * hd)
     assert not torch.isnan(got).any(), "a slot beyond a request's length was read"
     close(got, want, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,G,hd,page", [(6, 2, 80, 8), (5, 5, 48, 16), (7, 1, 16, 3), (2, 1, 256, 32), (32, 4, 64, 64),
+                                         (32, 8, 128, 16), (3, 1, 36, 5)])
+@pytest.mark.parametrize("window", [None, 40, 300])
+def test_cuda_core_attention_portions_and_decoding_tokens(dtype, H, G, hd, page, window):
+    """The float32 path's attention (register-tiled products on the CUDA cores): portions of
+    any length beside single tokens, decoding tokens first as the scheduler orders them
+    (contexts over 256 keys are cut into chunks and merged), all single, windows that end
+    inside chunks and tiles."""
+    for lengths, n_new in (([700, 257, 1, 70, 33, 129], [1, 1, 1, 70, 2, 64]),
+                           ([300, 700, 1, 257, 256, 513], [1, 1, 1, 1, 1, 1]),
+                           ([70, 600], [70, 333])):
+        got, want = attention_case(dtype, H, G, hd, page, lengths, n_new, window, seed=H * hd + len(lengths),
+                                   kernel="simt")
+        assert not torch.isnan(got.float()).any(), "a slot beyond a request's length was read"
+        close(got, want, dtype, f"lengths {lengths}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_cuda_core_attention_finds_one_far_key_among_hundreds(dtype):
+    H, G, hd, L = 4, 2, 32, 700
+    far = 3
+
+    def plant(s, q, k, v):
+        q[-1] *= 0.05
+        k[far, 1] = 8.0 * np.sign(q[-1, 2])
+        q[-1, 2] = 3.0 * np.sign(q[-1, 2])
+
+    for n_new in (1, 90):
+        got, want = attention_case(dtype, H, G, hd, 16, [L], [n_new], None, seed=7, plant=plant, kernel="simt")
+        close(got, want, dtype)
+        assert np.abs(want.reshape(n_new, H, hd)[-1, 2]).max() > 0.5
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window", [1, 5, 16, 17, 64, 255, 257])
+def test_cuda_core_attention_window_edge(dtype, window):
+    H, G, hd, L = 2, 1, 16, 600
+
+    def plant(s, q, k, v):
+        outside = L - 1 - window
+        if s == 0 and outside >= 0:
+            k[outside, 0] = 50.0 * q[-1, 0] / np.abs(q[-1, 0]).max()
+            v[outside, 0] = 1e4
+
+    for n_new in (L, 1):
+        got, want = attention_case(dtype, H, G, hd, 8, [L, 40], [n_new, 3], window, seed=window, plant=plant,
+                                   kernel="simt")
+        close(got, want, dtype)
+        assert float(got[n_new - 1].float().abs().max()) < 100.0
 
 
 TC_SHAPES = [(8, 2, 64, 16), (6, 2, 80, 8), (5, 5, 48, 16), (7, 1, 16, 3), (32, 4, 128, 64), (3, 1, 32, 16),

@@ -7,7 +7,8 @@ Here it is called the way such a caller would, through the exported C symbol of
 the shared library with raw device pointers, twice in a row on different inputs
 (the second call finds the first call's leftovers in the shared scratch), and each
 result is held against the regular entry point's, which gets freshly allocated
-scratch buffers.  The file sorts last so that a run which stops at the first
+scratch buffers, and against the plain float64 formula, so that a fault the two
+entry points shared would show as well.  The file sorts last so that a run which stops at the first
 failure has already run every other test.
 """
 import ctypes
@@ -46,6 +47,22 @@ def make_case(seed, H, G, hd, page, lengths):
     return q, kc, vc, pos, req, torch.from_numpy(table).cuda()
 
 
+def plain_answer(q, kc, vc, table, H, G, hd, page, lengths):
+    """The float64 formula (tests/plain) on the same bfloat16 values, read back through
+    the block table: the last token of each request attends to all of its keys."""
+    from plain import llama_plain as plain
+    rows = []
+    tab = table.cpu().numpy()
+    for s, L in enumerate(lengths):
+        pages = tab[s, :-(-L // page)]
+        k = kc[pages].float().cpu().numpy().transpose(0, 2, 1, 3).reshape(-1, G * hd)[:L]
+        v = vc[pages].float().cpu().numpy().transpose(0, 2, 1, 3).reshape(-1, G * hd)[:L]
+        qs = np.zeros((L, H * hd))
+        qs[-1] = q[s].float().cpu().numpy()
+        rows.append(plain.attention(qs, k, v, H, G, hd)[-1])
+    return np.stack(rows)
+
+
 def call_static(lib, out, q, kc, vc, pos, req, table, H, G, hd, splits, window=0):
     p = lambda t: ctypes.c_void_p(t.data_ptr())
     fn = lib.kllm_attention_decode_static
@@ -75,6 +92,8 @@ def test_static_scratch_entry_point_matches_the_regular_one_twice_in_a_row():
         assert not torch.isnan(got.float()).any()
         scale = float(want.float().abs().max())
         assert float((got.float() - want.float()).abs().max()) <= TOL * scale
+        formula = plain_answer(q, kc, vc, table, H, G, hd, page, lengths)
+        assert float(np.abs(got.float().cpu().numpy() - formula).max()) <= TOL * float(np.abs(formula).max())
 
 
 def test_static_scratch_entry_point_refuses_what_does_not_fit():
