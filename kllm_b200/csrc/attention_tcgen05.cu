@@ -49,6 +49,8 @@
 
 KLLM_EXPORT_LAST_ERROR(attention_tcgen05)
 
+#include "tc5_common.cuh"
+
 namespace {
 
 constexpr int HD = KLLM_HD;
@@ -65,9 +67,6 @@ constexpr int STAGES = HD == 64 ? 4 : 2;
 constexpr int SMEM_BYTES = 1024 + Q_BYTES + P_BYTES + STAGES * 2 * KV_BYTES;
 constexpr float kRescaleAt = 8.f;                     // move a row's reference when its maximum grew by 2^8
 constexpr int TMEM_COLS = 256;                        // two score buffers (2 x 64) + output tile (HD): a power of two
-constexpr long long kCycleLimit = 4000000000LL;       // about two seconds
-
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void cp_async16(unsigned dst, const void* gmem, bool valid) {
     const int bytes = valid ? 16 : 0;
@@ -78,19 +77,6 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
 }
 // shared-memory writes of this thread become visible to the tensor core's (async proxy) reads
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
-    unsigned ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-
 // Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor
 // version 1.  K-major operands: 8-row groups 1024 bytes apart (stride offset), leading
 // offset 1.  MN-major operands: 8-k groups 1024 bytes apart (stride offset), 64-element
@@ -111,26 +97,6 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool b_mn_major)
            ((uint32_t)(m >> 4) << 24);
 }
 
-__device__ __forceinline__ void umma(unsigned d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((unsigned)accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-// 32 consecutive float32 columns of this thread's TMEM lane
-__device__ __forceinline__ void tmem_ld32(unsigned taddr, float (&v)[32]) {
-    uint32_t* r = reinterpret_cast<uint32_t*>(v);
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr) : "memory");
-}
 __device__ __forceinline__ void tmem_st32(unsigned taddr, const float (&v)[32]) {
     const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
     asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -143,8 +109,6 @@ __device__ __forceinline__ void tmem_st32(unsigned taddr, const float (&v)[32]) 
                  : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
-
 // byte offset of 16-byte piece `ch` (0..7) of row `r` inside a swizzled panel of 128-byte rows
 __device__ __forceinline__ unsigned swz(int r, int ch) {
     return (unsigned)((r >> 3) * 1024 + (r & 7) * 128 + ((ch ^ (r & 7)) << 4));
@@ -155,37 +119,10 @@ __device__ __forceinline__ float fast_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
 }
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
-
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
 // the barrier gets one arrival when all cp.async copies that this thread has issued so far have landed
 __device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
-// Bounded wait.  Returns false (and raises the flags) when the limit ran out or another
-// role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag, int* status, int where) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    unsigned spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 63u) == 0) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > kCycleLimit) {
-                *abort_flag = 1;
-                if (status) atomicCAS(status, 0, where);
-                return false;
-            }
-        }
-    }
-    return true;
-}
-
 // keys key0 .. key0+63 of kv head g into a stage (K panels, then V panels), by the 32
 // lanes of the loader warp.  A lane keeps its 16-byte piece of the row and walks the rows.
 __device__ __forceinline__ void load_kv(unsigned stage, const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,

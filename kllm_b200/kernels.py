@@ -395,19 +395,29 @@ def attention_prefill(out, q, kcache, vcache, q_start, start_pos, block_table, n
 
 
 def attention_prefill_tcgen05(out, q, kcache, vcache, q_start, start_pos, block_table, n_requests, n_heads, n_kv,
-                              head_dim, window, scale) -> None:
+                              head_dim, window, scale, probabilities: Optional[str] = None) -> None:
     """Attention of portions on tcgen05 tensor cores with TMEM accumulators (head size
-    64 or 128); same contract as ``attention_prefill``."""
+    64 or 128); same contract as ``attention_prefill``.  Two kernels, which differ in where
+    the probabilities wait for the second product: ``probabilities="smem"``
+    (csrc/attention_tcgen05.cu: two score buffers in tensor memory, P through shared
+    memory, two CTAs of head size 64 per SM) or ``"tmem"`` (csrc/attention_tcgen05_ptmem.cu:
+    P written over the scores in tensor memory and read from there, half the tensor memory
+    and shared memory per CTA, four / two CTAs per SM).  Default: the faster one as measured,
+    tmem for head size 128 (1.3 to 1.6 times faster), smem for head size 64 (equal within
+    a tenth either way; smem wins for a single long prompt, tmem for many portions)."""
     _cuda(out, q, kcache, vcache, q_start, start_pos, block_table)
     _check_attention(out, q, kcache, vcache, block_table, n_kv, head_dim)
     _i32(q_start, "q_start"); _i32(start_pos, "start_pos")
-    lib = load_library("attention_tcgen05", {"KLLM_HD": head_dim})
-    rc = lib.kllm_attention_prefill_tcgen05(_p(out), _p(q), ctypes.c_int64(q.stride(0)), _p(kcache), _p(vcache),
-                                            _p(q_start), _p(start_pos), _p(block_table), block_table.shape[1],
-                                            q.shape[0], int(n_requests), n_heads, n_kv, head_dim, kcache.shape[2],
-                                            int(window or 0), ctypes.c_float(scale), _p(status_word(q.device)),
-                                            _stream())
-    _check(lib, "attention_tcgen05", rc)
+    probabilities = probabilities or ("tmem" if head_dim == 128 else "smem")
+    if probabilities not in ("smem", "tmem"):
+        raise KernelError("attention (tcgen05): probabilities wait in 'smem' or in 'tmem'")
+    name = "attention_tcgen05" + ("_ptmem" if probabilities == "tmem" else "")
+    lib = load_library(name, {"KLLM_HD": head_dim})
+    fn = lib.kllm_attention_prefill_tcgen05_ptmem if probabilities == "tmem" else lib.kllm_attention_prefill_tcgen05
+    rc = fn(_p(out), _p(q), ctypes.c_int64(q.stride(0)), _p(kcache), _p(vcache), _p(q_start), _p(start_pos),
+            _p(block_table), block_table.shape[1], q.shape[0], int(n_requests), n_heads, n_kv, head_dim,
+            kcache.shape[2], int(window or 0), ctypes.c_float(scale), _p(status_word(q.device)), _stream())
+    _check(lib, name, rc)
 
 
 _status_words = {}      # device index -> int32 tensor that kernels set when a bounded wait runs out

@@ -212,9 +212,12 @@ def attention_case(dtype, H, G, hd, page_size, lengths, n_new, window, seed, pla
     else:
         q_start = np.concatenate([[0], np.cumsum(n_new)]).astype(np.int32)
         start_pos = np.array([L - nn for L, nn in zip(lengths, n_new)], dtype=np.int32)
-        fn = kernels.attention_prefill if kernel == "prefill" else kernels.attention_prefill_tcgen05
-        fn(out, q, kc, vc, dev(q_start), dev(start_pos), table, len(lengths), H, G, hd, window or 0, scale)
-        if kernel == "tcgen05":
+        fn, extra = kernels.attention_prefill, {}
+        if kernel.startswith("tcgen05"):           # "tcgen05": the default form for the head size; else named
+            fn = kernels.attention_prefill_tcgen05
+            extra = {"probabilities": kernel.split("_")[1]} if "_" in kernel else {}
+        fn(out, q, kc, vc, dev(q_start), dev(start_pos), table, len(lengths), H, G, hd, window or 0, scale, **extra)
+        if kernel.startswith("tcgen05"):
             kernels.check_status("cuda")
     return out, np.concatenate(want)
 
@@ -296,9 +299,11 @@ def test_tensor_core_attention_shapes_pages_and_mixed_query_lengths(kernel, spli
 
 @pytest.mark.parametrize("H,G,hd,page", [(8, 2, 64, 16), (32, 4, 64, 64), (32, 4, 128, 64), (3, 1, 64, 5), (4, 4, 128, 16),
                                          (40, 1, 64, 16)])
-def test_tcgen05_attention_shapes_pages_and_mixed_query_lengths(H, G, hd, page):
+@pytest.mark.parametrize("where", ["smem", "tmem"])
+def test_tcgen05_attention_shapes_pages_and_mixed_query_lengths(H, G, hd, page, where):
+    """Both tcgen05 kernels: the probabilities through shared memory, or kept in tensor memory."""
     lengths, n_new = [70, 1, 33, 129, 300, 500], [70, 1, 2, 1, 64, 500]
-    got, want = attention_case("bfloat16", H, G, hd, page, lengths, n_new, None, seed=H * hd, kernel="tcgen05")
+    got, want = attention_case("bfloat16", H, G, hd, page, lengths, n_new, None, seed=H * hd, kernel="tcgen05_" + where)
     assert not torch.isnan(got.float()).any(), "a slot beyond a request's length was read"
     close(got, want, "bfloat16")
 
@@ -329,7 +334,8 @@ def test_attention_of_a_mixed_step_is_cut_into_decode_and_prefill_forms(H, G, hd
     assert [c[0] for c in calls][0] == "attention_decode" and len(calls) == 2
 
 
-@pytest.mark.parametrize("kernel,splits", [("decode", 1), ("decode", 5), ("prefill", 1), ("tcgen05", 1)])
+@pytest.mark.parametrize("kernel,splits", [("decode", 1), ("decode", 5), ("prefill", 1), ("tcgen05_smem", 1),
+                                           ("tcgen05_tmem", 1)])
 @pytest.mark.parametrize("window", [1, 5, 64, 65, 200])
 def test_tensor_core_attention_window_edge(kernel, splits, window):
     H, G, hd, L = 4, 2, 64, 330
@@ -346,7 +352,8 @@ def test_tensor_core_attention_window_edge(kernel, splits, window):
     assert float(got[L - 1].float().abs().max()) < 100.0
 
 
-@pytest.mark.parametrize("kernel,splits", [("decode", 1), ("decode", 4), ("prefill", 1), ("tcgen05", 1)])
+@pytest.mark.parametrize("kernel,splits", [("decode", 1), ("decode", 4), ("prefill", 1), ("tcgen05_smem", 1),
+                                           ("tcgen05_tmem", 1)])
 def test_tensor_core_attention_finds_one_far_key(kernel, splits):
     H, G, hd, L = 4, 2, 64, 900
     far = 3
