@@ -223,7 +223,8 @@ def loaded_libraries() -> Dict[str, "CheckedLibrary"]:
 # Libraries that are built once per value of a compile-time size: build_all()
 # compiles every allowed value, a running process only the one its model has.
 VARIANTS = {"attention_tc": [{"KLLM_HD": hd} for hd in range(16, 129, 16)],
-            "attention_tcgen05": [{"KLLM_HD": hd} for hd in (64, 128)]}
+            "attention_tcgen05": [{"KLLM_HD": hd} for hd in (64, 128)],
+            "attention_tcgen05_ptmem": [{"KLLM_HD": hd} for hd in (64, 128)]}
 
 
 def build_all(verbose: bool = True) -> List[str]:
