@@ -38,10 +38,7 @@ constexpr int THREADS = 512;       // one CTA per SM: X is prepared once per SM,
 constexpr int WARPS = 16;
 constexpr int UNROLL = 4;          // k-steps of 32 in flight per lane and buffer
 constexpr int NORM_F4 = 16;        // float4 a lane may hold in the one-pass norm prologue
-#ifndef KLLM_SKINNY_EARLY_TILES
-#define KLLM_SKINNY_EARLY_TILES 3
-#endif
-constexpr int EARLY_START_TILES = KLLM_SKINNY_EARLY_TILES;   // most tiles per CTA of a kernel that starts early
+constexpr int EARLY_START_TILES = 3;   // most tiles per CTA of a kernel that starts early
 
 enum { X_BF16 = 0, X_F32_NORM = 1 };
 enum { STORE_BF16 = 0, STORE_F32 = 1, ADD_F32 = 2, SWIGLU = 3 };
