@@ -522,10 +522,18 @@ _PRO = {"bf16": 0, "norm": 1}
 _EPI = {"bf16": 0, "f32": 1, "add": 2, "swiglu": 3}
 
 
+SKINNY_F32_MAX_ROWS = 8
+SKINNY_F32_MAX_WIDTH = 220 * 1024 // (8 * 4) // 128 * 128      # 8 float32 rows in shared memory
+
+
 def skinny_fits(n: int, k: int, dtype: torch.dtype, sliced: bool = False) -> bool:
-    """Whether the weight-streaming product takes n rows of width k in this dtype.
-    ``sliced``: the caller adds into a float32 matrix from bfloat16 rows, where a width
-    too long for shared memory is taken slice by slice (any multiple of 32 fits then)."""
+    """Whether the weight-streaming product takes n rows of width k in this dtype
+    (bfloat16: csrc/skinny_gemm.cu, up to 16 rows; float32: csrc/skinny_gemm_f32.cu, up to
+    8 rows, width a multiple of 128).  ``sliced``: the caller adds into a float32 matrix
+    from rows of the weights' dtype, where a width too long for shared memory is taken
+    slice by slice."""
+    if dtype == torch.float32:
+        return 1 <= n <= SKINNY_F32_MAX_ROWS and k >= 128 and k % 128 == 0 and (sliced or k <= SKINNY_F32_MAX_WIDTH)
     if dtype != torch.bfloat16 or not (1 <= n <= SKINNY_MAX_ROWS) or k < 32 or k % 32:
         return False
     return sliced or k <= _skinny_max_width(n)
@@ -554,12 +562,15 @@ def skinny_gemm(weight: torch.Tensor, *, x: Optional[torch.Tensor] = None, x_f32
                 gain: Optional[torch.Tensor] = None, eps: float = 0.0, rows: Optional[torch.Tensor] = None,
                 n_rows: Optional[int] = None, weight_up: Optional[torch.Tensor] = None, epilogue: str = "bf16",
                 out: Optional[torch.Tensor] = None, prefetch: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """y = X @ weight^T for at most 16 rows, the weights streamed once (csrc/skinny_gemm.cu).
+    """y = X @ weight^T for at most 16 rows, the weights streamed once (csrc/skinny_gemm.cu
+    for bfloat16 weights, csrc/skinny_gemm_f32.cu for float32 weights: true float32 FMAs,
+    at most 8 rows).
 
-    X is either ``x`` (bfloat16 [n, K]) or rmsnorm(``x_f32``) * ``gain`` computed inside
-    the kernel (rows ``rows`` of x_f32 when given).  ``epilogue``: "bf16" / "f32" store
-    y [n, N]; "add" adds y into the float32 ``out``; "swiglu" takes ``weight`` as gate and
-    ``weight_up`` as up matrix and stores silu(gate) * up as bfloat16 [n, N].
+    X is either ``x`` ([n, K] in the weights' dtype) or rmsnorm(``x_f32``) * ``gain`` computed
+    inside the kernel (rows ``rows`` of x_f32 when given).  ``epilogue``: "store" stores y
+    [n, N] in the weights' dtype ("bf16" / "f32" name the dtype); "add" adds y into the
+    float32 ``out``; "swiglu" takes ``weight`` as gate and ``weight_up`` as up matrix and
+    stores silu(gate) * up [n, N] in the weights' dtype.
     ``prefetch``: a contiguous tensor that a later kernel will stream (the next weight
     matrix); the kernel asks for it to be brought into L2 before its own work.
     A width K too long for shared memory is taken in column slices, one launch each, when
@@ -568,6 +579,10 @@ def skinny_gemm(weight: torch.Tensor, *, x: Optional[torch.Tensor] = None, x_f32
     """
     _cuda(weight, x, x_f32, gain, rows, weight_up, out, prefetch)
     N, K = weight.shape
+    if epilogue == "store":
+        epilogue = "f32" if weight.dtype == torch.float32 else "bf16"
+    if weight.dtype == torch.float32:
+        return _skinny_gemm_f32(weight, x, x_f32, gain, eps, rows, n_rows, weight_up, epilogue, out)
     if weight.dtype != torch.bfloat16 or weight.stride(1) != 1 or weight.stride(0) % 8:
         raise KernelError("skinny_gemm: the weight must be bfloat16 with dense rows at a stride that is a multiple of 8")
     if weight_up is not None and weight_up.stride() != weight.stride():
@@ -616,6 +631,51 @@ def skinny_gemm(weight: torch.Tensor, *, x: Optional[torch.Tensor] = None, x_f32
                               ctypes.c_float(eps), _p(y16), _p(y32), ctypes.c_int64(out.stride(0)), pro, epi,
                               *_prefetch_args(prefetch), _stream())
     _check(lib, "skinny_gemm", rc)
+    return out
+
+
+def _skinny_gemm_f32(weight, x, x_f32, gain, eps, rows, n_rows, weight_up, epilogue, out):
+    """The float32 form of ``skinny_gemm`` (same arguments; no prefetch hint)."""
+    N, K = weight.shape
+    if weight.stride(1) != 1 or weight.stride(0) % 4:
+        raise KernelError("skinny_gemm: float32 weights need dense rows at a stride that is a multiple of 4")
+    if epilogue not in ("f32", "add", "swiglu"):
+        raise KernelError(f"skinny_gemm: float32 weights have no epilogue {epilogue!r}")
+    if x is not None:
+        n = x.shape[0]
+        if x.dtype != torch.float32 or x.stride(1) != 1 or x.shape[1] != K:
+            raise KernelError("skinny_gemm: x must be float32 [n, K] with dense rows")
+        if epilogue == "add" and out is not None and K > SKINNY_F32_MAX_WIDTH and K % 128 == 0 and n <= SKINNY_F32_MAX_ROWS:
+            parts = -(-K // SKINNY_F32_MAX_WIDTH)
+            width = -(-K // parts // 128) * 128
+            for lo in range(0, K, width):
+                hi = min(K, lo + width)
+                _skinny_gemm_f32(weight[:, lo:hi], x[:, lo:hi], None, None, 0.0, None, None, None, "add", out)
+            return out
+        src, pro, stride = x, 0, x.stride(0)
+    else:
+        _i32(rows, "rows")
+        n = n_rows if n_rows is not None else (rows.numel() if rows is not None else x_f32.shape[0])
+        if x_f32.dtype != torch.float32 or not x_f32.is_contiguous() or x_f32.shape[1] != K \
+                or gain.dtype != torch.float32 or gain.numel() != K:
+            raise KernelError("skinny_gemm: x_f32 [rows, K] and gain [K] must be contiguous float32")
+        src, pro, stride = x_f32, 1, K
+    if not skinny_fits(n, K, torch.float32):
+        raise KernelError(f"skinny_gemm: {n} float32 rows of width {K} are not supported")
+    if epilogue == "swiglu" and (weight_up is None or weight_up.shape != weight.shape or weight_up.dtype != torch.float32
+                                 or weight_up.stride() != weight.stride()):
+        raise KernelError("skinny_gemm: swiglu needs an up matrix like the gate matrix")
+    if out is None:
+        if epilogue == "add":
+            raise KernelError("skinny_gemm: 'add' needs the matrix to add into")
+        out = torch.empty((n, N), dtype=torch.float32, device=weight.device)
+    if out.dtype != torch.float32 or out.stride(1) != 1 or out.shape[0] < n or out.shape[1] != N:
+        raise KernelError("skinny_gemm: out has the wrong dtype or shape")
+    lib = load_library("skinny_gemm_f32")
+    rc = lib.kllm_skinny_gemm_f32(_p(weight), _p(weight_up), ctypes.c_int64(weight.stride(0)), N, K, n, _p(src),
+                                  ctypes.c_int64(stride), _p(gain), _p(rows), ctypes.c_float(eps), _p(out),
+                                  ctypes.c_int64(out.stride(0)), pro, {"f32": 0, "add": 1, "swiglu": 2}[epilogue], _stream())
+    _check(lib, "skinny_gemm_f32", rc)
     return out
 
 

@@ -157,7 +157,7 @@ class PagedAttention:
             q, k, v = self._split(kernels.linear(norm.forward(x, None), w), cache.writes)
             kernels.linear_add(x, self._attend(q, k, v, ctx, cache), self.w_o)
             return True
-        qkv = kernels.skinny_gemm(w, x_f32=x, gain=norm.gain, eps=norm.eps, epilogue="bf16")
+        qkv = kernels.skinny_gemm(w, x_f32=x, gain=norm.gain, eps=norm.eps, epilogue="store")
         q, k, v = self._split(qkv, cache.writes)
         attn = self._attend(q, k, v, ctx, cache, prefetch=self._target(0))
         kernels.skinny_gemm(self.w_o, x=attn, epilogue="add", out=x, prefetch=self._target(1))

@@ -637,6 +637,54 @@ def test_skinny_gemm_prologues_and_epilogues(n, N, K):
     close(got, plain.round_act_bf16(plain.rmsnorm(big[:n], gain, 1e-5)) @ ws.T, "bfloat16", "norm prologue, no gather")
 
 
+@pytest.mark.parametrize("n", [1, 3, 8])
+@pytest.mark.parametrize("N,K", [(48, 128), (2560, 2048), (101, 384), (2048, 5632), (33, 4096), (2, 256)])
+def test_float32_skinny_gemm_prologues_and_epilogues(n, N, K):
+    """The float32 path's weight-streaming product (true 32-bit FMAs on the CUDA cores)
+    against float64, and bit-equal rows whatever the number of rows in the call."""
+    from kllm_b200 import kernels
+    rng = np.random.default_rng(n * 1000 + N + K)
+    w = (rng.standard_normal((N, K)) * 0.05).astype(np.float32)
+    w2 = (rng.standard_normal((N, K)) * 0.05).astype(np.float32)
+    x = rng.standard_normal((n, K)).astype(np.float32)
+    wt, w2t, xt = dev(w), dev(w2), dev(x)
+    want = x.astype(np.float64) @ w.astype(np.float64).T
+    got = kernels.skinny_gemm(wt, x=xt, epilogue="store")
+    assert got.dtype == torch.float32
+    close(got, want, "float32", "store")
+    alone = kernels.skinny_gemm(wt, x=xt[n - 1:], epilogue="f32")
+    assert torch.equal(alone[0], got[n - 1]), "a row's sum must not depend on the other rows of the call"
+    base = rng.standard_normal((n, N)).astype(np.float32)
+    acc = dev(base)
+    kernels.skinny_gemm(wt, x=xt, epilogue="add", out=acc)
+    close(acc, base.astype(np.float64) + want, "float32", "residual add")
+    u = x.astype(np.float64) @ w2.astype(np.float64).T
+    close(kernels.skinny_gemm(wt, x=xt, weight_up=w2t, epilogue="swiglu"), plain.silu(want) * u, "float32", "swiglu")
+    big = (rng.standard_normal((n + 5, K)) * 2).astype(np.float32)
+    gain = (1 + 0.2 * rng.standard_normal(K)).astype(np.float32)
+    rows = rng.permutation(n + 5)[:n].astype(np.int32)
+    xn = plain.rmsnorm(big[rows], gain, 1e-5)
+    got = kernels.skinny_gemm(wt, x_f32=dev(big), gain=dev(gain), eps=1e-5, rows=dev(rows), epilogue="f32")
+    close(got, xn @ w.astype(np.float64).T, "float32", "norm prologue on gathered rows")
+    got = kernels.skinny_gemm(wt, weight_up=w2t, x_f32=dev(big[:n].copy()), gain=dev(gain), eps=1e-5, epilogue="swiglu")
+    xn = plain.rmsnorm(big[:n], gain, 1e-5)
+    close(got, plain.silu(xn @ w.astype(np.float64).T) * (xn @ w2.astype(np.float64).T), "float32", "norm -> swiglu")
+
+
+def test_float32_skinny_gemm_adds_a_long_k_in_slices():
+    from kllm_b200 import kernels
+    rng = np.random.default_rng(77)
+    n, N, K = 5, 50, 14336
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    x = rng.standard_normal((n, K)).astype(np.float32)
+    w[:, K - 1] = 0.5
+    x[:, K - 1] = 8.0
+    base = rng.standard_normal((n, N)).astype(np.float32)
+    acc = dev(base)
+    kernels.skinny_gemm(dev(w), x=dev(x), epilogue="add", out=acc)
+    close(acc, base.astype(np.float64) + x.astype(np.float64) @ w.astype(np.float64).T, "float32", "sliced residual add")
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (200, 264, 136), (77, 520, 72), (300, 96, 1000), (1000, 1544, 520)])
 @pytest.mark.parametrize("bn", [0, 256, 192, 64])
 def test_tcgen05_gemm_epilogues(M, N, K, bn):
@@ -699,6 +747,8 @@ def test_skinny_gemm_refusals():
     with pytest.raises(kernels.KernelError, match="not supported"):
         kernels.skinny_gemm(w, x=torch.zeros(17, 64, device="cuda", dtype=torch.bfloat16))
     assert not kernels.skinny_fits(8, 64, torch.float32) and kernels.skinny_fits(16, 5632, torch.bfloat16)
+    assert kernels.skinny_fits(8, 5632, torch.float32) and not kernels.skinny_fits(9, 2048, torch.float32)
+    assert not kernels.skinny_fits(8, 14336, torch.float32) and kernels.skinny_fits(8, 14336, torch.float32, sliced=True)
     assert not kernels.skinny_fits(16, 14336, torch.bfloat16)
     assert kernels.skinny_fits(16, 14336, torch.bfloat16, sliced=True)
     assert not kernels.skinny_fits(16, 14336 + 8, torch.bfloat16, sliced=True)
