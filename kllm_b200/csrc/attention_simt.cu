@@ -74,14 +74,22 @@ attn_simt_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restr
 
     // which request and which of its tiles this CTA has
     int tile = blockIdx.x, s = 0, n_new = 0;
-    bool found = false;
-    for (s = 0; s < n_requests; s++) {
-        n_new = q_start[s + 1] - q_start[s];
-        const int nt = (n_new + qt - 1) / qt;
-        if (tile < nt) { found = true; break; }
-        tile -= nt;
+    if (chunk > 0) {
+        // keys in chunks: the launcher vouches that every request brings one token, tile = request
+        s = tile;
+        tile = 0;
+        n_new = 1;
+        if (s >= n_requests) return;
+    } else {
+        bool found = false;
+        for (s = 0; s < n_requests; s++) {
+            n_new = q_start[s + 1] - q_start[s];
+            const int nt = (n_new + qt - 1) / qt;
+            if (tile < nt) { found = true; break; }
+            tile -= nt;
+        }
+        if (!found) return;
     }
-    if (!found) return;
     const int q0 = tile * qt;
     const int nq = min(qt, n_new - q0);
     const int gs = n_heads / n_kv, g = blockIdx.y, split = blockIdx.z;
@@ -124,21 +132,29 @@ attn_simt_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restr
         for (int c = 0; c < NC; c++) acc[i][c] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     const bool active = ty < R;                             // row ty exists; the thread's other rows may not
+    const int ri = (R + 15) >> 4;                           // row slots i < ri hold rows of this tile (the same for all threads)
 
     for (int key0 = lo; key0 < hi; key0 += KEYS) {
         __syncthreads();                                    // the tile before is no longer read
-        for (int e = tid; e < KEYS * hd4; e += THREADS) {
-            const int k = e / hd4, c = e - k * hd4;
-            const int kp = key0 + k;
-            float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
-            if (kp < hi) {
+        {
+            // four threads per key: one look-up of the key's page, then independent 16-byte loads
+            const int k = tid >> 2, kp = key0 + k;
+            const bool ok = kp < hi;
+            int64_t off = 0;
+            if (ok) {
                 const int lp = kp / page_size;
-                const int64_t off = (((int64_t)table[lp] * n_kv + g) * page_size + (kp - lp * page_size)) * hd + 4 * c;
-                kv = load4(kcache + off);
-                vv = load4(vcache + off);
+                off = (((int64_t)table[lp] * n_kv + g) * page_size + (kp - lp * page_size)) * hd;
             }
-            *reinterpret_cast<float4*>(Ks + k * ld + 4 * c) = kv;
-            *reinterpret_cast<float4*>(Vs + k * ld + 4 * c) = vv;
+#pragma unroll 4
+            for (int c = tid & 3; c < hd4; c += 4) {
+                float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
+                if (ok) {
+                    kv = load4(kcache + off + 4 * c);
+                    vv = load4(vcache + off + 4 * c);
+                }
+                *reinterpret_cast<float4*>(Ks + k * ld + 4 * c) = kv;
+                *reinterpret_cast<float4*>(Vs + k * ld + 4 * c) = vv;
+            }
         }
         __syncthreads();
 
@@ -151,11 +167,13 @@ attn_simt_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restr
             for (int d = 0; d < hd; d += 4) {
                 float4 qv[4], kv[4];
 #pragma unroll
-                for (int i = 0; i < 4; i++) qv[i] = *reinterpret_cast<const float4*>(Qs + (ty + 16 * i) * ld + d);
+                for (int i = 0; i < 4; i++)
+                    if (i < ri) qv[i] = *reinterpret_cast<const float4*>(Qs + (ty + 16 * i) * ld + d);
 #pragma unroll
                 for (int j = 0; j < 4; j++) kv[j] = *reinterpret_cast<const float4*>(Ks + (tx + 16 * j) * ld + d);
 #pragma unroll
                 for (int i = 0; i < 4; i++)
+                    if (i < ri)
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
                         sc[i][j] += qv[i].x * kv[j].x;
@@ -167,6 +185,7 @@ attn_simt_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restr
         }
 #pragma unroll
         for (int i = 0; i < 4; i++) {
+            if (i >= ri) break;
             bool vis[4];
             float mx = -INFINITY;
 #pragma unroll
@@ -203,7 +222,8 @@ attn_simt_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restr
             for (int k = 0; k < nk; k += 4) {
                 float4 p4[4];
 #pragma unroll
-                for (int i = 0; i < 4; i++) p4[i] = *reinterpret_cast<const float4*>(Ps + (ty + 16 * i) * PLD + k);
+                for (int i = 0; i < 4; i++)
+                    if (i < ri) p4[i] = *reinterpret_cast<const float4*>(Ps + (ty + 16 * i) * PLD + k);
 #pragma unroll
                 for (int kk = 0; kk < 4; kk++) {
 #pragma unroll
@@ -213,6 +233,7 @@ attn_simt_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restr
                             const float4 v = *reinterpret_cast<const float4*>(Vs + (k + kk) * ld + d);
 #pragma unroll
                             for (int i = 0; i < 4; i++) {
+                                if (i >= ri) break;
                                 const float pv = kk == 0 ? p4[i].x : kk == 1 ? p4[i].y : kk == 2 ? p4[i].z : p4[i].w;
                                 acc[i][c].x += pv * v.x; acc[i][c].y += pv * v.y;
                                 acc[i][c].z += pv * v.z; acc[i][c].w += pv * v.w;
@@ -251,7 +272,8 @@ attn_simt_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restr
     }
 }
 
-// One warp per (token, head): the chunks' partial results in chunk order.
+// One warp per (token, head): the chunks' partial results, weighted by exp(m_chunk - max)
+// and added in chunk order.
 template <typename T>
 __global__ void __launch_bounds__(128)
 attn_simt_merge_kernel(T* __restrict__ out, const float* __restrict__ part_o, const float* __restrict__ part_ml,
@@ -265,21 +287,38 @@ attn_simt_merge_kernel(T* __restrict__ out, const float* __restrict__ part_o, co
     const int p = positions[row / n_heads];
     const int lo_all = (window > 0 && p + 1 > window) ? p + 1 - window : 0;
     const int ns = (p + 1 - lo_all + chunk - 1) / chunk;
-    float M = -INFINITY, L = 0.f;
+    // the chunks' maxima first (all loads at once), then their weights, then the sums in chunk order
+    float M = -INFINITY;
+    for (int j0 = 0; j0 < ns; j0 += 32) {
+        const int j = j0 + lane;
+        const float mj = j < ns ? __ldcg(part_ml + (row * max_splits + j) * 2) : -INFINITY;
+        M = fmaxf(M, warp_max(mj));
+    }
+    float L = 0.f;
     float o[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) o[i] = 0.f;
-    for (int j = 0; j < ns; j++) {
-        const float2 ml = *reinterpret_cast<const float2*>(part_ml + (row * max_splits + j) * 2);
-        const float* po = part_o + (row * max_splits + j) * hd;
-        const float m_new = fmaxf(M, ml.x);
-        const float a = expf(M - m_new), b = expf(ml.x - m_new);
-        L = L * a + ml.y * b;
-        M = m_new;
+    for (int j0 = 0; j0 < ns; j0 += 4) {
+        float2 ml[4];
+        float po[4][8];
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int d = lane + 32 * i;
-            if (d < hd) o[i] = o[i] * a + po[d] * b;
+        for (int u = 0; u < 4; u++) {
+            const int j = min(j0 + u, ns - 1);
+            ml[u] = __ldcg(reinterpret_cast<const float2*>(part_ml + (row * max_splits + j) * 2));
+            const float* src = part_o + (row * max_splits + j) * hd;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int d = lane + 32 * i;
+                po[u][i] = d < hd ? __ldcg(src + d) : 0.f;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            if (j0 + u >= ns) break;
+            const float b = expf(ml[u].x - M);
+            L += ml[u].y * b;
+#pragma unroll
+            for (int i = 0; i < 8; i++) o[i] += po[u][i] * b;
         }
     }
     const float inv = 1.f / L;

@@ -4,8 +4,8 @@
 // The reference runs these products through cublasSgemm (backend/model.cu:496-503,
 // :1090-1115); at a few rows the library picks matrix-vector kernels by the row count,
 // which stream at a fraction of the memory's speed and sum in an order that depends on
-// the batch.  Here every output element is one warp's sum in an order that depends on K
-// alone.  Prologues and epilogues as in skinny_gemm.cu:
+// the batch.  Here every output element is summed in an order that depends on K alone.
+// Prologues and epilogues as in skinny_gemm.cu:
 //
 //   prologue  X_PLAIN     X is a float32 matrix [n, K]
 //             X_NORM      X = rmsnorm(x) * gain of float32 rows x (optionally gathered by
@@ -16,19 +16,24 @@
 //                         silu(gate row) * (up row) as float32 [n, F]
 //                         (backend/model.cu:477-483, :1112-1114)
 //
-// Layout of the work: a CTA of 16 warps, one per SM, keeps X in shared memory.  A warp
-// takes four weight rows at a time (SWIGLU: two gate rows and their two up rows); its
-// lanes split K in interleaved float4 pieces, so a lane's X values (8 rows x float4, read
-// once per k step) serve all four weight rows from registers.  The lanes' partial sums
-// meet in a butterfly of shuffles whose order is fixed.
+// Layout of the work: a CTA of 16 warps, one per SM, keeps X in shared memory.  A tile is
+// eight weight rows (SWIGLU: four gate rows and their four up rows).  The warps of a CTA
+// are two row groups (four rows each) times eight k slices: a warp takes the k steps of
+// 128 elements of its slice, its lanes split a step in float4 pieces, so a lane's X values
+// (8 rows x float4, read once per k step) serve its four weight rows from registers.  Two
+// register buffers take turns, so the next step's (or the next tile's) weights are in
+// flight while this one's are multiplied.  The lanes' partial sums meet in a butterfly of
+// shuffles, the eight slices' sums in shared memory, added in slice order: every order is
+// fixed by K alone.
 #include "common.cuh"
 
 KLLM_EXPORT_LAST_ERROR(skinny_gemm_f32)
 
 namespace {
 
-constexpr int THREADS = 512, WARPS = 16, ROWS = 8, WR = 4;      // X rows; weight rows per warp and pass
-constexpr int UNROLL = 2;                                       // k steps of 128 in flight per lane
+constexpr int THREADS = 512, WARPS = 16, ROWS = 8, WR = 4;      // X rows; weight rows per warp
+constexpr int KSLICES = 8, GROUPS = 2;                          // the 16 warps: k slices x row groups
+constexpr int UNROLL = 2;                                       // k steps of 128 per register buffer
 enum { X_PLAIN = 0, X_NORM = 1 };
 enum { STORE = 0, ADD = 1, SWIGLU = 2 };
 
@@ -58,32 +63,35 @@ __global__ void __launch_bounds__(THREADS, 1)
 skinny_f32_kernel(const Args a) {
     extern __shared__ __align__(16) float xs[];            // [ROWS][K]
     __shared__ float ss_part[ROWS][2];
+    __shared__ float red[KSLICES * GROUPS * 32];           // per warp: its 4 rows x 8 tokens
     const int K = a.K, N = a.N, n = a.n;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    constexpr int OUT_PER_TILE = EPI == SWIGLU ? 2 : WR;   // output columns of a warp's pass
+    const int grp = warp & 1, ks = warp >> 1;
+    constexpr int OUT_PER_TILE = EPI == SWIGLU ? WR : GROUPS * WR;   // output columns of a tile
     const int n_tiles = (N + OUT_PER_TILE - 1) / OUT_PER_TILE;
     const int steps = K / 128;
+    const int my_steps = steps > ks ? (steps - ks + KSLICES - 1) / KSLICES : 0;
+    const int nb = max(1, ((steps + KSLICES - 1) / KSLICES + UNROLL - 1) / UNROLL);   // batches per tile, same for all warps
 
-    // the four weight rows of a tile (rows past the end repeat the last one; their sums are not stored)
+    // this warp's four weight rows of a tile (rows past the end repeat the last one; their sums are not stored)
     auto row_ptr = [&](int tile, int r) -> const float* {
-        if (EPI == SWIGLU) {
-            const int col = min(tile * 2 + (r & 1), N - 1);
-            return (r < 2 ? a.w : a.w_up) + (int64_t)col * a.w_stride + 4 * lane;
-        }
-        return a.w + (int64_t)min(tile * WR + r, N - 1) * a.w_stride + 4 * lane;
+        if (EPI == SWIGLU) return (grp == 0 ? a.w : a.w_up) + (int64_t)min(tile * WR + r, N - 1) * a.w_stride + 4 * lane;
+        return a.w + (int64_t)min(tile * GROUPS * WR + grp * WR + r, N - 1) * a.w_stride + 4 * lane;
     };
-    int tile = blockIdx.x * WARPS + warp;
-    const int tile_step = gridDim.x * WARPS;
-    float4 wbuf[UNROLL][WR];
-    auto load_w = [&](int t, int s0) {
+    float4 buf0[UNROLL][WR], buf1[UNROLL][WR];
+    auto load_batch = [&](float4 (&buf)[UNROLL][WR], int tile, int b) {
 #pragma unroll
-        for (int u = 0; u < UNROLL; u++)
-            if (s0 + u < steps) {
+        for (int u = 0; u < UNROLL; u++) {
+            const int i = b * UNROLL + u;
+            if (i < my_steps) {
+                const int off = (ks + i * KSLICES) * 128;
 #pragma unroll
-                for (int r = 0; r < WR; r++) wbuf[u][r] = ldg_stream(row_ptr(t, r) + (s0 + u) * 128);
+                for (int r = 0; r < WR; r++) buf[u][r] = ldg_stream(row_ptr(tile, r) + off);
             }
+        }
     };
-    if (tile < n_tiles) load_w(tile, 0);           // weights do not depend on X: on their way first
+    int cur_tile = blockIdx.x, cur_b = 0;          // the batch that sits in the buffer used next
+    if (cur_tile < n_tiles) load_batch(buf0, cur_tile, 0);     // weights do not depend on X: on their way first
     griddep_wait();
     griddep_launch();
 
@@ -123,61 +131,85 @@ skinny_f32_kernel(const Args a) {
     __syncthreads();
 
     // ---- tiles ----
-    for (; tile < n_tiles; tile += tile_step) {
-        float acc[WR][ROWS];
+    float acc[WR][ROWS];
 #pragma unroll
-        for (int r = 0; r < WR; r++)
+    for (int r = 0; r < WR; r++)
 #pragma unroll
-            for (int c = 0; c < ROWS; c++) acc[r][c] = 0.f;
-        for (int s0 = 0; s0 < steps; s0 += UNROLL) {
-            float4 wcur[UNROLL][WR];
+        for (int c = 0; c < ROWS; c++) acc[r][c] = 0.f;
+
+    // multiply the batch (cur_tile, cur_b) held in `cur` while the following batch loads into `nxt`
+    auto phase = [&](float4 (&cur)[UNROLL][WR], float4 (&nxt)[UNROLL][WR]) {
+        int nxt_tile = cur_tile, nxt_b = cur_b + 1;
+        if (nxt_b == nb) { nxt_b = 0; nxt_tile += gridDim.x; }
+        if (nxt_tile < n_tiles) load_batch(nxt, nxt_tile, nxt_b);
 #pragma unroll
-            for (int u = 0; u < UNROLL; u++)
-#pragma unroll
-                for (int r = 0; r < WR; r++) wcur[u][r] = wbuf[u][r];
-            // the next k steps of this tile, or the first of the warp's next tile
-            if (s0 + UNROLL < steps) load_w(tile, s0 + UNROLL);
-            else if (tile + tile_step < n_tiles) load_w(tile + tile_step, 0);
-#pragma unroll
-            for (int u = 0; u < UNROLL; u++) {
-                if (s0 + u >= steps) break;
-                const int k = (s0 + u) * 128 + 4 * lane;
+        for (int u = 0; u < UNROLL; u++) {
+            const int i = cur_b * UNROLL + u;
+            if (i < my_steps) {
+                const int k = (ks + i * KSLICES) * 128 + 4 * lane;
 #pragma unroll
                 for (int c = 0; c < ROWS; c++) {
                     const float4 xv = *reinterpret_cast<const float4*>(xs + (size_t)c * K + k);
 #pragma unroll
                     for (int r = 0; r < WR; r++) {
-                        acc[r][c] = fmaf(wcur[u][r].x, xv.x, acc[r][c]);
-                        acc[r][c] = fmaf(wcur[u][r].y, xv.y, acc[r][c]);
-                        acc[r][c] = fmaf(wcur[u][r].z, xv.z, acc[r][c]);
-                        acc[r][c] = fmaf(wcur[u][r].w, xv.w, acc[r][c]);
+                        acc[r][c] = fmaf(cur[u][r].x, xv.x, acc[r][c]);
+                        acc[r][c] = fmaf(cur[u][r].y, xv.y, acc[r][c]);
+                        acc[r][c] = fmaf(cur[u][r].z, xv.z, acc[r][c]);
+                        acc[r][c] = fmaf(cur[u][r].w, xv.w, acc[r][c]);
                     }
                 }
             }
         }
-        // the lanes' partial sums, in a fixed butterfly; lane r * 8 + c keeps output (r, c)
-        float mine = 0.f, partner = 0.f;
+        if (cur_b == nb - 1) {
+            // The lanes' partial sums: 32 values on 32 lanes are summed by halving (each step a
+            // lane hands half of its values to the partner lane and adds what it is handed), so
+            // that lane r * 8 + c ends with the warp's sum of (row r, token c): 31 shuffles instead
+            // of 160, in a fixed order.
+            float v[WR * ROWS];
 #pragma unroll
-        for (int r = 0; r < WR; r++)
+            for (int r = 0; r < WR; r++)
 #pragma unroll
-            for (int c = 0; c < ROWS; c++) {
-                const float v = warp_sum(acc[r][c]);
-                if (lane == r * ROWS + c) mine = v;
-                if (EPI == SWIGLU && lane + 2 * ROWS == r * ROWS + c) partner = v;     // the up row of this gate row
-            }
-        const int r = lane / ROWS, c = lane % ROWS;
-        if (c < n) {
-            if (EPI == SWIGLU) {
-                const int col = tile * 2 + r;
-                if (r < 2 && col < N) a.y[(int64_t)c * a.y_stride + col] = (mine / (1.f + expf(-mine))) * partner;
-            } else {
-                const int col = tile * WR + r;
-                if (col < N) {
-                    float* dst = a.y + (int64_t)c * a.y_stride + col;
-                    if (EPI == ADD) *dst += mine; else *dst = mine;
+                for (int c = 0; c < ROWS; c++) { v[r * ROWS + c] = acc[r][c]; acc[r][c] = 0.f; }
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) {
+                const bool upper = (lane & o) != 0;
+#pragma unroll
+                for (int j = 0; j < o; j++) {
+                    const float send = upper ? v[j] : v[j + o];
+                    const float keep = upper ? v[j + o] : v[j];
+                    v[j] = keep + __shfl_xor_sync(0xffffffffu, send, o);
                 }
             }
+            const float mine = v[0];
+            red[warp * 32 + lane] = mine;              // warp = ks * GROUPS + grp
+            __syncthreads();
+            const int tile = cur_tile;
+            if (threadIdx.x < (EPI == SWIGLU ? 32 : 64)) {
+                const int e = threadIdx.x, g2 = e >> 5, rc = e & 31, r = rc / ROWS, c = rc % ROWS;
+                float v = 0.f, up = 0.f;
+#pragma unroll
+                for (int q = 0; q < KSLICES; q++) v += red[(q * GROUPS + g2) * 32 + rc];      // the slices, in order
+                if (EPI == SWIGLU) {
+#pragma unroll
+                    for (int q = 0; q < KSLICES; q++) up += red[(q * GROUPS + 1) * 32 + rc];
+                }
+                const int col = EPI == SWIGLU ? tile * WR + r : tile * GROUPS * WR + g2 * WR + r;
+                if (c < n && col < N) {
+                    float* dst = a.y + (int64_t)c * a.y_stride + col;
+                    if (EPI == SWIGLU) *dst = (v / (1.f + expf(-v))) * up;
+                    else if (EPI == ADD) *dst += v;
+                    else *dst = v;
+                }
+            }
+            __syncthreads();
         }
+        cur_tile = nxt_tile;
+        cur_b = nxt_b;
+    };
+    while (cur_tile < n_tiles) {
+        phase(buf0, buf1);
+        if (cur_tile >= n_tiles) break;
+        phase(buf1, buf0);
     }
 }
 
@@ -198,10 +230,10 @@ int launch(const Args& a, cudaStream_t s) {
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int out_per_tile = EPI == SWIGLU ? 2 : WR;
+    const int out_per_tile = EPI == SWIGLU ? WR : GROUPS * WR;
     const int n_tiles = (a.N + out_per_tile - 1) / out_per_tile;
-    const int grid = max(1, min((n_tiles + WARPS - 1) / WARPS, max(1, sms)));
-    kllm_launch_dep(n_tiles <= 3 * grid * WARPS, (kern), dim3(grid), dim3(THREADS), smem, s, a);
+    const int grid = max(1, min(n_tiles, max(1, sms)));
+    kllm_launch_dep(n_tiles <= 3 * grid, (kern), dim3(grid), dim3(THREADS), smem, s, a);
     KLLM_LAUNCH_STATUS();
 }
 
