@@ -230,9 +230,10 @@ def main():
     ap.add_argument("--repeats", type=int, default=0, help="how often the K-step region is timed (0: 5, or 3 for K > 40)")
     ap.add_argument("--prefill-tokens", type=int, default=2048, help="length of the timed prompt")
     ap.add_argument("--no-points", action="store_true", help="skip the further points and the prefill")
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "attention"],
                     help="decode: the batch's decode run alone; prefill: the 2048-token prompt alone (partial "
-                         "records for profiling small cases, not the bench line)")
+                         "records for profiling small cases, not the bench line); attention: the tcgen05 attention "
+                         "kernels of prompt portions alone, both forms, at a few shapes")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
     ap.add_argument("--timeline", action="store_true",
                     help="decode run with the instrumented kernel builds; prints where the last step's time went, "
@@ -261,6 +262,8 @@ def main():
 
     if args.workload:
         return mixed_workload(args)
+    if args.only == "attention":
+        return attention_forms()
 
     cfg = dict(SHAPES[args.shape])
     cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], args.context, args.prefill_tokens)
@@ -482,6 +485,51 @@ def main():
     finally:
         if tmp is not None:
             shutil.rmtree(tmp, ignore_errors=True)
+
+
+def attention_forms():
+    """The two tcgen05 attention kernels of prompt portions (probabilities through shared
+    memory / kept in tensor memory) alone, on random caches: microseconds per call and
+    TFLOP/s of the causal work, by CUDA events over calls on alternating caches larger than
+    L2 in sum.  One JSON record."""
+    import math
+    import torch
+    from kllm_b200 import kernels
+    dev, page, layers, reps = "cuda", 64, 6, 10
+    rows = []
+    for n_req, per, H, G, hd in ((1, 2048, 32, 4, 64), (1, 8192, 32, 4, 64), (8, 512, 32, 4, 64), (1, 512, 32, 4, 64),
+                                 (1, 2048, 32, 8, 128), (1, 8192, 32, 8, 128), (1, 8192, 32, 32, 128)):
+        T = n_req * per
+        n_pages = n_req * (-(-per // page))
+        caches = [(torch.randn(n_pages, G, page, hd, device=dev).bfloat16(),
+                   torch.randn(n_pages, G, page, hd, device=dev).bfloat16()) for _ in range(layers)]
+        table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(n_req, -1).contiguous()
+        q = torch.randn(T, H * hd, device=dev).bfloat16()
+        out = torch.empty_like(q)
+        q_start = torch.arange(0, T + 1, per, dtype=torch.int32, device=dev)
+        start_pos = torch.zeros(n_req, dtype=torch.int32, device=dev)
+        rec = {"portions": n_req, "tokens_each": per, "heads": H, "kv_heads": G, "head_dim": hd}
+        for form in ("smem", "tmem"):
+            def call(i):
+                kernels.attention_prefill_tcgen05(out, q, caches[i][0], caches[i][1], q_start, start_pos, table, n_req,
+                                                  H, G, hd, 0, 1.0 / math.sqrt(hd), probabilities=form)
+            for i in range(layers):
+                call(i)
+            torch.cuda.synchronize()
+            kernels.check_status(dev)
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+            for _ in range(reps):
+                for i in range(layers):
+                    call(i)
+            ev1.record()
+            torch.cuda.synchronize()
+            us = ev0.elapsed_time(ev1) / (reps * layers) * 1e3
+            rec[form] = {"us": round(us, 1), "tflops": round(2.0 * per * per * H * hd * n_req / us / 1e6, 1)}
+        rows.append(rec)
+        del caches
+    print(json.dumps({"partial": "tcgen05 attention of prompt portions, both forms", "rows": rows}))
+    return 0
 
 
 def mixed_workload(args):
