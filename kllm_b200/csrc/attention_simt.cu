@@ -14,7 +14,9 @@
 // Formulas as the reference computes them (backend/model.cu:343-408): a query at
 // absolute position p sees keys [max(0, p + 1 - window), p], the keys of its own step
 // having been written before; score = (q . k) * scale, scale applied after the dot
-// (:376); max-subtracted expf; one division by the sum at the end (:395-406).
+// (:376); max-subtracted expf; one division by the sum at the end (:395-406).  Optionally a
+// bias that is linear in the distance is added to every score, slope[head] * (key position -
+// query position): position encodings that act on the scores instead of on q and k.
 //
 // Steps of single tokens (decode) have few rows per kv head and long contexts; there the
 // keys of a token are cut into chunks of `chunk` keys, one CTA each (grid.z), which store
@@ -62,7 +64,8 @@ attn_simt_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restr
                  const T* __restrict__ q, int64_t q_stride, const T* __restrict__ kcache,
                  const T* __restrict__ vcache, const int* __restrict__ q_start, const int* __restrict__ start_pos,
                  const int* __restrict__ block_table, int max_blocks, int n_requests, int n_heads, int n_kv, int hd,
-                 int page_size, int window, float scale, int qt, int chunk, int max_splits) {
+                 int page_size, int window, float scale, int qt, int chunk, int max_splits,
+                 const float* __restrict__ slopes) {
     extern __shared__ __align__(16) float sm[];
     const int ld = hd + 4;
     float* Qs = sm;
@@ -118,7 +121,7 @@ attn_simt_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restr
         *reinterpret_cast<float4*>(Qs + r * ld + 4 * c) = v;
     }
 
-    float m[4], l[4];
+    float m[4], l[4], slope[4];
     int pos[4], wlo[4];
     float4 acc[4][NC];
 #pragma unroll
@@ -127,6 +130,7 @@ attn_simt_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restr
         l[i] = 0.f;
         const int r = ty + 16 * i;
         pos[i] = r < R ? p0 + r / gs : -1;                  // -1: no key is visible to a row that does not exist
+        slope[i] = (slopes && r < R) ? slopes[g * gs + r % gs] : 0.f;
         wlo[i] = window > 0 ? pos[i] + 1 - window : 0;
 #pragma unroll
         for (int c = 0; c < NC; c++) acc[i][c] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -192,7 +196,7 @@ attn_simt_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restr
             for (int j = 0; j < 4; j++) {
                 const int kp = key0 + tx + 16 * j;
                 vis[j] = kp < hi && kp <= pos[i] && kp >= wlo[i];
-                sc[i][j] = vis[j] ? sc[i][j] * scale : -INFINITY;
+                sc[i][j] = vis[j] ? sc[i][j] * scale + slope[i] * (float)(kp - pos[i]) : -INFINITY;
                 mx = fmaxf(mx, sc[i][j]);
             }
             mx = half_warp_max(mx);
@@ -335,7 +339,7 @@ template <typename T, int NC>
 int launch(void* out, float* part_o, float* part_ml, const void* q, int64_t q_stride, const void* kcache,
            const void* vcache, const int* q_start, const int* start_pos, const int* block_table, int max_blocks,
            int n_requests, int max_tiles, int n_heads, int n_kv, int hd, int page_size, int window, float scale,
-           int qt, int chunk, int max_splits, cudaStream_t s) {
+           int qt, int chunk, int max_splits, const float* slopes, cudaStream_t s) {
     auto kern = attn_simt_kernel<T, NC>;
     static bool raised = false;
     const size_t smem = smem_bytes(hd);
@@ -349,7 +353,7 @@ int launch(void* out, float* part_o, float* part_ml, const void* q, int64_t q_st
     }
     kllm_launch(kern, dim3(max_tiles, n_kv, chunk > 0 ? max_splits : 1), dim3(THREADS), smem, s, (T*)out, part_o,
                 part_ml, (const T*)q, q_stride, (const T*)kcache, (const T*)vcache, q_start, start_pos, block_table,
-                max_blocks, n_requests, n_heads, n_kv, hd, page_size, window, scale, qt, chunk, max_splits);
+                max_blocks, n_requests, n_heads, n_kv, hd, page_size, window, scale, qt, chunk, max_splits, slopes);
     KLLM_LAUNCH_STATUS();
 }
 
@@ -363,11 +367,13 @@ int launch(void* out, float* part_o, float* part_ml, const void* q, int64_t q_st
 // qt == 1): the keys of a token are cut into chunks of that many keys, at most
 // max_splits of them, whose partial results go to part_o [rows, max_splits, hd] and
 // part_ml [rows, max_splits, 2] (row = token * n_heads + head) for kllm_attention_simt_merge.
+// slopes: optional float32 [n_heads]; slope[h] * (key position - query position) is added to
+// the scaled scores of head h.
 extern "C" int kllm_attention_simt(void* out, void* part_o, void* part_ml, const void* q, int64_t q_stride,
                                    const void* kcache, const void* vcache, const int* q_start, const int* start_pos,
                                    const int* block_table, int max_blocks, int n_requests, int max_tiles,
                                    int n_heads, int n_kv, int hd, int page_size, int window, float scale, int qt,
-                                   int chunk, int max_splits, int dtype, void* stream) {
+                                   int chunk, int max_splits, const float* slopes, int dtype, void* stream) {
     if (n_requests <= 0 || max_tiles <= 0) return 0;
     if (hd <= 0 || hd > 256 || hd % 4) KLLM_FAIL("attention (simt): head size %d is not a multiple of 4 up to 256", hd);
     if (n_kv <= 0 || n_heads % n_kv) KLLM_FAIL("attention (simt): %d heads over %d kv heads", n_heads, n_kv);
@@ -383,7 +389,7 @@ extern "C" int kllm_attention_simt(void* out, void* part_o, void* part_ml, const
 #define KLLM_SIMT(T, NC)                                                                                              \
     return launch<T, NC>(out, (float*)part_o, (float*)part_ml, q, q_stride, kcache, vcache, q_start, start_pos,      \
                          block_table, max_blocks, n_requests, max_tiles, n_heads, n_kv, hd, page_size, window, scale, \
-                         qt, chunk, max_splits, s)
+                         qt, chunk, max_splits, slopes, s)
     if (dtype == KLLM_F32) {
         if (hd <= 64) KLLM_SIMT(float, 1);
         if (hd <= 128) KLLM_SIMT(float, 2);

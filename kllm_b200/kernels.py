@@ -177,13 +177,18 @@ SIMT_CHUNK = 256      # keys per CTA when a decoding token's context is cut (att
 
 def attention_simt(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, ctx,
                    block_table: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, window: int,
-                   scale: float) -> None:
+                   scale: float, score_slopes: Optional[torch.Tensor] = None) -> None:
     """Causal GQA attention of the step's tokens on the CUDA cores, float32 arithmetic
     (csrc/attention_simt.cu): the attention of the float32 path.  The requests that bring
     one token each at the head of the batch (decoding requests, which the scheduler puts
     first) have their contexts cut into chunks of SIMT_CHUNK keys, one CTA each, merged in
-    chunk order; the portions after them run as tiles of up to 64 (token, head) rows."""
-    _cuda(out, q, kcache, vcache, block_table)
+    chunk order; the portions after them run as tiles of up to 64 (token, head) rows.
+    ``score_slopes`` (float32 [n_heads]): slope[h] * (key position - query position) is added
+    to the scaled scores of head h."""
+    _cuda(out, q, kcache, vcache, block_table, score_slopes)
+    if score_slopes is not None and (score_slopes.dtype != torch.float32 or not score_slopes.is_contiguous()
+                                     or score_slopes.numel() != n_heads):
+        raise KernelError("attention: score slopes must be a contiguous float32 tensor, one per head")
     _i32(block_table, "block_table"); _i32(ctx.q_start, "q_start"); _i32(ctx.start_pos, "start_pos")
     if q.stride(1) != 1 or not out.is_contiguous() or out.dtype != q.dtype or kcache.dtype != q.dtype:
         raise KernelError("attention: operands must share a dtype; out contiguous, q rows dense")
@@ -209,7 +214,7 @@ def attention_simt(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vca
         rc = lib.kllm_attention_simt(_p(out), _p(part_o), _p(part_ml), _p(q), ctypes.c_int64(q.stride(0)), _p(kcache),
                                      _p(vcache), _p(ctx.q_start), _p(ctx.start_pos), _p(block_table),
                                      block_table.shape[1], singles, singles, *common, 1, SIMT_CHUNK, splits,
-                                     dtype_code(q.dtype), _stream())
+                                     _p(score_slopes), dtype_code(q.dtype), _stream())
         _check(lib, "attention_simt", rc)
         rc = lib.kllm_attention_simt_merge(_p(out), _p(part_o), _p(part_ml), _p(ctx.positions), singles, n_heads,
                                            head_dim, int(window or 0), SIMT_CHUNK, splits, dtype_code(q.dtype), _stream())
@@ -221,7 +226,7 @@ def attention_simt(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vca
         rc = lib.kllm_attention_simt(_p(out), None, None, _p(q), ctypes.c_int64(q.stride(0)), _p(kcache), _p(vcache),
                                      _p(ctx.q_start[first:]), _p(ctx.start_pos[first:]), _p(block_table[first:]),
                                      block_table.shape[1], n_req - first, rest // qt + (n_req - first), *common, qt, 0, 1,
-                                     dtype_code(q.dtype), _stream())
+                                     _p(score_slopes), dtype_code(q.dtype), _stream())
         _check(lib, "attention_simt", rc)
 
 
@@ -271,7 +276,7 @@ def decode_splits(n_tokens: int, n_kv: int, ctx_bound: int) -> int:
 
 def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, ctx,
               block_table: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, window: int,
-              scale: float) -> None:
+              scale: float, score_slopes: Optional[torch.Tensor] = None) -> None:
     """Causal GQA attention of the step's tokens over the paged cache, by the
     kernel that fits: bfloat16 with a head size in TC_HEAD_DIMS runs on tensor cores
     (the decode form when every request brings one token, else the prefill form: on
@@ -281,8 +286,16 @@ def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: 
     step whose first requests bring one token each (the scheduler puts decoding requests
     first) is cut in two: those tokens take the decode form, which spreads a long context
     over many CTAs, the portions after them the prefill form, in which a single token
-    would walk its whole context with one CTA of 128 rows, 127 of them idle."""
+    would walk its whole context with one CTA of 128 rows, 127 of them idle.
+    ``score_slopes`` (a bias on the scores that is linear in the distance, per head) is
+    taken by the CUDA-core kernel only; the tensor-core kernels have no such argument."""
     group = n_heads // max(1, n_kv)
+    if score_slopes is not None:
+        if not simt_fits(q, n_heads, n_kv, head_dim):
+            raise KernelError("attention: a bias on the scores needs a head size that is a multiple of 4 up to 256, "
+                              "at most 64 heads per kv head and rows aligned to four elements")
+        return attention_simt(out, q, kcache, vcache, ctx, block_table, n_heads, n_kv, head_dim, window, scale,
+                              score_slopes)
     tc = q.dtype == torch.bfloat16 and head_dim in TC_HEAD_DIMS
     if tc and ctx.all_single and group <= 16:
         return attention_decode(out, q, kcache, vcache, ctx.positions, ctx.token_req, block_table, n_heads,

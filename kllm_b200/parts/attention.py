@@ -9,7 +9,11 @@ and keys before the position encoding, such as a norm per head or a bias; interf
 ``tensor_specs()``, ``bind(tensors)``, ``apply(q, k, ctx, n_heads, n_kv_heads,
 head_dim)`` which changes q [n, H*hd] and k [n, G*hd] (None when the layer reads
 another layer's cache) in place; with one, a decode step takes the separate rotary
-and attention kernels, since the fused kernel rotates the raw projections itself).
+and attention kernels, since the fused kernel rotates the raw projections itself),
+``score_slopes`` (a list of one float per head, None for Llama: slope[h] * (key
+position - query position) is added to the scaled scores, the form of position
+encodings that act on the scores; such a layer runs the CUDA-core attention kernel, the
+only one that takes the argument).
 Tensors: ``<prefix>.{q,k,v,o}_proj.weight`` with shapes [H*hd, d], [G*hd, d],
 [G*hd, d], [d, H*hd]; no bias (reference backend/model.cu:1090-1104).  At bind time
 q, k and v are stacked into one [(H+2G)*hd, d] matrix so the three projections are
@@ -58,6 +62,11 @@ class PagedAttention:
         self.position = part_factory("position", pos.kind)(pos, env) if pos is not None else None
         qt = p.get("qk_transform")
         self.qk_transform = part_factory("qk_transform", qt.kind)(qt, env) if qt is not None else None
+        slopes = p.get("score_slopes")
+        if slopes is not None and len(slopes) != self.n_heads:
+            raise ValueError(f"score_slopes: {len(slopes)} values for {self.n_heads} heads")
+        self.score_slopes = None if slopes is None else torch.tensor([float(v) for v in slopes], dtype=torch.float32,
+                                                                     device=env.device)
         self.w_qkv = None
         self.w_o = None
         # Zeroed scratch of the fused decode kernel, which leaves it zero.  A captured decode
@@ -117,6 +126,8 @@ class PagedAttention:
         if self.qk_transform is not None:
             self.qk_transform.apply(q, k if cache.writes else None, ctx, self.n_heads, self.n_kv, self.head_dim)
             table = None          # the fused decode kernel takes the raw projections
+        if self.score_slopes is not None:
+            table = None          # ... and has no bias on its scores
         if (table is not None and cache.writes and ctx.all_single and self.dtype == torch.bfloat16 and group <= 16
                 and self.head_dim in kernels.TC_HEAD_DIMS and self.head_dim % 32 == 0):
             # decode: rotary encoding, cache write and attention in one kernel
@@ -137,7 +148,7 @@ class PagedAttention:
                                 cache.k, cache.v, self.n_heads, self.n_kv, self.head_dim)
         attn = torch.empty((n, self.q_dim), dtype=self.dtype, device=q.device)
         kernels.attention(attn, q, cache.k, cache.v, ctx, cache.block_table, self.n_heads, self.n_kv,
-                          self.head_dim, self.window or 0, self.scale)
+                          self.head_dim, self.window or 0, self.scale, score_slopes=self.score_slopes)
         return attn
 
     def forward(self, xn, ctx, cache):

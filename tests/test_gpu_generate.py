@@ -194,6 +194,25 @@ def test_command_line(tmp_path):
                          capture_output=True, text=True, timeout=300)
     assert rnd.returncode == 0, rnd.stderr
     assert os.path.exists(tmp_path / "r" / "model.safetensors") and "generated: [" in rnd.stdout
+    # the cache sized from a byte budget: 2 layers x (k, v) x 2 kv heads x 16 slots x 16 dims x 4 bytes = 8 KiB a page
+    sized = subprocess.run(cmd + ["--cache-gb", "0.0001"], capture_output=True, text=True, timeout=300)
+    assert sized.returncode == 0, sized.stderr
+    assert sized.stdout == out.stdout              # 12 pages hold the 11 tokens; same tokens as with the default pool
+    small = subprocess.run(cmd + ["--cache-gb", "0.000001"], capture_output=True, text=True, timeout=300)
+    assert small.returncode != 0 and "holds no page" in small.stderr
+
+
+def test_cache_pool_from_a_byte_budget(tmp_path):
+    from kllm_b200.engine import Engine, Options
+    cfg, w = make_weights("B", "bfloat16")
+    d = write_model_dir(str(tmp_path / "m"), cfg, w)
+    eng = Engine(d, Options(dtype="bfloat16", max_seq=64, block_size=16, cache_bytes=100_000))
+    per = 3 * 2 * 1 * 16 * 32 * 2                  # layers x (k, v) x kv heads x slots x dims x bytes
+    assert eng.cache.bytes_per_page() == per and eng.cache.num_pages == 100_000 // per == 16
+    assert eng.cache.groups[0].storage.numel() * 2 == 16 * per
+    out = eng.generate(prompts_for(cfg, [20], seed=4)[0], max_new_tokens=5)
+    assert len(out) >= 1
+    eng.close()
 
 
 def test_a_captured_decode_graph_survives_a_larger_batch(tmp_path):

@@ -724,3 +724,52 @@ def test_attention_part_with_a_qk_transform_registered_from_outside(dtype):
     q, k = rnd(plain.rope(q, np.arange(n), H, hd, theta)), rnd(plain.rope(k, np.arange(n), G, hd, theta))
     att = rnd(plain.attention(q, k, v, H, G, hd, rnd_p=None if dtype == "float32" else rnd))
     close(xs, x + att @ ws["a.o_proj.weight"].T, dtype, "attention with a q/k norm per head")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window", [None, 300])
+def test_attention_part_with_a_bias_on_the_scores_instead_of_a_rotation(dtype, window):
+    """A position encoding that acts on the scores: slope[h] * (key position - query position)
+    added to the scaled scores, no rotation of q and k.  The part takes the CUDA-core
+    attention kernel (the tensor-core kernels have no such argument): a portion of 290
+    tokens, then single tokens whose contexts are cut into chunks of 256 keys and merged."""
+    from kllm_b200.cache import CacheManager
+    from kllm_b200.parts.spec import PartSpec, part_factory
+    rng = np.random.default_rng(31)
+    d, H, G, hd, n = 64, 4, 2, 32, 300
+    slopes = [2.0 ** -(h + 1) for h in range(H)]
+    spec = PartSpec("paged_attention", "a", {"hidden": d, "n_heads": H, "n_kv_heads": G, "head_dim": hd, "window": window,
+                                             "position": None, "score_slopes": slopes})
+    part = part_factory("mixer", "paged_attention")(spec, env_for(dtype, d, max_position=512))
+    w = {f"a.{k}_proj.weight": (rng.standard_normal(s) * 0.3).astype(np.float32)
+         for k, s in (("q", (H * hd, d)), ("k", (G * hd, d)), ("v", (G * hd, d)), ("o", (d, H * hd)))}
+    bind(part, w, dtype)
+    cache = CacheManager([part.cache_need()], page_size=16, num_pages=20, max_requests=1, dtype=DT[dtype], device="cuda")
+    req = cache.open()
+    x = rng.standard_normal((n, d)).astype(np.float32)
+    xt = torch.from_numpy(x).cuda().to(DT[dtype])
+    outs, start = [], 0
+    for cnt in [290] + [1] * 10:
+        cache.reserve(req, cnt)
+        ctx = one_request_context(cnt, start)
+        table = torch.full((1, 20), -1, dtype=torch.int32)
+        table[0, :len(req.tables[0])] = torch.tensor(req.tables[0])
+        outs.append(part.forward(xt[start:start + cnt], ctx, cache.layer_caches({0: table.cuda()})[0]))
+        cache.commit(req, cnt)
+        start += cnt
+    rnd = plain.round_act_bf16 if dtype == "bfloat16" else (lambda a: a)
+    ws = {k: stored(v, dtype) for k, v in w.items()}
+    xs = stored(x, dtype)
+    q, k, v = (rnd(xs @ ws[f"a.{m}_proj.weight"].T) for m in "qkv")
+    pos = np.arange(n)
+    mask = pos[:, None] >= pos[None, :]
+    if window:
+        mask &= pos[None, :] > pos[:, None] - window
+    att = np.zeros((n, H * hd))
+    for h in range(H):
+        g = h // (H // G)
+        sc = (q[:, h * hd:(h + 1) * hd] @ k[:, g * hd:(g + 1) * hd].T) / math.sqrt(hd) + slopes[h] * (pos[None, :] - pos[:, None])
+        sc = np.where(mask, sc, -np.inf)
+        p = np.exp(sc - sc.max(axis=1, keepdims=True))
+        att[:, h * hd:(h + 1) * hd] = (p @ v[:, g * hd:(g + 1) * hd]) / p.sum(axis=1, keepdims=True)
+    close(torch.cat(outs), rnd(att) @ ws["a.o_proj.weight"].T, dtype, "attention with a bias on the scores")
