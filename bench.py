@@ -388,7 +388,7 @@ def main():
     def prefill_run(eng, T=args.prefill_tokens):
         ids = prompts(1, T)[0]
         times = []
-        for _ in range(6):
+        for _ in range(7):                                  # the first two are warm-up (library set-up, first use of a route)
             req = eng.cache.open()
             ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
@@ -398,14 +398,15 @@ def main():
             torch.cuda.synchronize()
             times.append(ev0.elapsed_time(ev1))
             eng.cache.close(req)
-        ms = median(times[1:])
+        times = times[2:]
+        ms = median(times)
         per_layer, _ = model_bytes_and_flops(cfg, layers)
         qd = cfg["num_attention_heads"] * cfg["head_dim"]
         flops = 2 * T * (per_layer * layers) + 2 * cfg["vocab_size"] * cfg["hidden_size"] \
             + 2 * T * T * qd * layers          # causal attention: QK^T and PV over half the square
         out = {"value": round(T / (ms * 1e-3), 1), "tokens": T, "ms": round(ms, 3),
                "frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
-               "spread_ms": [round(min(times[1:]), 3), round(max(times[1:]), 3)]}
+               "spread_ms": [round(min(times), 3), round(max(times), 3)]}
         if eng.dtype != torch.bfloat16:
             out["frac_of"] = "bf16 tensor peak (the float32 path does not use tensor cores)"
         return out
