@@ -315,7 +315,9 @@ def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: 
         q_start, start_pos, table, n_req = q_start[singles:], start_pos[singles:], block_table[singles:], n_req - singles
     if tc and USE_TCGEN05 and head_dim in TCGEN05_HEAD_DIMS and group <= 128:
         return attention_prefill_tcgen05(out, q, kcache, vcache, q_start, start_pos, table,
-                                         n_req, n_heads, n_kv, head_dim, window, scale)
+                                         n_req, n_heads, n_kv, head_dim, window, scale,
+                                         probabilities=tcgen05_form(head_dim, group, n_kv, ctx.n_tokens - singles,
+                                                                    n_req, ctx.max_ctx))
     if tc and group <= 64:
         return attention_prefill(out, q, kcache, vcache, q_start, start_pos, table,
                                  n_req, n_heads, n_kv, head_dim, window, scale)
@@ -407,6 +409,20 @@ def attention_prefill(out, q, kcache, vcache, q_start, start_pos, block_table, n
     _check(lib, "attention_tc", rc)
 
 
+def tcgen05_form(head_dim: int, group: int, n_kv: int, n_tokens: int, n_requests: int, max_ctx: int) -> str:
+    """Which of the two tcgen05 attention kernels a step of portions takes ("smem" / "tmem",
+    see ``attention_prefill_tcgen05``), from measurements (profiles/attn_prefill_tc5_forms.md):
+    head size 128 always keeps its probabilities in tensor memory.  At head size 64 that form
+    (four CTAs per SM) wins when the step is many short chains of tiles or several waves of
+    CTAs, and loses to the other (two CTAs per SM, two score buffers) when one long prompt's
+    longest chain is the whole kernel: all CTAs resident at once and more than 16 key tiles."""
+    if head_dim != 64:
+        return "tmem"
+    ctas = (n_tokens // max(1, 128 // group) + n_requests) * n_kv
+    tiles = -(-max_ctx // 64)
+    return "tmem" if tiles <= 16 or ctas >= 6 * sm_count() else "smem"
+
+
 def attention_prefill_tcgen05(out, q, kcache, vcache, q_start, start_pos, block_table, n_requests, n_heads, n_kv,
                               head_dim, window, scale, probabilities: Optional[str] = None) -> None:
     """Attention of portions on tcgen05 tensor cores with TMEM accumulators (head size
@@ -415,9 +431,9 @@ def attention_prefill_tcgen05(out, q, kcache, vcache, q_start, start_pos, block_
     (csrc/attention_tcgen05.cu: two score buffers in tensor memory, P through shared
     memory, two CTAs of head size 64 per SM) or ``"tmem"`` (csrc/attention_tcgen05_ptmem.cu:
     P written over the scores in tensor memory and read from there, half the tensor memory
-    and shared memory per CTA, four / two CTAs per SM).  Default: the faster one as measured,
-    tmem for head size 128 (1.3 to 1.6 times faster), smem for head size 64 (equal within
-    a tenth either way; smem wins for a single long prompt, tmem for many portions)."""
+    and shared memory per CTA, four / two CTAs per SM).  Default (no step shape known): tmem
+    for head size 128 (1.3 to 1.6 times faster), smem for head size 64; ``attention`` picks
+    by the step's shape (``tcgen05_form``)."""
     _cuda(out, q, kcache, vcache, q_start, start_pos, block_table)
     _check_attention(out, q, kcache, vcache, block_table, n_kv, head_dim)
     _i32(q_start, "q_start"); _i32(start_pos, "start_pos")

@@ -443,6 +443,15 @@ def fused_decode_case(H, G, hd, page, splits, window):
             assert torch.equal(vc[pg, :, slot].float().cpu(), torch.from_numpy(as_stored(vnew[s], "bfloat16").reshape(G, hd)).float())
 
 
+def test_tcgen05_form_follows_the_measurements():
+    from kllm_b200 import kernels
+    assert kernels.tcgen05_form(128, 4, 8, 2048, 1, 2048) == "tmem"
+    assert kernels.tcgen05_form(64, 8, 4, 2048, 1, 2048) == "smem"        # one prompt of 2048: its longest chain rules
+    assert kernels.tcgen05_form(64, 8, 4, 8192, 1, 8192) == "tmem"        # several waves of CTAs
+    assert kernels.tcgen05_form(64, 8, 4, 4096, 8, 512) == "tmem"         # many short chains
+    assert kernels.tcgen05_form(64, 8, 4, 700, 1, 700) == "tmem"
+
+
 def test_tensor_core_attention_refusals():
     from kllm_b200 import kernels
     q = torch.zeros(1, 34 * 64, device="cuda", dtype=torch.bfloat16)
