@@ -86,33 +86,37 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
 // shared-memory writes of this thread become visible to the tensor core's (async proxy) reads
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 
-// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor
-// version 1.  K-major operands: 8-row groups 1024 bytes apart (stride offset), leading
-// offset 1.  MN-major operands: 8-k groups 1024 bytes apart (stride offset), 64-element
-// panels `lbo_bytes` apart (leading offset).
-__device__ __forceinline__ uint64_t make_desc(unsigned addr, unsigned lbo_bytes, unsigned sbo_bytes) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr >> 4) & 0x3FFF);
-    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
-    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
-    d |= (uint64_t)1 << 46;       // descriptor version for this architecture
-    d |= (uint64_t)2 << 61;       // SWIZZLE_128B
-    return d;
-}
-
 // Instruction descriptor: float32 accumulator, bfloat16 A and B, M x N, B optionally MN-major.
 __host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool b_mn_major) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
            ((uint32_t)(m >> 4) << 24);
 }
 
-// D += A . B with the A operand in tensor memory: row i of A in lane i, its k elements in
-// consecutive columns, two bfloat16 per 32-bit column (8 columns for the 16 k of one instruction)
-__device__ __forceinline__ void umma_tmem_a(unsigned d_tmem, unsigned a_tmem, uint64_t b_desc, uint32_t idesc, bool accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
-                 ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"((unsigned)accumulate) : "memory");
+// Shared-memory matrix descriptors, 128-byte swizzle (layout type 2), descriptor version 1, in
+// two words.  K-major operands: 8-row groups 1024 bytes apart (stride offset), leading offset 1.
+// MN-major operands: 8-k groups 1024 bytes apart (stride offset), 64-element panels `lbo_bytes`
+// apart (leading offset).  The high word is the same for every tile of an operand kind, the low
+// word holds the address (in units of 16 bytes, so the next k step or the next stage is one
+// integer add).  With the A operand in tensor memory: row i of A in lane i, its k elements in
+// consecutive columns, two bfloat16 per 32-bit column (8 columns for the 16 k of one instruction).  The issuing thread shares its scheduler with softmax
+// warps, and every instruction it needs per tcgen05.mma delays the tensor core's next one.
+__device__ __forceinline__ uint32_t desc_lo(unsigned addr, unsigned lbo_bytes) {
+    return ((addr >> 4) & 0x3FFFu) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
 }
+__host__ __device__ constexpr uint32_t desc_hi(unsigned sbo_bytes) {
+    return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);       // stride offset, descriptor version, SWIZZLE_128B
+}
+__device__ __forceinline__ void umma_words(unsigned d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, bool accumulate) {
+    asm volatile("{\n.reg .pred p;\n.reg .b64 da, db;\nsetp.ne.b32 p, %5, 0;\nmov.b64 da, {%1, %3};\nmov.b64 db, {%2, %3};\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n}\n"
+                 ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi(1024)), "r"(idesc), "r"((unsigned)accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_tmem_a_words(unsigned d_tmem, unsigned a_tmem, uint32_t b_lo, uint32_t idesc, bool accumulate) {
+    asm volatile("{\n.reg .pred p;\n.reg .b64 db;\nsetp.ne.b32 p, %5, 0;\nmov.b64 db, {%2, %3};\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n}\n"
+                 ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(desc_hi(1024)), "r"(idesc), "r"((unsigned)accumulate) : "memory");
+}
+
 __device__ __forceinline__ void tmem_st32(unsigned taddr, const uint32_t (&r)[32]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
                  "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
@@ -259,14 +263,14 @@ attn_prefill_tc5_ptmem_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
         // ---- the issuer: S(0), then per tile P.V(j) and S(j + 1), in this order ------------
         constexpr uint32_t IDESC_S = make_idesc(ROWS, TILE, false);
         constexpr uint32_t IDESC_O = make_idesc(ROWS, HD, true);
+        const uint32_t q_lo = desc_lo(sQ, 16), k_lo0 = desc_lo(sKV, 16), v_lo0 = desc_lo(sKV + KV_BYTES, TILE * 128);
+        const unsigned t_s = tmem + COL_S, t_o = tmem + COL_O;
         auto issue_scores = [&](int s) {
-            const unsigned st = sKV + (unsigned)s * 2u * KV_BYTES;
+            const uint32_t k_lo = k_lo0 + (uint32_t)s * (2u * KV_BYTES >> 4);
 #pragma unroll
-            for (int kk = 0; kk < HD / 16; kk++) {
-                const unsigned a = sQ + (unsigned)((kk >> 2) * (ROWS * 128) + (kk & 3) * 32);
-                const unsigned bb = st + (unsigned)((kk >> 2) * (TILE * 128) + (kk & 3) * 32);
-                umma(tmem + COL_S, make_desc(a, 16, 1024), make_desc(bb, 16, 1024), IDESC_S, kk > 0);
-            }
+            for (int kk = 0; kk < HD / 16; kk++)
+                umma_words(t_s, q_lo + (uint32_t)(((kk >> 2) * (ROWS * 128) + (kk & 3) * 32) >> 4),
+                           k_lo + (uint32_t)(((kk >> 2) * (TILE * 128) + (kk & 3) * 32) >> 4), IDESC_S, kk > 0);
             umma_commit(&bar_s_full);
         };
         bool ok = mbar_wait(&bar_q_full, 0, abort_flag, status, 2) &&
@@ -284,13 +288,10 @@ attn_prefill_tc5_ptmem_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
             if (!ok) break;
             tc_fence_after();
             if (lane == 0) {                   // output += P . V
-                const unsigned st = sKV + (unsigned)s * 2u * KV_BYTES;
+                const uint32_t v_lo = v_lo0 + (uint32_t)s * (2u * KV_BYTES >> 4);
 #pragma unroll
-                for (int kk = 0; kk < TILE / 16; kk++) {
-                    const unsigned bb = st + KV_BYTES + (unsigned)(kk * 2048);
-                    umma_tmem_a(tmem + COL_O, tmem + COL_S + (unsigned)(kk * 8), make_desc(bb, TILE * 128, 1024), IDESC_O,
-                                j > 0 || kk > 0);
-                }
+                for (int kk = 0; kk < TILE / 16; kk++)
+                    umma_tmem_a_words(t_o, t_s + (unsigned)(kk * 8), v_lo + (uint32_t)(kk * (2048 >> 4)), IDESC_O, j > 0 || kk > 0);
                 umma_commit(&bar_kv_empty[s]);             // this stage's K was read by the scores before
                 if (j == ntiles - 1) umma_commit(&bar_o_full);
             }
