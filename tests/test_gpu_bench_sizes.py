@@ -176,3 +176,38 @@ def test_every_way_of_cutting_at_bench_sizes(shape, dtype, monkeypatch):
     check("m1", 1, 0, len(seqs[1]), "mixed")
     check("m2", 2, 0, len(seqs[2]), "mixed")
     check("m3", 3, 0, len(seqs[3]), "mixed")
+
+
+def test_float32_decode_logits_do_not_depend_on_the_batch_bit_for_bit(shape):
+    """The float32 path's decode steps run kernels of this repository only (for up to 8 tokens a
+    step), and each of them sums a row in an order that depends on that row alone.  So a request
+    that is decoded alone and the same request decoded beside three others (its prompt prefilled
+    alone both times, so that the caches hold the same bits) must give the same logits bit for
+    bit, not merely within a tolerance."""
+    from kllm_b200.engine import Engine, Options, StepEntry
+    cfg, seqs, page = shape["cfg"], shape["seqs"], shape["page"]
+    eng = Engine(shape["dir"], Options(dtype="float32", max_seq=768, block_size=page, num_blocks=4 * (768 // page),
+                                       max_batch=4, max_step_tokens=1024))
+    runs = []
+    for together in (False, True):
+        reqs = [eng.cache.open() for _ in seqs]
+        for r, ids in zip(reqs, seqs):
+            eng.step([StepEntry(r, ids[:-8], [])])              # every prompt alone, the same steps in both runs
+        rows = []
+        for k in range(8, 0, -1):
+            entries = [StepEntry(r, [ids[len(ids) - k]], [0]) for r, ids in zip(reqs, seqs)]
+            if together:
+                rows.append(eng.step(entries)[0].cpu().numpy())
+            else:
+                rows.append(eng.step(entries[:1])[0].cpu().numpy())
+                for e in entries[1:]:
+                    eng.step([e])
+        runs.append(np.stack(rows))
+        for r in reqs:
+            eng.cache.close(r)
+    eng.close()
+    assert np.array_equal(runs[0], runs[1]), (
+        f"{shape['name']}: float32 logits of a request decoded alone and in a batch of 4 differ by "
+        f"{np.abs(runs[0] - runs[1]).max():.3e}")
+    want = plain_logits(shape["weights"], cfg, seqs[0], "float32") if "float32" not in shape["plain"] else shape["plain"]["float32"][0]
+    assert_close(runs[0], want[-8:], "float32", f"{shape['name']} float32 last 8 tokens alone")
