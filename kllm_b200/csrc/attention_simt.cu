@@ -76,7 +76,10 @@ attn_simt_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restr
     griddep_launch();
 
     // which request and which of its tiles this CTA has
-    int tile = blockIdx.x, s = 0, n_new = 0;
+    // CTAs start in the order of blockIdx.x: portions hand out their tiles back to front, every
+    // kv head's share of a tile next to each other, so that the longest key ranges start first
+    const int g = blockIdx.x % n_kv;
+    int tile = chunk > 0 ? blockIdx.x / n_kv : (gridDim.x - 1 - blockIdx.x) / n_kv, s = 0, n_new = 0;
     if (chunk > 0) {
         // keys in chunks: the launcher vouches that every request brings one token, tile = request
         s = tile;
@@ -95,7 +98,7 @@ attn_simt_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restr
     }
     const int q0 = tile * qt;
     const int nq = min(qt, n_new - q0);
-    const int gs = n_heads / n_kv, g = blockIdx.y, split = blockIdx.z;
+    const int gs = n_heads / n_kv, split = blockIdx.z;
     const int R = nq * gs;
     const int tok0 = q_start[s] + q0;
     const int p0 = start_pos[s] + q0;                       // position of the tile's first token
@@ -351,7 +354,7 @@ int launch(void* out, float* part_o, float* part_ml, const void* q, int64_t q_st
         }
         raised = true;
     }
-    kllm_launch(kern, dim3(max_tiles, n_kv, chunk > 0 ? max_splits : 1), dim3(THREADS), smem, s, (T*)out, part_o,
+    kllm_launch(kern, dim3(max_tiles * n_kv, 1, chunk > 0 ? max_splits : 1), dim3(THREADS), smem, s, (T*)out, part_o,
                 part_ml, (const T*)q, q_stride, (const T*)kcache, (const T*)vcache, q_start, start_pos, block_table,
                 max_blocks, n_requests, n_heads, n_kv, hd, page_size, window, scale, qt, chunk, max_splits, slopes);
     KLLM_LAUNCH_STATUS();

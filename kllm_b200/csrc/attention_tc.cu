@@ -541,14 +541,14 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t 
     __shared__ int s_req, s_tok0;
     griddep_wait();
     griddep_launch();
-    const int g = blockIdx.y;
+    const int g = blockIdx.x % n_kv;
     const int gs = n_heads / n_kv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tq = lane & 3;
     if (threadIdx.x == 0) {
-        // CTAs start in the order of blockIdx.x: hand out the tiles back to front, so
-        // that those with the longest key ranges (the ends of the portions) start first
-        // and the short ones fill the tail of the launch
-        int tile = gridDim.x - 1 - blockIdx.x, req = -1, tok0 = 0;
+        // CTAs start in the order of blockIdx.x: hand out the tiles back to front, every
+        // kv head's share of a tile next to each other, so that those with the longest key
+        // ranges (the ends of the portions) start first and the short ones fill the tail
+        int tile = (gridDim.x - 1 - blockIdx.x) / n_kv, req = -1, tok0 = 0;
         for (int s = 0; s < n_requests; s++) {
             const int n = q_start[s + 1] - q_start[s];
             const int nt = (n + tokens_per_tile - 1) / tokens_per_tile;
@@ -926,9 +926,8 @@ extern "C" int kllm_attention_prefill(void* out, const void* q, int64_t q_stride
     if ((rc = set_attributes())) return rc;
     const int tpt = PRE_ROWS / gs;
     const int max_tiles = n_tokens / tpt + n_requests;          // >= sum of ceil(n_s / tpt)
-    if (n_kv > 65535) KLLM_FAIL("attention prefill: grid too large");
     const float sl2e = scale * 1.4426950408889634f;
-    dim3 grid(max_tiles, n_kv);
+    dim3 grid(max_tiles * n_kv);
     kllm_launch((attn_prefill_kernel), dim3(grid), dim3(THREADS), PRE_SMEM_BYTES, (cudaStream_t)stream, 
         (bf16*)out, (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache, q_start, start_pos,
         block_table, max_blocks, n_requests, n_heads, n_kv, page_size, window, sl2e, tpt);

@@ -196,11 +196,11 @@ attn_prefill_tc5_ptmem_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
     __shared__ __align__(8) uint64_t bar_kv_full[STAGES], bar_kv_empty[STAGES], bar_q_full, bar_s_full, bar_p_full, bar_o_full;
     __shared__ unsigned s_tmem;
     __shared__ int s_req, s_tok0, s_abort;
-    const int g = blockIdx.y;
+    const int g = blockIdx.x % n_kv;          // CTAs start in the order of blockIdx.x: all kv heads' longest tiles first
     const int gs = n_heads / n_kv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        int tile = gridDim.x - 1 - blockIdx.x, req = -1, tok0 = 0;       // longest key ranges first
+        int tile = (gridDim.x - 1 - blockIdx.x) / n_kv, req = -1, tok0 = 0;       // longest key ranges first
         for (int s = 0; s < n_requests; s++) {
             const int n = q_start[s + 1] - q_start[s];
             const int nt = (n + tokens_per_tile - 1) / tokens_per_tile;
@@ -466,9 +466,8 @@ extern "C" int kllm_attention_prefill_tcgen05_ptmem(void* out, const void* q, in
     }
     const int tpt = ROWS / gs;
     const int max_tiles = n_tokens / tpt + n_requests;
-    if (n_kv > 65535) KLLM_FAIL("attention: grid too large");
     const float sl2e = scale * 1.4426950408889634f;
-    kllm_launch((attn_prefill_tc5_ptmem_kernel), dim3(max_tiles, n_kv), dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream,
+    kllm_launch((attn_prefill_tc5_ptmem_kernel), dim3(max_tiles * n_kv), dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream,
                 (bf16*)out, (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache, q_start, start_pos,
                 block_table, max_blocks, n_requests, n_heads, n_kv, page_size, window, sl2e, tpt, status);
     KLLM_LAUNCH_STATUS();
