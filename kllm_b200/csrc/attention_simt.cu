@@ -279,6 +279,222 @@ attn_simt_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restr
     }
 }
 
+// ---- one chunk of one decoding token, float32 storage, head size 64 or 128 ---------
+// The tile kernel above gives a decoding token's 1 to 16 rows (the heads of a kv group)
+// an eighth of its threads.  Here every thread works: the chunk is walked in sub-tiles of
+// KT keys (K and V by 16-byte asynchronous copies, a key's row contiguous); for the scores
+// thread (key, head group) forms the dot products of its key with its heads' queries, which
+// it reads as broadcasts; one warp per head runs the online softmax over the sub-tile; for
+// the second product thread (dims 4 d4 .. 4 d4 + 3, up to four heads, key group) adds up
+// its keys, and the key groups' sums meet in shared memory in group order.  Same partial
+// results, in the same layout, as the tile kernel writes for a chunk; every sum's order
+// depends on the token's position, the window and the head alone.
+__device__ __forceinline__ void cp_async16_zfill(float* smem_dst, const float* src, bool valid) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    const int bytes = valid ? 16 : 0;                       // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
+
+constexpr int DEC_THREADS = 256;
+constexpr int dec_keys(int hd) { return 8192 / hd; }                        // keys of a sub-tile: 128 or 64
+constexpr size_t dec_smem_floats(int hd, int gs) {
+    return (size_t)2 * dec_keys(hd) * (hd + 4) + (size_t)gs * hd + (size_t)dec_keys(hd) * gs + 3 * gs;
+}
+
+template <int HD, int GS>
+__global__ void __launch_bounds__(DEC_THREADS, 2)
+attn_simt_decode_kernel(float* __restrict__ part_o, float* __restrict__ part_ml, const float* __restrict__ q,
+                        int64_t q_stride, const float* __restrict__ kcache, const float* __restrict__ vcache,
+                        const int* __restrict__ q_start, const int* __restrict__ start_pos,
+                        const int* __restrict__ block_table, int max_blocks, int n_requests, int n_heads, int n_kv,
+                        int page_size, int window, float scale, int chunk, int max_splits,
+                        const float* __restrict__ slopes) {
+    constexpr int KT = dec_keys(HD), LD = HD + 4, D4 = HD / 4;
+    constexpr int HGRP = DEC_THREADS / KT;                  // head groups of the first product
+    constexpr int HPG = (GS + HGRP - 1) / HGRP;             // heads of a group
+    constexpr int HPT = GS < 4 ? GS : 4;                    // heads of a thread in the second product
+    constexpr int HG3 = GS / HPT, KG = DEC_THREADS / (D4 * HG3), KPG = KT / KG;
+    static_assert(KG >= 1 && KPG >= 1 && KG * KPG == KT && HG3 * HPT == GS, "thread layout");
+    extern __shared__ __align__(16) float sm[];
+    float* Ks = sm;                                         // [KT][LD]; at the end the key groups' sums
+    float* Vs = Ks + KT * LD;                               // [KT][LD]
+    float* Qs = Vs + KT * LD;                               // [GS][HD]
+    float* Ps = Qs + GS * HD;                               // [KT][GS]: scores, then probabilities
+    float* m_s = Ps + KT * GS;                              // [GS] running maximum, sum, and this sub-tile's factor
+    float* l_s = m_s + GS;
+    float* a_s = l_s + GS;
+    griddep_wait();
+    griddep_launch();
+    const int g = blockIdx.x % n_kv, s = blockIdx.x / n_kv, split = blockIdx.z;
+    if (s >= n_requests) return;
+    const int tok = q_start[s], pos = start_pos[s];
+    const int lo_all = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+    const int lo = lo_all + split * chunk, hi = min(pos + 1, lo + chunk);
+    if (lo >= hi) return;
+    const int* table = block_table + (int64_t)s * max_blocks;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    auto load_tile = [&](int key0) {
+#pragma unroll
+        for (int u = 0; u < KT * D4 / DEC_THREADS; u++) {
+            const int e = tid + u * DEC_THREADS, k = e / D4, c = e - k * D4, kp = key0 + k;
+            const bool ok = kp < hi;
+            int64_t off = 0;
+            if (ok) {
+                const int lp = kp / page_size;
+                off = (((int64_t)table[lp] * n_kv + g) * page_size + (kp - lp * page_size)) * HD + 4 * c;
+            }
+            cp_async16_zfill(Ks + k * LD + 4 * c, kcache + off, ok);
+            cp_async16_zfill(Vs + k * LD + 4 * c, vcache + off, ok);
+        }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
+    load_tile(lo);
+    for (int e = tid; e < GS * D4; e += DEC_THREADS) {
+        const int h = e / D4, c = e - h * D4;
+        *reinterpret_cast<float4*>(Qs + h * HD + 4 * c) =
+            __ldg(reinterpret_cast<const float4*>(q + (int64_t)tok * q_stride + (int64_t)(g * GS + h) * HD + 4 * c));
+    }
+    if (tid < GS) { m_s[tid] = -INFINITY; l_s[tid] = 0.f; }
+
+    const int k1 = tid % KT, hg1 = tid / KT;                // first product: key and head group
+    const int d4 = tid % D4, hg3 = (tid / D4) % HG3, kg = tid / (D4 * HG3);   // second product
+    float4 acc[HPT];
+#pragma unroll
+    for (int i = 0; i < HPT; i++) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+
+    for (int key0 = lo; key0 < hi; key0 += KT) {
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        __syncthreads();
+        // ---- scores of key k1 with the heads of group hg1 ----
+        {
+            float4 sc[HPG];
+#pragma unroll
+            for (int i = 0; i < HPG; i++) sc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (hg1 * HPG < GS) {
+#pragma unroll 4
+                for (int c = 0; c < D4; c++) {
+                    const float4 kv = *reinterpret_cast<const float4*>(Ks + k1 * LD + 4 * c);
+#pragma unroll
+                    for (int i = 0; i < HPG; i++) {
+                        const int h = hg1 * HPG + i;
+                        if (h < GS) {
+                            const float4 qv = *reinterpret_cast<const float4*>(Qs + h * HD + 4 * c);
+                            sc[i].x += qv.x * kv.x; sc[i].y += qv.y * kv.y; sc[i].z += qv.z * kv.z; sc[i].w += qv.w * kv.w;
+                        }
+                    }
+                }
+                const int kp = key0 + k1;
+#pragma unroll
+                for (int i = 0; i < HPG; i++) {
+                    const int h = hg1 * HPG + i;
+                    if (h < GS) {
+                        float v = ((sc[i].x + sc[i].y) + (sc[i].z + sc[i].w)) * scale;
+                        if (slopes) v += slopes[g * GS + h] * (float)(kp - pos);
+                        Ps[k1 * GS + h] = kp < hi ? v : -INFINITY;
+                    }
+                }
+            }
+        }
+        __syncthreads();
+        // ---- online softmax: one warp per head over the sub-tile's keys ----
+        for (int h = warp; h < GS; h += DEC_THREADS / 32) {
+            float v[KT / 32], mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < KT / 32; j++) {
+                v[j] = Ps[(lane + 32 * j) * GS + h];
+                mx = fmaxf(mx, v[j]);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            const float m_old = m_s[h], m_new = fmaxf(m_old, mx);        // finite: key0 itself is below hi
+            float sum = 0.f;
+#pragma unroll
+            for (int j = 0; j < KT / 32; j++) {
+                const float pj = expf(v[j] - m_new);                    // 0 for a key past the end
+                Ps[(lane + 32 * j) * GS + h] = pj;
+                sum += pj;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if (lane == 0) {
+                const float alpha = expf(m_old - m_new);                // 0 while nothing had been seen
+                a_s[h] = alpha;
+                l_s[h] = l_s[h] * alpha + sum;
+                m_s[h] = m_new;
+            }
+        }
+        __syncthreads();
+        // ---- probabilities x values: dims 4 d4 .. + 3 of heads hg3 * HPT .. of the keys of group kg ----
+        {
+#pragma unroll
+            for (int i = 0; i < HPT; i++) {
+                const float al = a_s[hg3 * HPT + i];
+                acc[i].x *= al; acc[i].y *= al; acc[i].z *= al; acc[i].w *= al;
+            }
+#pragma unroll 4
+            for (int kk = 0; kk < KPG; kk++) {
+                const int k = kg * KPG + kk;
+                const float4 vv = *reinterpret_cast<const float4*>(Vs + k * LD + 4 * d4);
+                float pr[HPT];
+                if constexpr (HPT == 4) {
+                    const float4 p4 = *reinterpret_cast<const float4*>(Ps + k * GS + hg3 * 4);
+                    pr[0] = p4.x; pr[1] = p4.y; pr[2] = p4.z; pr[3] = p4.w;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < HPT; i++) pr[i] = Ps[k * GS + hg3 * HPT + i];
+                }
+#pragma unroll
+                for (int i = 0; i < HPT; i++) {
+                    acc[i].x += pr[i] * vv.x; acc[i].y += pr[i] * vv.y; acc[i].z += pr[i] * vv.z; acc[i].w += pr[i] * vv.w;
+                }
+            }
+        }
+        __syncthreads();                                    // K, V and P of this sub-tile are no longer read
+        if (key0 + KT < hi) load_tile(key0 + KT);
+    }
+    // ---- the key groups' sums, added in group order ----
+    float* red = Ks;                                        // [KG][GS][HD]
+#pragma unroll
+    for (int i = 0; i < HPT; i++)
+        *reinterpret_cast<float4*>(red + ((size_t)kg * GS + hg3 * HPT + i) * HD + 4 * d4) = acc[i];
+    __syncthreads();
+    for (int e = tid; e < GS * D4; e += DEC_THREADS) {
+        const int h = e / D4, c = e - h * D4;
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < KG; k++) {
+            const float4 v = *reinterpret_cast<const float4*>(red + ((size_t)k * GS + h) * HD + 4 * c);
+            o.x += v.x; o.y += v.y; o.z += v.z; o.w += v.w;
+        }
+        const int64_t row = (int64_t)tok * n_heads + g * GS + h;
+        *reinterpret_cast<float4*>(part_o + (row * max_splits + split) * HD + 4 * c) = o;
+        if (c == 0) *reinterpret_cast<float2*>(part_ml + (row * max_splits + split) * 2) = make_float2(m_s[h], l_s[h]);
+    }
+}
+
+template <int HD, int GS>
+int launch_decode(float* part_o, float* part_ml, const void* q, int64_t q_stride, const void* kcache, const void* vcache,
+                  const int* q_start, const int* start_pos, const int* block_table, int max_blocks, int n_requests,
+                  int n_heads, int n_kv, int page_size, int window, float scale, int chunk, int max_splits,
+                  const float* slopes, cudaStream_t s) {
+    auto kern = attn_simt_decode_kernel<HD, GS>;
+    static bool raised = false;
+    constexpr size_t smem = dec_smem_floats(HD, GS) * sizeof(float);
+    if (!raised) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            snprintf(g_kllm_err, sizeof(g_kllm_err), "attention (simt, decode): shared memory limit: %s", cudaGetErrorString(e));
+            return (int)e;
+        }
+        raised = true;
+    }
+    kllm_launch(kern, dim3(n_requests * n_kv, 1, max_splits), dim3(DEC_THREADS), smem, s, part_o, part_ml, (const float*)q,
+                q_stride, (const float*)kcache, (const float*)vcache, q_start, start_pos, block_table, max_blocks,
+                n_requests, n_heads, n_kv, page_size, window, scale, chunk, max_splits, slopes);
+    KLLM_LAUNCH_STATUS();
+}
+
 // One warp per (token, head): the chunks' partial results, weighted by exp(m_chunk - max)
 // and added in chunk order.
 template <typename T>
@@ -389,6 +605,17 @@ extern "C" int kllm_attention_simt(void* out, void* part_o, void* part_ml, const
     if (((uintptr_t)q | (uintptr_t)kcache | (uintptr_t)vcache | (uintptr_t)out) % (4 * esize) || (q_stride % 4))
         KLLM_FAIL("attention (simt): operands must be aligned to four elements");
     cudaStream_t s = (cudaStream_t)stream;
+    // decoding tokens in float32 at the common head sizes and group widths: the kernel in which every thread works
+    if (chunk > 0 && dtype == KLLM_F32 && (hd == 64 || hd == 128) && n_requests == max_tiles) {
+#define KLLM_SIMT_DEC(HD_, GS_)                                                                                        \
+    if (hd == HD_ && gs == GS_)                                                                                       \
+        return launch_decode<HD_, GS_>((float*)part_o, (float*)part_ml, q, q_stride, kcache, vcache, q_start, start_pos, \
+                                       block_table, max_blocks, n_requests, n_heads, n_kv, page_size, window, scale,  \
+                                       chunk, max_splits, slopes, s)
+        KLLM_SIMT_DEC(64, 1); KLLM_SIMT_DEC(64, 2); KLLM_SIMT_DEC(64, 4); KLLM_SIMT_DEC(64, 8); KLLM_SIMT_DEC(64, 16);
+        KLLM_SIMT_DEC(128, 1); KLLM_SIMT_DEC(128, 2); KLLM_SIMT_DEC(128, 4); KLLM_SIMT_DEC(128, 8); KLLM_SIMT_DEC(128, 16);
+#undef KLLM_SIMT_DEC
+    }
 #define KLLM_SIMT(T, NC)                                                                                              \
     return launch<T, NC>(out, (float*)part_o, (float*)part_ml, q, q_stride, kcache, vcache, q_start, start_pos,      \
                          block_table, max_blocks, n_requests, max_tiles, n_heads, n_kv, hd, page_size, window, scale, \

@@ -249,6 +249,22 @@ def test_cuda_core_attention_portions_and_decoding_tokens(dtype, H, G, hd, page,
         close(got, want, dtype, f"lengths {lengths}")
 
 
+@pytest.mark.parametrize("gs", [1, 2, 4, 8, 16])
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("window", [None, 300])
+def test_float32_decode_attention_every_group_width(gs, hd, window):
+    """Decoding tokens in float32 at head sizes 64 and 128 take a kernel of their own (every
+    thread of the CTA works on a chunk of one token's keys): every width of a kv group it is
+    built for, contexts that end inside a chunk, a sub-tile and a page, one kv head and
+    three, beside a first token."""
+    for G, page in ((1, 16), (3, 5)):
+        lengths = [700, 257, 1, 300, 513, 1000, 129]
+        got, want = attention_case("float32", G * gs, G, hd, page, lengths, [1] * len(lengths), window,
+                                   seed=gs * hd + G, kernel="simt")
+        assert not torch.isnan(got).any(), "a slot beyond a request's length was read"
+        close(got, want, "float32", f"{G * gs} heads over {G} kv heads of {hd}")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_cuda_core_attention_finds_one_far_key_among_hundreds(dtype):
     H, G, hd, L = 4, 2, 32, 700
