@@ -108,7 +108,7 @@ __host__ __device__ inline int x_row_elems(int K) {      // row stride of X in s
     return K + (((K * 2) % 128 == 0) ? 32 : 0);           // bytes = 64 (mod 128): 16-byte reads of 8 rows x 4
 }                                                         // quarter-row offsets hit 8 different bank groups
 
-// EXACT (used with two token tiles): K is a multiple of 2048, so every warp has whole batches of k-steps only.
+// EXACT: K is a multiple of 2048, so every warp has whole batches of k-steps only.
 template <int NT, int PRO, int EPI, bool EXACT>
 __global__ void __launch_bounds__(THREADS)
 skinny_gemm_kernel(const Args a) {
@@ -145,9 +145,12 @@ skinny_gemm_kernel(const Args a) {
     // by memory: there a batch whose k-steps all exist is loaded and multiplied without a test
     // per step, its addresses fixed offsets from one pointer (EXACT: K is a multiple of 2048
     // and no batch needs the tests at all); 1.3 to 1.9 times faster than the loop with a test
-    // per step.  With one token tile that loop is the faster one (a decode step of batch 8:
-    // 0.802 ms against 0.822, alternating runs), so those kernels keep it.
-    constexpr bool WHOLE_BATCHES = NT == 2;
+    // per step.  With one token tile the loads keep their tests: without them a decode step
+    // of batch 8 was measured slower (0.822 ms against 0.802, alternating runs of the two
+    // builds), while its MMAs without the tests, where K is a multiple of 2048, make it a
+    // little faster (0.797).
+    constexpr bool WHOLE_BATCHES = NT == 2;              // loads without a test per step
+    constexpr bool WHOLE_MMA = NT == 2 || EXACT;         // MMAs without a test per step
     auto load_batch = [&](uint4 (&ra)[UNROLL], uint4 (&rb)[UNROLL], int tile, int b) {
         const bf16 *pa, *pb;
         row_ptrs(tile, pa, pb);
@@ -283,7 +286,7 @@ skinny_gemm_kernel(const Args a) {
         {
             const int s0 = cur_b * UNROLL;
             const bf16* xk = xs + g * XS + (warp + s0 * WARPS) * 32 + 8 * t;       // this lane's X row 0 at the batch's first k-step
-            if (WHOLE_BATCHES && (EXACT || s0 + UNROLL <= my_steps)) {
+            if (WHOLE_MMA && (EXACT || s0 + UNROLL <= my_steps)) {
 #pragma unroll
                 for (int u = 0; u < UNROLL; u++) {
 #pragma unroll
@@ -393,8 +396,7 @@ int launch_exact(const Args& a, cudaStream_t s) {
 
 template <int NT, int PRO, int EPI>
 int launch(const Args& a, cudaStream_t s) {
-    if (NT == 2 && a.K % (WARPS * UNROLL * 32) == 0) return launch_exact<NT, PRO, EPI, NT == 2>(a, s);
-    return launch_exact<NT, PRO, EPI, false>(a, s);
+    return a.K % (WARPS * UNROLL * 32) == 0 ? launch_exact<NT, PRO, EPI, true>(a, s) : launch_exact<NT, PRO, EPI, false>(a, s);
 }
 
 template <int NT, int PRO>
