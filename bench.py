@@ -230,10 +230,12 @@ def main():
     ap.add_argument("--repeats", type=int, default=0, help="how often the K-step region is timed (0: 5, or 3 for K > 40)")
     ap.add_argument("--prefill-tokens", type=int, default=2048, help="length of the timed prompt")
     ap.add_argument("--no-points", action="store_true", help="skip the further points and the prefill")
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "attention"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "attention", "products"],
                     help="decode: the batch's decode run alone; prefill: the 2048-token prompt alone (partial "
                          "records for profiling small cases, not the bench line); attention: the tcgen05 attention "
-                         "kernels of prompt portions alone, both forms, at a few shapes")
+                         "kernels of prompt portions alone, both forms, at a few shapes; products: the "
+                         "weight-streaming products of small steps alone, at --rows rows")
+    ap.add_argument("--rows", type=int, default=8, help="rows of X for --only products (1 to 16)")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
     ap.add_argument("--timeline", action="store_true",
                     help="decode run with the instrumented kernel builds; prints where the last step's time went, "
@@ -264,6 +266,8 @@ def main():
         return mixed_workload(args)
     if args.only == "attention":
         return attention_forms()
+    if args.only == "products":
+        return streaming_products(args.rows)
 
     cfg = dict(SHAPES[args.shape])
     cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], args.context, args.prefill_tokens)
@@ -530,6 +534,62 @@ def attention_forms():
         rows.append(rec)
         del caches
     print(json.dumps({"partial": "tcgen05 attention of prompt portions, both forms", "rows": rows}))
+    return 0
+
+
+def streaming_products(rows: int):
+    """The weight-streaming products of steps of up to 16 tokens (csrc/skinny_gemm.cu) alone:
+    microseconds per call and TB/s of weight bytes at ``rows`` rows of X, by CUDA events
+    over 24 calls replayed as a graph on weights that rotate through more than L2 holds.
+    One JSON record."""
+    import torch
+    from kllm_b200 import kernels
+    dev = "cuda"
+    torch.manual_seed(0)
+    cases = [("head 32000 x 2048", 32000, 2048, "norm", "f32"), ("head 128256 x 4096", 128256, 4096, "norm", "f32"),
+             ("gate/up 2 x 14336 x 4096", 14336, 4096, "norm", "swiglu"),
+             ("gate/up 2 x 5632 x 2048", 5632, 2048, "norm", "swiglu"), ("QKV 6144 x 4096", 6144, 4096, "norm", "bf16"),
+             ("QKV 2560 x 2048", 2560, 2048, "norm", "bf16"), ("down 2048 x 5632", 2048, 5632, "x", "add"),
+             ("down slice 4096 x 7168", 4096, 7168, "x", "add"), ("O 4096 x 4096", 4096, 4096, "x", "add"),
+             ("O 2048 x 2048", 2048, 2048, "x", "add")]
+    out = []
+    for name, N, K, pro, epi in cases:
+        mats = 2 if epi == "swiglu" else 1
+        copies = int(400e6 // (N * K * 2 * mats)) + 1
+        ws = [torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+        w2 = [torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(copies)] if mats == 2 else None
+        xf = torch.randn(rows, K, device=dev)
+        gain = torch.ones(K, device=dev)
+        xb = xf.to(torch.bfloat16)
+        acc = torch.zeros(rows, N, device=dev)
+        turn = [0]
+
+        def call():
+            j = turn[0] % copies
+            turn[0] += 1
+            if pro == "norm":
+                kernels.skinny_gemm(ws[j], x_f32=xf, gain=gain, eps=1e-5, weight_up=w2[j] if w2 else None, epilogue=epi)
+            else:
+                kernels.skinny_gemm(ws[j], x=xb, epilogue="add", out=acc)
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize()
+        graph, stream = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        with torch.cuda.stream(stream), torch.cuda.graph(graph, stream=stream):
+            for _ in range(24):
+                call()
+        times = []
+        for _ in range(8):
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+            graph.replay()
+            ev1.record()
+            torch.cuda.synchronize()
+            times.append(ev0.elapsed_time(ev1) / 24 * 1e3)
+        us = sorted(times)[len(times) // 2]
+        out.append({"product": name, "us": round(us, 1), "tb_per_s": round(N * K * 2 * mats / us / 1e6, 2)})
+        del ws, w2
+    print(json.dumps({"partial": f"weight-streaming products alone, {rows} rows", "rows": out}))
     return 0
 
 
