@@ -267,7 +267,7 @@ def main():
     if args.only == "attention":
         return attention_forms()
     if args.only == "products":
-        return streaming_products(args.rows)
+        return streaming_products(args.rows, args.dtype)
 
     cfg = dict(SHAPES[args.shape])
     cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], args.context, args.prefill_tokens)
@@ -537,8 +537,9 @@ def attention_forms():
     return 0
 
 
-def streaming_products(rows: int):
-    """The weight-streaming products of steps of up to 16 tokens (csrc/skinny_gemm.cu) alone:
+def streaming_products(rows: int, dtype: str = "bfloat16"):
+    """The weight-streaming products of steps of up to 16 tokens (csrc/skinny_gemm.cu; with
+    ``--dtype float32`` csrc/skinny_gemm_f32.cu, up to 8 rows, TinyLlama's shapes) alone:
     microseconds per call and TB/s of weight bytes at ``rows`` rows of X, by CUDA events
     over 24 calls replayed as a graph on weights that rotate through more than L2 holds.
     One JSON record."""
@@ -546,21 +547,27 @@ def streaming_products(rows: int):
     from kllm_b200 import kernels
     dev = "cuda"
     torch.manual_seed(0)
+    wt = torch.float32 if dtype == "float32" else torch.bfloat16
+    esize = 4 if dtype == "float32" else 2
     cases = [("head 32000 x 2048", 32000, 2048, "norm", "f32"), ("head 128256 x 4096", 128256, 4096, "norm", "f32"),
              ("gate/up 2 x 14336 x 4096", 14336, 4096, "norm", "swiglu"),
              ("gate/up 2 x 5632 x 2048", 5632, 2048, "norm", "swiglu"), ("QKV 6144 x 4096", 6144, 4096, "norm", "bf16"),
              ("QKV 2560 x 2048", 2560, 2048, "norm", "bf16"), ("down 2048 x 5632", 2048, 5632, "x", "add"),
              ("down slice 4096 x 7168", 4096, 7168, "x", "add"), ("O 4096 x 4096", 4096, 4096, "x", "add"),
              ("O 2048 x 2048", 2048, 2048, "x", "add")]
+    if dtype == "float32":
+        cases = [c for c in cases if c[2] in (2048, 5632) and c[1] != 32000] + [("head 32000 x 2048", 32000, 2048, "norm", "f32")]
     out = []
     for name, N, K, pro, epi in cases:
         mats = 2 if epi == "swiglu" else 1
-        copies = int(400e6 // (N * K * 2 * mats)) + 1
-        ws = [torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
-        w2 = [torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(copies)] if mats == 2 else None
+        copies = int(400e6 // (N * K * esize * mats)) + 1
+        ws = [(torch.randn(N, K, device=dev) * 0.02).to(wt) for _ in range(copies)]
+        w2 = [(torch.randn(N, K, device=dev) * 0.02).to(wt) for _ in range(copies)] if mats == 2 else None
         xf = torch.randn(rows, K, device=dev)
         gain = torch.ones(K, device=dev)
-        xb = xf.to(torch.bfloat16)
+        xb = xf.to(wt)
+        if epi in ("bf16", "f32"):
+            epi = "store"
         acc = torch.zeros(rows, N, device=dev)
         turn = [0]
 
@@ -587,9 +594,9 @@ def streaming_products(rows: int):
             torch.cuda.synchronize()
             times.append(ev0.elapsed_time(ev1) / 24 * 1e3)
         us = sorted(times)[len(times) // 2]
-        out.append({"product": name, "us": round(us, 1), "tb_per_s": round(N * K * 2 * mats / us / 1e6, 2)})
+        out.append({"product": name, "us": round(us, 1), "tb_per_s": round(N * K * esize * mats / us / 1e6, 2)})
         del ws, w2
-    print(json.dumps({"partial": f"weight-streaming products alone, {rows} rows", "rows": out}))
+    print(json.dumps({"partial": f"weight-streaming products alone, {rows} rows, {dtype}", "rows": out}))
     return 0
 
 
